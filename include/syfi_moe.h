@@ -1,0 +1,130 @@
+/*
+ * C ABI of the B200-native fused FP8 block-scale DeepSeek-V3 MoE layer
+ * (definition moe_fp8_block_scale_ds_routing_topk8_ng8_kg4_e32_h7168_i2048).
+ *
+ * This is the drop-in boundary for the reference's single exported function,
+ *   TVM_FFI_DLL_EXPORT_TYPED_FUNC(run_moe, run_impl)      moe/solution/cuda/moe.cu:3260
+ * whose typed signature is at moe/solution/cuda/moe.cu:2987-2998.  All pointers are
+ * DEVICE pointers to contiguous row-major tensors on the context's device unless a
+ * function says otherwise; nothing is owned by the library except its workspace.
+ * Every function returns 0 on success and a non-zero code on failure;
+ * syfi_moe_last_error() then returns a message for the calling thread.
+ * There is no CPU path: without a CUDA device every call fails.
+ */
+#ifndef SYFI_MOE_H_
+#define SYFI_MOE_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct syfi_moe_ctx syfi_moe_ctx;
+
+enum {
+  SYFI_MOE_OK = 0,
+  SYFI_MOE_ERR_INVALID = 1,   /* bad argument (null pointer, shape, expert range, alignment) */
+  SYFI_MOE_ERR_CUDA = 2,      /* a CUDA runtime / driver call failed */
+  SYFI_MOE_ERR_DEVICE = 3     /* a kernel reported a failure through the status word (bounded wait expired, bad index) */
+};
+
+/* Fixed problem sizes of the definition (reference constants: moe/solution/cuda/moe.cu:40-53). */
+#define SYFI_MOE_HIDDEN 7168
+#define SYFI_MOE_INTER 2048
+#define SYFI_MOE_EXPERTS_GLOBAL 256
+#define SYFI_MOE_TOP_K 8
+#define SYFI_MOE_MAX_LOCAL_EXPERTS 32
+
+/* Creates the per-device context and its workspace, sized for max_tokens tokens per call
+ * (it grows on demand).  Replaces the reference's file-static Workspace g_ws and its
+ * ensure_singletons / ensure_per_token / ensure_schedule (moe.cu:2832-2926). */
+int syfi_moe_create(int device, int64_t max_tokens, syfi_moe_ctx** out_ctx);
+
+/* Frees the workspace (the reference never frees, moe.cu:2896-2926). */
+int syfi_moe_destroy(syfi_moe_ctx* ctx);
+
+/* The layer.  Replaces run_impl / run_moe (moe.cu:2987-3258, exported at :3260), same argument
+ * order and meaning:
+ *   routing_logits       f32  [T, 256]
+ *   routing_bias         bf16 [256]
+ *   hidden_states        e4m3 [T, 7168]
+ *   hidden_states_scale  f32  [56, T]
+ *   gemm1_weights        e4m3 [E_local, 4096, 7168]   gemm1_weights_scale f32 [E_local, 32, 56]
+ *   gemm2_weights        e4m3 [E_local, 7168, 2048]   gemm2_weights_scale f32 [E_local, 56, 16]
+ *   local_expert_offset  first global expert owned by this call; experts [offset, offset + E_local)
+ *   routed_scaling_factor
+ *   output               bf16 [T, 7168] (destination-passing, moe/config.toml:10)
+ * Differences from the reference, all deliberate: E_local (1..32) is an argument so an
+ * expert-parallel rank can own a slice; work is enqueued on `stream` (a cudaStream_t; the
+ * reference uses stream 0, moe.cu:3005) and the call never synchronises with the host (the
+ * reference blocks on a device->host copy for T >= 128, moe.cu:3127-3131); arguments are
+ * validated.  T == 0 is a no-op, as in the reference (moe.cu:3001).
+ * Calls on one context must not overlap on the GPU (they share the workspace). */
+int syfi_moe_forward(syfi_moe_ctx* ctx, const void* routing_logits, const void* routing_bias,
+                     const void* hidden_states, const void* hidden_states_scale, const void* gemm1_weights,
+                     const void* gemm1_weights_scale, const void* gemm2_weights, const void* gemm2_weights_scale,
+                     int64_t num_tokens, int32_t num_local_experts, int64_t local_expert_offset,
+                     double routed_scaling_factor, void* output, void* stream);
+
+/* Same, but writes the un-rounded f32 [T, 7168] partial sum of this rank's experts instead of
+ * bf16 — what an expert-parallel rank feeds to the cross-rank reduction (the reference has no
+ * multi-GPU path; its only hook is local_expert_offset, moe.cu:182-185, 250-256). */
+int syfi_moe_forward_partial_f32(syfi_moe_ctx* ctx, const void* routing_logits, const void* routing_bias,
+                                 const void* hidden_states, const void* hidden_states_scale,
+                                 const void* gemm1_weights, const void* gemm1_weights_scale,
+                                 const void* gemm2_weights, const void* gemm2_weights_scale, int64_t num_tokens,
+                                 int32_t num_local_experts, int64_t local_expert_offset,
+                                 double routed_scaling_factor, void* output_f32, void* stream);
+
+/* Same as syfi_moe_forward but every tensor argument except the four weight tensors is a HOST
+ * pointer (pinned memory makes the copies asynchronous): inputs are copied to the device, the
+ * layer runs, the bf16 output is copied back and the stream is synchronised before returning.
+ * The reference's harness does these copies outside the kernel (moe/scripts/debug_correctness.py:35-55). */
+int syfi_moe_forward_host(syfi_moe_ctx* ctx, const void* routing_logits_host, const void* routing_bias_host,
+                          const void* hidden_states_host, const void* hidden_states_scale_host,
+                          const void* gemm1_weights, const void* gemm1_weights_scale, const void* gemm2_weights,
+                          const void* gemm2_weights_scale, int64_t num_tokens, int32_t num_local_experts,
+                          int64_t local_expert_offset, double routed_scaling_factor, void* output_host,
+                          void* stream);
+
+/* Router only (replaces route_kernel, moe.cu:62-188): writes topk_idx int32 [T, 8] (global expert
+ * ids, best first) and topk_weights f32 [T, 8] to DEVICE buffers supplied by the caller. */
+int syfi_moe_route(syfi_moe_ctx* ctx, const void* routing_logits, const void* routing_bias, int64_t num_tokens,
+                   int32_t num_local_experts, int64_t local_expert_offset, double routed_scaling_factor,
+                   int32_t* topk_idx, float* topk_weights, void* stream);
+
+/* Copies the routing result of the most recent forward on this context into HOST buffers
+ * (either may be null): topk_idx int32 [T, 8], topk_weights f32 [T, 8].  Synchronises `stream`. */
+int syfi_moe_last_routing(syfi_moe_ctx* ctx, int64_t num_tokens, int32_t* topk_idx_host, float* topk_weights_host,
+                          void* stream);
+
+/* Synchronises `stream`, then reads the device status word and the work counters of the most
+ * recent forward: stats[0] = token tiles, [1] = padded rows, [2] = routed (token, local expert)
+ * rows, [3] = active local experts (stats may be null).  Returns SYFI_MOE_ERR_DEVICE when a
+ * kernel gave up on a bounded wait (the reference's mbarrier waits spin for ever, moe.cu:1298-1305). */
+int syfi_moe_check(syfi_moe_ctx* ctx, int32_t* stats4, void* stream);
+
+/* Test hook: copies a named workspace buffer of the most recent forward into HOST memory
+ * ("row_token", "route_row", "tiles", "meta", "counts", "a_perm", "a_scale", "c_hi", "c_lo",
+ * "c_scale", "o_rows", "topk_idx", "topk_w").  *bytes receives the buffer's size; at most
+ * max_bytes are copied (dst_host may be null to query the size); *row_cap receives the row
+ * capacity, the leading dimension of the k-block-major scale arrays.  Synchronises the device.
+ * The reference exposes no intermediates; its debug script only compares the final output
+ * (moe/scripts/debug_correctness.py:58-91). */
+int syfi_moe_debug_read(syfi_moe_ctx* ctx, const char* name, void* dst_host, int64_t max_bytes, int64_t* bytes,
+                        int32_t* row_cap);
+
+/* Number of kernels the most recent forward enqueued (for launch accounting). */
+int syfi_moe_last_launch_count(syfi_moe_ctx* ctx);
+
+/* Bytes of device workspace currently held. */
+int64_t syfi_moe_workspace_bytes(syfi_moe_ctx* ctx);
+
+/* Message for the last failure on the calling thread ("" if none). */
+const char* syfi_moe_last_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SYFI_MOE_H_ */

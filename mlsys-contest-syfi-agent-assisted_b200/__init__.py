@@ -1,0 +1,12 @@
+"""B200-native fused FP8 block-scale DeepSeek-V3 MoE layer (sm_100a only).
+
+Public surface: :func:`run_moe` (the reference's entry point, same argument order),
+:func:`run_moe_host`, :func:`route`, :class:`MoeContext`, and the seeded workload
+generator in :mod:`workloads`.
+"""
+from .moe import (ABI, MoeContext, MoeError, get_context, library_path, load_library, release_contexts, route,
+                  run_moe, run_moe_host)
+from .workloads import MoeInputs, algorithmic_work, make_inputs
+
+__all__ = ["ABI", "MoeContext", "MoeError", "MoeInputs", "algorithmic_work", "get_context", "library_path",
+           "load_library", "make_inputs", "release_contexts", "route", "run_moe", "run_moe_host"]

@@ -1,0 +1,426 @@
+// C ABI, workspace management, tensor maps and the launch sequence of the MoE layer.
+//
+// Host-side counterpart of the reference's run_impl and Workspace
+// (moe/solution/cuda/moe.cu:2832-3258).  Unlike the reference there is no host
+// synchronisation inside a call (its tile schedule is built on the host after a
+// device->host copy, moe.cu:3127-3186): the tile table is built on the device and the
+// persistent GEMM kernels read their work count from device memory.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <string>
+
+#include "../../include/syfi_moe.h"
+#include "moe_internal.h"
+
+using namespace syfi;
+
+struct syfi_moe_ctx {
+  Workspace ws;
+  int num_sms = 0;
+  int launches = 0;
+  // staging buffers of syfi_moe_forward_host
+  void* stage = nullptr;
+  size_t stage_bytes = 0;
+  std::mutex mu;
+};
+
+namespace {
+
+thread_local std::string g_err;
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_err = buf;
+  return code;
+}
+
+#define CU_TRY(expr)                                                                                 \
+  do {                                                                                               \
+    cudaError_t _e = (expr);                                                                         \
+    if (_e != cudaSuccess)                                                                           \
+      return fail(SYFI_MOE_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), __FILE__, __LINE__); \
+  } while (0)
+
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = false;
+  explicit DeviceGuard(int dev) {
+    if (cudaGetDevice(&prev) == cudaSuccess && cudaSetDevice(dev) == cudaSuccess) ok = true;
+  }
+  ~DeviceGuard() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// 2-D byte tensor [rows, cols] (cols contiguous), box [box_rows, 128 bytes], 128-byte swizzle.
+int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return fail(SYFI_MOE_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols};
+  const cuuint32_t box[2] = {128, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(SYFI_MOE_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return SYFI_MOE_OK;
+}
+
+void free_workspace(Workspace& ws) {
+  void* ptrs[] = {ws.topk_idx, ws.topk_w, ws.local_mask, ws.counts, ws.meta, ws.status, ws.row_token, ws.route_row,
+                  ws.tiles, ws.a_perm, ws.a_scale, ws.c_hi, ws.c_lo, ws.c_scale, ws.o_rows};
+  for (void* p : ptrs)
+    if (p) cudaFree(p);
+  const int dev = ws.device;
+  ws = Workspace();
+  ws.device = dev;
+}
+
+template <typename T>
+cudaError_t dev_alloc(T** p, size_t count, size_t* total) {
+  const size_t bytes = (count * sizeof(T) + 255) / 256 * 256;
+  *total += bytes;
+  return cudaMalloc(reinterpret_cast<void**>(p), bytes);
+}
+
+int alloc_workspace(Workspace& ws, int64_t max_tokens) {
+  if (max_tokens < 1) max_tokens = 1;
+  free_workspace(ws);
+  const int64_t T = max_tokens;
+  // worst case: every one of the 8 routes of every token is local, plus per-expert padding
+  const int64_t row_cap = (8 * T + kRowPad * kMaxLocalExperts + kTokenTile - 1) / kTokenTile * kTokenTile;
+  const int64_t tile_cap = row_cap / kTokenTile + kMaxLocalExperts;
+  if (row_cap * (int64_t)kHidden > (int64_t)1 << 40) return fail(SYFI_MOE_ERR_INVALID, "max_tokens too large");
+  size_t total = 0;
+  CU_TRY(dev_alloc(&ws.topk_idx, T * kTopK, &total));
+  CU_TRY(dev_alloc(&ws.topk_w, T * kTopK, &total));
+  CU_TRY(dev_alloc(&ws.local_mask, T, &total));
+  CU_TRY(dev_alloc(&ws.counts, kMaxLocalExperts, &total));
+  CU_TRY(dev_alloc(&ws.meta, kMetaInts, &total));
+  CU_TRY(dev_alloc(&ws.status, 4, &total));
+  CU_TRY(dev_alloc(&ws.row_token, row_cap, &total));
+  CU_TRY(dev_alloc(&ws.route_row, T * kTopK, &total));
+  CU_TRY(dev_alloc(&ws.tiles, tile_cap, &total));
+  CU_TRY(dev_alloc(&ws.a_perm, row_cap * kHidden, &total));
+  CU_TRY(dev_alloc(&ws.a_scale, row_cap * kHBlocks, &total));
+  CU_TRY(dev_alloc(&ws.c_hi, row_cap * kInter, &total));
+  CU_TRY(dev_alloc(&ws.c_lo, row_cap * kInter, &total));
+  CU_TRY(dev_alloc(&ws.c_scale, row_cap * kIBlocks, &total));
+  CU_TRY(dev_alloc(&ws.o_rows, row_cap * kHidden, &total));
+  CU_TRY(cudaMemset(ws.status, 0, 4 * sizeof(int)));
+  CU_TRY(cudaMemset(ws.meta, 0, kMetaInts * sizeof(int)));
+  ws.max_tokens = (int)T;
+  ws.row_cap = (int)row_cap;
+  ws.tile_cap = (int)tile_cap;
+  ws.bytes = total;
+  return SYFI_MOE_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int validate(syfi_moe_ctx* ctx, const void* const* ptrs, int nptrs, int64_t T, int32_t e_local, int64_t offset,
+             double scaling) {
+  if (!ctx) return fail(SYFI_MOE_ERR_INVALID, "context is null");
+  if (T < 0 || T > (1 << 24)) return fail(SYFI_MOE_ERR_INVALID, "num_tokens %lld out of range", (long long)T);
+  if (e_local < 1 || e_local > kMaxLocalExperts)
+    return fail(SYFI_MOE_ERR_INVALID, "num_local_experts %d must be in [1, %d]", e_local, kMaxLocalExperts);
+  if (offset < 0 || offset + e_local > kExpertsGlobal)
+    return fail(SYFI_MOE_ERR_INVALID, "local experts [%lld, %lld) outside [0, %d)", (long long)offset,
+                (long long)(offset + e_local), kExpertsGlobal);
+  if (!(scaling == scaling) || scaling > 3.0e38 || scaling < -3.0e38)
+    return fail(SYFI_MOE_ERR_INVALID, "routed_scaling_factor is not a finite float");
+  if (T == 0) return SYFI_MOE_OK;
+  for (int i = 0; i < nptrs; ++i) {
+    if (!ptrs[i]) return fail(SYFI_MOE_ERR_INVALID, "tensor argument %d is null", i);
+    if (!aligned16(ptrs[i])) return fail(SYFI_MOE_ERR_INVALID, "tensor argument %d is not 16-byte aligned", i);
+  }
+  return SYFI_MOE_OK;
+}
+
+int ensure_capacity(syfi_moe_ctx* ctx, int64_t T) {
+  if (T <= ctx->ws.max_tokens) return SYFI_MOE_OK;
+  // growing frees buffers that earlier calls may still be using
+  CU_TRY(cudaDeviceSynchronize());
+  return alloc_workspace(ctx->ws, T);
+}
+
+int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const void* hs, const void* hs_scale,
+              const void* w13, const void* w13_scale, const void* w2, const void* w2_scale, int64_t T64,
+              int32_t e_local, int64_t offset, double scaling, void* out, int out_is_f32, cudaStream_t st) {
+  Workspace& ws = ctx->ws;
+  const int T = (int)T64;
+  GemmLaunch g1, g2;
+  int rc;
+  if ((rc = make_map(&g1.tm_w, w13, (uint64_t)e_local * 2 * kInter, kHidden, 128))) return rc;
+  if ((rc = make_map(&g1.tm_b0, ws.a_perm, ws.row_cap, kHidden, kTokenTile))) return rc;
+  g1.tm_b1 = g1.tm_b0;
+  if ((rc = make_map(&g2.tm_w, w2, (uint64_t)e_local * kHidden, kInter, 128))) return rc;
+  if ((rc = make_map(&g2.tm_b0, ws.c_hi, ws.row_cap, kInter, kTokenTile))) return rc;
+  if ((rc = make_map(&g2.tm_b1, ws.c_lo, ws.row_cap, kInter, kTokenTile))) return rc;
+
+  ctx->launches = 0;
+  CU_TRY(launch_router(static_cast<const float*>(logits), bias, T, e_local, (int)offset, (float)scaling, ws, st));
+  ctx->launches += 1;
+  CU_TRY(launch_build_rows(T, e_local, (int)offset, ws, st));
+  ctx->launches += 1;
+  CU_TRY(launch_gather(static_cast<const uint8_t*>(hs), static_cast<const float*>(hs_scale), T, ws, st));
+  ctx->launches += 1;
+  CU_TRY(launch_gemm1(g1, static_cast<const float*>(w13_scale), ws, ctx->num_sms, st));
+  ctx->launches += 1;
+  CU_TRY(launch_gemm2(g2, static_cast<const float*>(w2_scale), ws, ctx->num_sms, st));
+  ctx->launches += 1;
+  CU_TRY(launch_combine(T, ws, out, out_is_f32, st));
+  ctx->launches += 1;
+  return SYFI_MOE_OK;
+}
+
+int forward_common(syfi_moe_ctx* ctx, const void* logits, const void* bias, const void* hs, const void* hs_scale,
+                   const void* w13, const void* w13_scale, const void* w2, const void* w2_scale, int64_t T,
+                   int32_t e_local, int64_t offset, double scaling, void* out, int out_is_f32, void* stream) {
+  const void* ptrs[] = {logits, bias, hs, hs_scale, w13, w13_scale, w2, w2_scale, out};
+  int rc = validate(ctx, ptrs, 9, T, e_local, offset, scaling);
+  if (rc) return rc;
+  if (T == 0) return SYFI_MOE_OK;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard guard(ctx->ws.device);
+  if (!guard.ok) return fail(SYFI_MOE_ERR_CUDA, "cannot select device %d", ctx->ws.device);
+  if ((rc = ensure_capacity(ctx, T))) return rc;
+  return run_layer(ctx, logits, bias, hs, hs_scale, w13, w13_scale, w2, w2_scale, T, e_local, offset, scaling, out,
+                   out_is_f32, static_cast<cudaStream_t>(stream));
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* syfi_moe_last_error(void) { return g_err.c_str(); }
+
+int syfi_moe_create(int device, int64_t max_tokens, syfi_moe_ctx** out_ctx) {
+  if (!out_ctx) return fail(SYFI_MOE_ERR_INVALID, "out_ctx is null");
+  *out_ctx = nullptr;
+  if (max_tokens < 0 || max_tokens > (1 << 24)) return fail(SYFI_MOE_ERR_INVALID, "max_tokens out of range");
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev == 0)
+    return fail(SYFI_MOE_ERR_CUDA, "no CUDA device: this library has no CPU path");
+  if (device < 0 || device >= ndev) return fail(SYFI_MOE_ERR_INVALID, "device %d out of range [0, %d)", device, ndev);
+  DeviceGuard guard(device);
+  if (!guard.ok) return fail(SYFI_MOE_ERR_CUDA, "cannot select device %d", device);
+  cudaDeviceProp prop;
+  CU_TRY(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10)
+    return fail(SYFI_MOE_ERR_CUDA, "device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major,
+                prop.minor);
+  CU_TRY(gemm_set_attributes());
+  syfi_moe_ctx* ctx = new (std::nothrow) syfi_moe_ctx();
+  if (!ctx) return fail(SYFI_MOE_ERR_INVALID, "out of host memory");
+  ctx->ws.device = device;
+  ctx->num_sms = prop.multiProcessorCount;
+  int rc = alloc_workspace(ctx->ws, max_tokens);
+  if (rc) {
+    free_workspace(ctx->ws);
+    delete ctx;
+    return rc;
+  }
+  *out_ctx = ctx;
+  return SYFI_MOE_OK;
+}
+
+int syfi_moe_destroy(syfi_moe_ctx* ctx) {
+  if (!ctx) return SYFI_MOE_OK;
+  {
+    DeviceGuard guard(ctx->ws.device);
+    cudaDeviceSynchronize();
+    free_workspace(ctx->ws);
+    if (ctx->stage) cudaFree(ctx->stage);
+  }
+  delete ctx;
+  return SYFI_MOE_OK;
+}
+
+int syfi_moe_forward(syfi_moe_ctx* ctx, const void* routing_logits, const void* routing_bias,
+                     const void* hidden_states, const void* hidden_states_scale, const void* gemm1_weights,
+                     const void* gemm1_weights_scale, const void* gemm2_weights, const void* gemm2_weights_scale,
+                     int64_t num_tokens, int32_t num_local_experts, int64_t local_expert_offset,
+                     double routed_scaling_factor, void* output, void* stream) {
+  return forward_common(ctx, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                        gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, num_tokens, num_local_experts,
+                        local_expert_offset, routed_scaling_factor, output, 0, stream);
+}
+
+int syfi_moe_forward_partial_f32(syfi_moe_ctx* ctx, const void* routing_logits, const void* routing_bias,
+                                 const void* hidden_states, const void* hidden_states_scale,
+                                 const void* gemm1_weights, const void* gemm1_weights_scale,
+                                 const void* gemm2_weights, const void* gemm2_weights_scale, int64_t num_tokens,
+                                 int32_t num_local_experts, int64_t local_expert_offset,
+                                 double routed_scaling_factor, void* output_f32, void* stream) {
+  return forward_common(ctx, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                        gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, num_tokens, num_local_experts,
+                        local_expert_offset, routed_scaling_factor, output_f32, 1, stream);
+}
+
+int syfi_moe_forward_host(syfi_moe_ctx* ctx, const void* routing_logits_host, const void* routing_bias_host,
+                          const void* hidden_states_host, const void* hidden_states_scale_host,
+                          const void* gemm1_weights, const void* gemm1_weights_scale, const void* gemm2_weights,
+                          const void* gemm2_weights_scale, int64_t num_tokens, int32_t num_local_experts,
+                          int64_t local_expert_offset, double routed_scaling_factor, void* output_host,
+                          void* stream) {
+  const int64_t T = num_tokens;
+  {
+    const void* hp[] = {routing_logits_host, routing_bias_host, hidden_states_host, hidden_states_scale_host,
+                        output_host};
+    if (!ctx) return fail(SYFI_MOE_ERR_INVALID, "context is null");
+    if (T < 0 || T > (1 << 24)) return fail(SYFI_MOE_ERR_INVALID, "num_tokens %lld out of range", (long long)T);
+    if (T == 0) return SYFI_MOE_OK;
+    for (int i = 0; i < 5; ++i)
+      if (!hp[i]) return fail(SYFI_MOE_ERR_INVALID, "host tensor argument %d is null", i);
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t b_logits = (size_t)T * kExpertsGlobal * 4, b_bias = kExpertsGlobal * 2;
+  const size_t b_hs = (size_t)T * kHidden, b_hss = (size_t)T * kHBlocks * 4, b_out = (size_t)T * kHidden * 2;
+  auto up = [](size_t v) { return (v + 255) / 256 * 256; };
+  const size_t o_logits = 0, o_bias = o_logits + up(b_logits), o_hs = o_bias + up(b_bias), o_hss = o_hs + up(b_hs),
+               o_out = o_hss + up(b_hss), need = o_out + up(b_out);
+  {
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    DeviceGuard guard(ctx->ws.device);
+    if (!guard.ok) return fail(SYFI_MOE_ERR_CUDA, "cannot select device %d", ctx->ws.device);
+    if (need > ctx->stage_bytes) {
+      CU_TRY(cudaDeviceSynchronize());
+      if (ctx->stage) cudaFree(ctx->stage);
+      ctx->stage = nullptr;
+      ctx->stage_bytes = 0;
+      CU_TRY(cudaMalloc(&ctx->stage, need));
+      ctx->stage_bytes = need;
+    }
+  }
+  DeviceGuard guard(ctx->ws.device);
+  char* base = static_cast<char*>(ctx->stage);
+  CU_TRY(cudaMemcpyAsync(base + o_logits, routing_logits_host, b_logits, cudaMemcpyHostToDevice, st));
+  CU_TRY(cudaMemcpyAsync(base + o_bias, routing_bias_host, b_bias, cudaMemcpyHostToDevice, st));
+  CU_TRY(cudaMemcpyAsync(base + o_hs, hidden_states_host, b_hs, cudaMemcpyHostToDevice, st));
+  CU_TRY(cudaMemcpyAsync(base + o_hss, hidden_states_scale_host, b_hss, cudaMemcpyHostToDevice, st));
+  int rc = forward_common(ctx, base + o_logits, base + o_bias, base + o_hs, base + o_hss, gemm1_weights,
+                          gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, T, num_local_experts,
+                          local_expert_offset, routed_scaling_factor, base + o_out, 0, stream);
+  if (rc) return rc;
+  CU_TRY(cudaMemcpyAsync(output_host, base + o_out, b_out, cudaMemcpyDeviceToHost, st));
+  CU_TRY(cudaStreamSynchronize(st));
+  return SYFI_MOE_OK;
+}
+
+int syfi_moe_route(syfi_moe_ctx* ctx, const void* routing_logits, const void* routing_bias, int64_t num_tokens,
+                   int32_t num_local_experts, int64_t local_expert_offset, double routed_scaling_factor,
+                   int32_t* topk_idx, float* topk_weights, void* stream) {
+  const void* ptrs[] = {routing_logits, routing_bias, topk_idx, topk_weights};
+  int rc = validate(ctx, ptrs, 4, num_tokens, num_local_experts, local_expert_offset, routed_scaling_factor);
+  if (rc) return rc;
+  if (num_tokens == 0) return SYFI_MOE_OK;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard guard(ctx->ws.device);
+  if (!guard.ok) return fail(SYFI_MOE_ERR_CUDA, "cannot select device %d", ctx->ws.device);
+  if ((rc = ensure_capacity(ctx, num_tokens))) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int T = (int)num_tokens;
+  CU_TRY(launch_router(static_cast<const float*>(routing_logits), routing_bias, T, num_local_experts,
+                       (int)local_expert_offset, (float)routed_scaling_factor, ctx->ws, st));
+  CU_TRY(cudaMemcpyAsync(topk_idx, ctx->ws.topk_idx, sizeof(int) * T * kTopK, cudaMemcpyDeviceToDevice, st));
+  CU_TRY(cudaMemcpyAsync(topk_weights, ctx->ws.topk_w, sizeof(float) * T * kTopK, cudaMemcpyDeviceToDevice, st));
+  ctx->launches = 1;
+  return SYFI_MOE_OK;
+}
+
+int syfi_moe_last_routing(syfi_moe_ctx* ctx, int64_t num_tokens, int32_t* topk_idx_host, float* topk_weights_host,
+                          void* stream) {
+  if (!ctx) return fail(SYFI_MOE_ERR_INVALID, "context is null");
+  if (num_tokens < 0 || num_tokens > ctx->ws.max_tokens)
+    return fail(SYFI_MOE_ERR_INVALID, "num_tokens %lld exceeds the workspace (%d)", (long long)num_tokens,
+                ctx->ws.max_tokens);
+  DeviceGuard guard(ctx->ws.device);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (topk_idx_host)
+    CU_TRY(cudaMemcpyAsync(topk_idx_host, ctx->ws.topk_idx, sizeof(int) * num_tokens * kTopK, cudaMemcpyDeviceToHost, st));
+  if (topk_weights_host)
+    CU_TRY(cudaMemcpyAsync(topk_weights_host, ctx->ws.topk_w, sizeof(float) * num_tokens * kTopK, cudaMemcpyDeviceToHost, st));
+  CU_TRY(cudaStreamSynchronize(st));
+  return SYFI_MOE_OK;
+}
+
+int syfi_moe_check(syfi_moe_ctx* ctx, int32_t* stats4, void* stream) {
+  if (!ctx) return fail(SYFI_MOE_ERR_INVALID, "context is null");
+  DeviceGuard guard(ctx->ws.device);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int status[4] = {0, 0, 0, 0};
+  int meta[kMetaInts] = {0};
+  CU_TRY(cudaMemcpyAsync(status, ctx->ws.status, sizeof(status), cudaMemcpyDeviceToHost, st));
+  CU_TRY(cudaMemcpyAsync(meta, ctx->ws.meta, sizeof(meta), cudaMemcpyDeviceToHost, st));
+  CU_TRY(cudaStreamSynchronize(st));
+  if (stats4)
+    for (int i = 0; i < 4; ++i) stats4[i] = meta[i];
+  if (status[0] != kStatusOk) {
+    cudaMemsetAsync(ctx->ws.status, 0, sizeof(status), st);
+    return fail(SYFI_MOE_ERR_DEVICE, "a kernel reported status %d (101/102/103: bounded wait expired in the TMA / MMA / "
+                "epilogue role of a grouped GEMM; 104: row or tile table overflow)", status[0]);
+  }
+  return SYFI_MOE_OK;
+}
+
+int syfi_moe_debug_read(syfi_moe_ctx* ctx, const char* name, void* dst_host, int64_t max_bytes, int64_t* bytes,
+                        int32_t* row_cap) {
+  if (!ctx || !name || !bytes) return fail(SYFI_MOE_ERR_INVALID, "null argument");
+  DeviceGuard guard(ctx->ws.device);
+  const Workspace& ws = ctx->ws;
+  const int64_t T = ws.max_tokens, R = ws.row_cap;
+  struct Entry { const char* name; void* ptr; int64_t bytes; };
+  const Entry table[] = {
+      {"row_token", ws.row_token, R * 4},        {"route_row", ws.route_row, T * kTopK * 4},
+      {"tiles", ws.tiles, (int64_t)ws.tile_cap * (int64_t)sizeof(TokenTile)},
+      {"meta", ws.meta, kMetaInts * 4},          {"counts", ws.counts, kMaxLocalExperts * 4},
+      {"a_perm", ws.a_perm, R * kHidden},        {"a_scale", ws.a_scale, R * kHBlocks * 4},
+      {"c_hi", ws.c_hi, R * kInter},             {"c_lo", ws.c_lo, R * kInter},
+      {"c_scale", ws.c_scale, R * kIBlocks * 4}, {"o_rows", ws.o_rows, R * kHidden * 4},
+      {"topk_idx", ws.topk_idx, T * kTopK * 4},  {"topk_w", ws.topk_w, T * kTopK * 4},
+  };
+  for (const Entry& e : table) {
+    if (strcmp(e.name, name) == 0) {
+      *bytes = e.bytes;
+      if (row_cap) *row_cap = ws.row_cap;
+      if (dst_host && max_bytes > 0) {
+        CU_TRY(cudaDeviceSynchronize());
+        CU_TRY(cudaMemcpy(dst_host, e.ptr, (size_t)(e.bytes < max_bytes ? e.bytes : max_bytes), cudaMemcpyDeviceToHost));
+      }
+      return SYFI_MOE_OK;
+    }
+  }
+  return fail(SYFI_MOE_ERR_INVALID, "unknown workspace buffer '%s'", name);
+}
+
+int syfi_moe_last_launch_count(syfi_moe_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+int64_t syfi_moe_workspace_bytes(syfi_moe_ctx* ctx) { return ctx ? (int64_t)ctx->ws.bytes : 0; }
+
+}  // extern "C"

@@ -1,0 +1,92 @@
+// Internal declarations shared by the translation units of the MoE library:
+// problem constants, the device workspace layout and the per-stage launchers.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace syfi {
+
+constexpr int kHidden = 7168;       // H
+constexpr int kInter = 2048;        // I
+constexpr int kBlock = 128;         // quantisation block
+constexpr int kExpertsGlobal = 256;
+constexpr int kGroups = 8;
+constexpr int kGroupSize = 32;
+constexpr int kTopKGroups = 4;
+constexpr int kTopK = 8;
+constexpr int kMaxLocalExperts = 32;
+constexpr int kHBlocks = kHidden / kBlock;   // 56
+constexpr int kIBlocks = kInter / kBlock;    // 16
+constexpr int kRowPad = 16;                  // each expert's row range is padded to this
+constexpr int kTokenTile = 64;               // token rows per GEMM work item (MMA N)
+constexpr float kLoRatio = 28.0f;            // scale(hi) / scale(lo) of the two-term e4m3 intermediate
+
+// status codes written by kernels into Workspace::status[0]
+enum : int {
+  kStatusOk = 0,
+  kStatusWaitTimeoutProducer = 101,
+  kStatusWaitTimeoutMma = 102,
+  kStatusWaitTimeoutEpilogue = 103,
+  kStatusBadIndex = 104,
+};
+
+// Device-side control block (one int array); the GEMM kernels read the tile count from it.
+//   meta[0] = number of token tiles, meta[1] = padded row total, meta[2] = routed (token, local expert) rows,
+//   meta[3] = active local experts
+constexpr int kMetaInts = 8;
+
+// One token tile of one expert: rows [row_start, row_start + n) of the permuted row space.
+struct TokenTile {
+  int expert;
+  int row_start;
+  int n;       // multiple of 16, <= kTokenTile
+  int pad;
+};
+
+struct Workspace {
+  int device = -1;
+  int max_tokens = 0;
+  int row_cap = 0;        // capacity of the permuted row space
+  int tile_cap = 0;
+  // routing
+  int* topk_idx = nullptr;        // [T, 8] global expert ids
+  float* topk_w = nullptr;        // [T, 8]
+  uint32_t* local_mask = nullptr; // [T] bit e set when local expert e was selected
+  int* counts = nullptr;          // [32] rows per local expert
+  int* meta = nullptr;            // [kMetaInts]
+  int* status = nullptr;          // [4]
+  // permutation
+  int* row_token = nullptr;       // [row_cap] token of each row, -1 for padding
+  int* route_row = nullptr;       // [T, 8] row of each (token, k) route, -1 when the expert is not local
+  TokenTile* tiles = nullptr;     // [tile_cap]
+  // operands
+  uint8_t* a_perm = nullptr;      // [row_cap, 7168] e4m3 gathered activations
+  float* a_scale = nullptr;       // [56, row_cap]
+  uint8_t* c_hi = nullptr;        // [row_cap, 2048] e4m3 SwiGLU output, leading term
+  uint8_t* c_lo = nullptr;        // [row_cap, 2048] e4m3 residual term (scale = c_scale / 28)
+  float* c_scale = nullptr;       // [16, row_cap]
+  float* o_rows = nullptr;        // [row_cap, 7168] f32 per-route expert outputs
+  size_t bytes = 0;
+};
+
+struct GemmLaunch {
+  CUtensorMap tm_w;    // weights, 2-D [E * rows_per_expert, K], box 128 x 128
+  CUtensorMap tm_b0;   // token-side operand, box kTokenTile x 128 (GEMM1: a_perm; GEMM2: c_hi)
+  CUtensorMap tm_b1;   // GEMM2: c_lo (unused by GEMM1)
+};
+
+// launchers (each returns the cudaGetLastError() of its launches)
+cudaError_t launch_router(const float* logits, const void* bias_bf16, int T, int e_local, int expert_offset,
+                          float scaling, const Workspace& ws, cudaStream_t st);
+cudaError_t launch_build_rows(int T, int e_local, int expert_offset, const Workspace& ws, cudaStream_t st);
+cudaError_t launch_gather(const uint8_t* hidden, const float* hidden_scale, int T, const Workspace& ws,
+                          cudaStream_t st);
+cudaError_t launch_gemm1(const GemmLaunch& g, const float* w13_scale, const Workspace& ws, int num_sms,
+                         cudaStream_t st);
+cudaError_t launch_gemm2(const GemmLaunch& g, const float* w2_scale, const Workspace& ws, int num_sms,
+                         cudaStream_t st);
+cudaError_t launch_combine(int T, const Workspace& ws, void* out, int out_is_f32, cudaStream_t st);
+cudaError_t gemm_set_attributes();
+
+}  // namespace syfi

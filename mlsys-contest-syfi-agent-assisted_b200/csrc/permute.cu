@@ -1,0 +1,129 @@
+// Per-expert row lists, the token-tile table, and the gathered activation operand.
+//
+// Replaces the reference's scan_offsets_kernel / perm_fill_kernel /
+// scan_fill_small_kernel (moe/solution/cuda/moe.cu:214-303), its host-side tile
+// schedule (moe.cu:3127-3186, a device->host->device round trip) and
+// gather_hs_fp8_kernel (moe.cu:2356-2399).
+//
+// Row order is deterministic: inside an expert, rows are sorted by token.  The router
+// leaves one 32-bit word per token with a bit per selected local expert, so the row of
+// token t in expert e is the number of earlier tokens with bit e set; CTA e computes
+// that with ballots.  Every expert's row range is padded to a multiple of 16 rows
+// (the tcgen05 N granularity), padding rows carry token -1 and zero data.
+#include "moe_internal.h"
+
+namespace syfi {
+
+namespace {
+
+constexpr int kBuildThreads = 256;
+
+__global__ void __launch_bounds__(kBuildThreads)
+build_rows_kernel(int T, int e_local, int expert_offset, const uint32_t* __restrict__ local_mask,
+                  const int* __restrict__ counts, const int* __restrict__ topk_idx, int* __restrict__ row_token,
+                  int* __restrict__ route_row, TokenTile* __restrict__ tiles, int* __restrict__ meta, int row_cap,
+                  int tile_cap, int* __restrict__ status) {
+  __shared__ int s_warp[kBuildThreads / 32];
+  const int e = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  int row_off = 0, tile_off = 0, rows_total = 0, tiles_total = 0, routed = 0, active = 0, cnt = 0;
+  for (int i = 0; i < e_local; ++i) {
+    const int c = counts[i];
+    const int cp = (c + kRowPad - 1) / kRowPad * kRowPad;
+    const int nt = (cp + kTokenTile - 1) / kTokenTile;
+    if (i < e) { row_off += cp; tile_off += nt; }
+    if (i == e) cnt = c;
+    rows_total += cp; tiles_total += nt; routed += c; active += (c > 0);
+  }
+  const int cnt_pad = (cnt + kRowPad - 1) / kRowPad * kRowPad;
+  if (rows_total > row_cap || tiles_total > tile_cap) {  // sizing bug: refuse to write out of bounds
+    if (tid == 0) { atomicExch(status, kStatusBadIndex); if (e == 0) { meta[0] = 0; meta[1] = 0; meta[2] = 0; meta[3] = 0; } }
+    return;
+  }
+
+  int base = 0;
+  for (int t0 = 0; t0 < T; t0 += kBuildThreads) {
+    const int t = t0 + tid;
+    const bool has = (t < T) && ((local_mask[t] >> e) & 1u);
+    const unsigned b = __ballot_sync(0xffffffffu, has);
+    if (lane == 0) s_warp[warp] = __popc(b);
+    __syncthreads();
+    int before = 0, block_total = 0;
+#pragma unroll
+    for (int w = 0; w < kBuildThreads / 32; ++w) {
+      const int c = s_warp[w];
+      before += (w < warp) ? c : 0;
+      block_total += c;
+    }
+    if (has) {
+      const int row = row_off + base + before + __popc(b & ((1u << lane) - 1u));
+      row_token[row] = t;
+      const int ge = e + expert_offset;
+#pragma unroll
+      for (int k = 0; k < kTopK; ++k)
+        if (topk_idx[t * kTopK + k] == ge) route_row[t * kTopK + k] = row;
+    }
+    base += block_total;
+    __syncthreads();
+  }
+  for (int r = cnt + tid; r < cnt_pad; r += kBuildThreads) row_token[row_off + r] = -1;
+  const int nt_e = (cnt_pad + kTokenTile - 1) / kTokenTile;
+  for (int i = tid; i < nt_e; i += kBuildThreads) {
+    TokenTile tt;
+    tt.expert = e;
+    tt.row_start = row_off + i * kTokenTile;
+    tt.n = min(kTokenTile, cnt_pad - i * kTokenTile);
+    tt.pad = 0;
+    tiles[tile_off + i] = tt;
+  }
+  if (e == 0 && tid == 0) {
+    meta[0] = tiles_total; meta[1] = rows_total; meta[2] = routed; meta[3] = active;
+  }
+}
+
+constexpr int kGatherThreads = 224;  // 7168 B per row = 448 x 16 B = 2 per thread
+
+__global__ void __launch_bounds__(kGatherThreads)
+gather_rows_kernel(const uint8_t* __restrict__ hidden, const float* __restrict__ hidden_scale, int T,
+                   const int* __restrict__ row_token, const int* __restrict__ meta, uint8_t* __restrict__ a_perm,
+                   float* __restrict__ a_scale, int row_cap) {
+  const int rows_total = meta[1];
+  const int tid = threadIdx.x;
+  for (int r = blockIdx.x; r < rows_total; r += gridDim.x) {
+    const int t = row_token[r];
+    uint4* dst = reinterpret_cast<uint4*>(a_perm + static_cast<size_t>(r) * kHidden);
+    if (t >= 0 && t < T) {
+      const uint4* src = reinterpret_cast<const uint4*>(hidden + static_cast<size_t>(t) * kHidden);
+      const uint4 v0 = __ldg(src + tid), v1 = __ldg(src + tid + kGatherThreads);
+      dst[tid] = v0;
+      dst[tid + kGatherThreads] = v1;
+      if (tid < kHBlocks) a_scale[static_cast<size_t>(tid) * row_cap + r] = __ldg(hidden_scale + static_cast<size_t>(tid) * T + t);
+    } else {
+      const uint4 z = make_uint4(0, 0, 0, 0);
+      dst[tid] = z;
+      dst[tid + kGatherThreads] = z;
+      if (tid < kHBlocks) a_scale[static_cast<size_t>(tid) * row_cap + r] = 0.0f;
+    }
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_build_rows(int T, int e_local, int expert_offset, const Workspace& ws, cudaStream_t st) {
+  build_rows_kernel<<<e_local, kBuildThreads, 0, st>>>(T, e_local, expert_offset, ws.local_mask, ws.counts,
+                                                       ws.topk_idx, ws.row_token, ws.route_row, ws.tiles, ws.meta,
+                                                       ws.row_cap, ws.tile_cap, ws.status);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_gather(const uint8_t* hidden, const float* hidden_scale, int T, const Workspace& ws,
+                          cudaStream_t st) {
+  const int max_rows = 8 * T + kRowPad * kMaxLocalExperts;
+  const int grid = max_rows < 148 * 8 ? max_rows : 148 * 8;
+  gather_rows_kernel<<<grid, kGatherThreads, 0, st>>>(hidden, hidden_scale, T, ws.row_token, ws.meta, ws.a_perm,
+                                                      ws.a_scale, ws.row_cap);
+  return cudaGetLastError();
+}
+
+}  // namespace syfi

@@ -1,0 +1,145 @@
+// DeepSeek-V3 no-aux router, one warp per token.
+//
+// Replaces the reference's route_kernel (moe/solution/cuda/moe.cu:62-188: one CTA of
+// 256 threads per token, eight block-wide argmax rounds).  Here a warp owns a token:
+// lane l holds experts [8l, 8l+8), so a routing group (32 experts) is four adjacent
+// lanes and every reduction is a handful of shuffles.
+//
+// Numerics follow the definition's reference (flashinfer/trace/templates/moe.py:139-170):
+// s = 1 / (1 + exp(-x)) with accurate expf and IEEE division (this file must not be
+// compiled with fast-math), biased = s + bias, group score = sum of the two largest
+// biased scores of the group, ties resolved towards the lower index, weights from the
+// un-biased s, normalised with +1e-20 and multiplied by the scaling factor.
+#include <cuda_bf16.h>
+#include <math_constants.h>
+
+#include "moe_internal.h"
+
+namespace syfi {
+
+namespace {
+
+constexpr int kWarpsPerBlock = 4;
+
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+route_kernel(const float* __restrict__ logits, const __nv_bfloat16* __restrict__ bias, int T, int e_local,
+             int expert_offset, float scaling, int* __restrict__ topk_idx, float* __restrict__ topk_w,
+             uint32_t* __restrict__ local_mask, int* __restrict__ route_row, int* __restrict__ counts) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  if (t >= T) return;
+  const unsigned full = 0xffffffffu;
+
+  float x[8];
+  {
+    const float4* lp = reinterpret_cast<const float4*>(logits + static_cast<size_t>(t) * kExpertsGlobal + lane * 8);
+    const float4 a = __ldg(lp), b = __ldg(lp + 1);
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w;
+    x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+  }
+  float bf[8];
+  {
+    const uint4 bv = __ldg(reinterpret_cast<const uint4*>(bias + lane * 8));
+    const uint32_t w[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      bf[2 * i] = __uint_as_float(w[i] << 16);
+      bf[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+  float s[8], v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    s[i] = 1.0f / (1.0f + expf(-x[i]));
+    v[i] = s[i] + bf[i];
+  }
+
+  // two largest biased scores of the group (4 lanes x 8 values)
+  float m1 = -CUDART_INF_F, m2 = -CUDART_INF_F;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    if (v[i] > m1) { m2 = m1; m1 = v[i]; }
+    else if (v[i] > m2) { m2 = v[i]; }
+  }
+#pragma unroll
+  for (int d = 1; d <= 2; d <<= 1) {
+    const float o1 = __shfl_xor_sync(full, m1, d);
+    const float o2 = __shfl_xor_sync(full, m2, d);
+    const float n1 = fmaxf(m1, o1);
+    const float n2 = fmaxf(fminf(m1, o1), fmaxf(m2, o2));
+    m1 = n1; m2 = n2;
+  }
+  const float gscore = m1 + m2;
+  const int g = lane >> 2;
+  int rank = 0;
+#pragma unroll
+  for (int gg = 0; gg < kGroups; ++gg) {
+    const float o = __shfl_sync(full, gscore, gg * 4);
+    rank += (o > gscore || (o == gscore && gg < g)) ? 1 : 0;
+  }
+  const bool keep = rank < kTopKGroups;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = keep ? v[i] : -CUDART_MAX_NORMAL_F;
+
+  // eight rounds of warp-wide argmax over the kept experts
+  int my_idx = 0;
+  float my_s = 0.0f;
+#pragma unroll 1
+  for (int r = 0; r < kTopK; ++r) {
+    float bv = v[0];
+    int bi = 0;
+#pragma unroll
+    for (int i = 1; i < 8; ++i)
+      if (v[i] > bv) { bv = v[i]; bi = i; }
+    bi += lane * 8;
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) {
+      const float ov = __shfl_xor_sync(full, bv, d);
+      const int oi = __shfl_xor_sync(full, bi, d);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    const int owner = bi >> 3, slot = bi & 7;
+    float sel = s[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) sel = (slot == i) ? s[i] : sel;
+    sel = __shfl_sync(full, sel, owner);
+    if (lane == owner) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (slot == i) v[i] = -CUDART_INF_F;
+    }
+    if (lane == r) { my_idx = bi; my_s = sel; }
+  }
+
+  float sum = (lane < kTopK) ? my_s : 0.0f;
+#pragma unroll
+  for (int d = 4; d >= 1; d >>= 1) sum += __shfl_xor_sync(full, sum, d);
+  sum = __shfl_sync(full, sum, 0);
+  const float w = (my_s / (sum + 1e-20f)) * scaling;
+
+  const int le = my_idx - expert_offset;
+  const bool local = (lane < kTopK) && le >= 0 && le < e_local;
+  const uint32_t mask = __reduce_or_sync(full, local ? (1u << le) : 0u);
+  if (lane < kTopK) {
+    topk_idx[t * kTopK + lane] = my_idx;
+    topk_w[t * kTopK + lane] = w;
+    route_row[t * kTopK + lane] = -1;
+    if (local) atomicAdd(&counts[le], 1);
+  }
+  if (lane == 0) local_mask[t] = mask;
+}
+
+}  // namespace
+
+cudaError_t launch_router(const float* logits, const void* bias_bf16, int T, int e_local, int expert_offset,
+                          float scaling, const Workspace& ws, cudaStream_t st) {
+  cudaError_t e = cudaMemsetAsync(ws.counts, 0, sizeof(int) * kMaxLocalExperts, st);
+  if (e != cudaSuccess) return e;
+  const int blocks = (T + kWarpsPerBlock - 1) / kWarpsPerBlock;
+  route_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>(logits, static_cast<const __nv_bfloat16*>(bias_bf16), T,
+                                                      e_local, expert_offset, scaling, ws.topk_idx, ws.topk_w,
+                                                      ws.local_mask, ws.route_row, ws.counts);
+  return cudaGetLastError();
+}
+
+}  // namespace syfi

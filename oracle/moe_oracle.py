@@ -1,0 +1,161 @@
+"""CPU oracle for the fused FP8 block-scale DeepSeek-V3 MoE layer.
+
+TEST INFRASTRUCTURE ONLY.  This module is the checker the parity tests, the
+smoke test and the benchmark's CPU-baseline leg compare the CUDA path against.
+The product never imports it and never falls back to it.
+
+It restates, in plain torch tensor arithmetic on the host, the PyTorch reference
+of the definition ``moe_fp8_block_scale_ds_routing_topk8_ng8_kg4_e32_h7168_i2048``.
+That reference is not part of the reference repository (which only holds the
+CUDA submission, moe/solution/cuda/moe.cu, graded against it by an external
+harness, moe/scripts/debug_correctness.py:39-55); it ships in the third-party
+package flashinfer-python 0.6.11.post2 as
+``flashinfer/trace/templates/moe.py`` (routing at :139-170, expert math at
+:56-100).  The restatement keeps that file's operation order so routing is
+bit-identical on the same host, and only differs in dequantising just the
+experts that received tokens (the published reference dequantises all of them).
+
+Pinning: ``tests/golden/make_golden.py`` runs the published reference function
+in a container that has flashinfer installed and stores its routing and output
+for fixed seeds; ``tests/test_oracle_golden.py`` checks this module against
+those files.  Parity of the CUDA path is then checked against this module.
+"""
+from __future__ import annotations
+
+import torch
+
+BLOCK = 128
+
+
+@torch.no_grad()
+def route(routing_logits, routing_bias, routed_scaling_factor, top_k=8, n_group=8, topk_group=4):
+    """DeepSeek-V3 no-aux routing (flashinfer/trace/templates/moe.py:139-170;
+    CUDA counterpart moe/solution/cuda/moe.cu:62-188).
+
+    s = sigmoid(logits); biased = s + bias; each group of E/n_group experts is
+    scored by the sum of its two largest biased scores; the topk_group best groups
+    stay; the top_k largest biased scores among the kept groups are the selected
+    experts; weights are the UN-biased s of the selected experts, normalised to sum
+    to one (+1e-20) and multiplied by routed_scaling_factor.
+
+    Returns (topk_idx int64 [T, top_k], topk_w f32 [T, top_k]).
+    """
+    logits = routing_logits.to(torch.float32)
+    bias = routing_bias.to(torch.float32).reshape(-1)
+    T, E = logits.shape
+    s = 1.0 / (1.0 + torch.exp(-logits))
+    biased = s + bias
+    gsz = E // n_group
+    grouped = biased.view(T, n_group, gsz)
+    top2, _ = torch.topk(grouped, k=2, dim=2, largest=True, sorted=False)
+    group_score = top2.sum(dim=2)
+    _, gidx = torch.topk(group_score, k=topk_group, dim=1, largest=True, sorted=False)
+    gmask = torch.zeros_like(group_score)
+    gmask.scatter_(1, gidx, 1.0)
+    emask = gmask.unsqueeze(2).expand(T, n_group, gsz).reshape(T, E)
+    pruned = biased.masked_fill(emask == 0, torch.finfo(torch.float32).min)
+    _, topk_idx = torch.topk(pruned, k=top_k, dim=1, largest=True, sorted=False)
+    sel = torch.zeros_like(s)
+    sel.scatter_(1, topk_idx, 1.0)
+    raw = s * sel
+    denom = raw.sum(dim=1, keepdim=True) + 1e-20
+    weights = (raw / denom) * routed_scaling_factor
+    return topk_idx, weights.gather(1, topk_idx)
+
+
+def dequant_act(hidden_states, hidden_states_scale):
+    """fp8 [T, K] with scales [K/128, T] -> f32 [T, K] (templates/moe.py:56-62)."""
+    T, K = hidden_states.shape
+    s = hidden_states_scale.to(torch.float32).t().contiguous()  # [T, K/128]
+    return (hidden_states.to(torch.float32).view(T, K // BLOCK, BLOCK) * s.unsqueeze(-1)).view(T, K)
+
+
+def dequant_weight(w, w_scale):
+    """fp8 [N, K] with scales [N/128, K/128] -> f32 [N, K] (templates/moe.py:64-74)."""
+    N, K = w.shape
+    wf = w.to(torch.float32).view(N // BLOCK, BLOCK, K // BLOCK, BLOCK)
+    return (wf * w_scale.to(torch.float32)[:, None, :, None]).view(N, K)
+
+
+@torch.no_grad()
+def run_experts(hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
+                gemm2_weights, gemm2_weights_scale, topk_w, topk_idx, local_expert_offset,
+                e_global=256):
+    """Per-expert FP32 math (flashinfer/trace/templates/moe.py:76-100; CUDA
+    counterparts: gather moe.cu:2356-2399, GEMM1 :2194-2350 and :1461-1627, SwiGLU
+    :1631-1714, GEMM2 + weighted scatter :1718-1887, final cast :2758-2779).
+
+    For each local expert: gather the tokens that chose it, G1 = A W13^T,
+    C = silu(G1[:, I:]) * G1[:, :I], O = C W2^T, and add O times the token's routing
+    weight into an f32 [T, H] accumulator.  No intermediate is rounded.
+    Returns the f32 accumulator (cast it to bf16 for the layer output).
+    """
+    T, H = hidden_states.shape
+    E_local, two_i, _ = gemm1_weights.shape
+    I = two_i // 2
+    A = dequant_act(hidden_states, hidden_states_scale)
+    out = torch.zeros((T, H), dtype=torch.float32, device=hidden_states.device)
+    for le in range(E_local):
+        ge = int(local_expert_offset) + le
+        if ge < 0 or ge >= e_global:
+            continue
+        hit = (topk_idx == ge)
+        rows = hit.any(dim=1)
+        if not bool(rows.any()):
+            continue
+        tok = torch.nonzero(rows, as_tuple=False).squeeze(1)
+        W13 = dequant_weight(gemm1_weights[le], gemm1_weights_scale[le])
+        W2 = dequant_weight(gemm2_weights[le], gemm2_weights_scale[le])
+        G1 = A.index_select(0, tok).matmul(W13.t())
+        X1, X2 = G1[:, :I], G1[:, I:]
+        C = (X2 / (1.0 + torch.exp(-X2))) * X1
+        O = C.matmul(W2.t())
+        w = (topk_w.index_select(0, tok) * hit.index_select(0, tok).float()).sum(dim=1)
+        out.index_add_(0, tok, O * w.unsqueeze(1))
+    return out
+
+
+@torch.no_grad()
+def moe_forward(routing_logits, routing_bias, hidden_states, hidden_states_scale,
+                gemm1_weights, gemm1_weights_scale, gemm2_weights, gemm2_weights_scale,
+                local_expert_offset, routed_scaling_factor, return_f32=False):
+    """Whole layer; same argument order as the reference entry point
+    (moe/solution/cuda/moe.cu:2987-2998) minus the destination tensor.
+
+    Returns (output bf16 [T, H], topk_idx int64 [T, 8], topk_w f32 [T, 8]); with
+    ``return_f32`` the un-rounded f32 accumulator is returned instead of bf16 (used
+    to sum expert-parallel ranks before the single final rounding).
+    """
+    topk_idx, topk_w = route(routing_logits, routing_bias, routed_scaling_factor)
+    acc = run_experts(hidden_states, hidden_states_scale, gemm1_weights, gemm1_weights_scale,
+                      gemm2_weights, gemm2_weights_scale, topk_w, topk_idx,
+                      local_expert_offset, e_global=routing_logits.shape[1])
+    return (acc if return_f32 else acc.to(torch.bfloat16)), topk_idx, topk_w
+
+
+def check_output(out, ref):
+    """The stated tolerance: max|out-ref| <= 1e-2 * max|ref| and at least 99.9 % of the
+    elements within atol 1e-2 + rtol 1e-2 * |ref|.  Returns (ok, stats)."""
+    o = out.detach().float().cpu()
+    r = ref.detach().float().cpu()
+    d = (o - r).abs()
+    max_abs = float(d.max()) if d.numel() else 0.0
+    limit = 1e-2 * float(r.abs().max()) if r.numel() else 0.0
+    frac = float((d <= 1e-2 + 1e-2 * r.abs()).float().mean()) if d.numel() else 1.0
+    finite = bool(torch.isfinite(o).all())
+    ok = finite and max_abs <= limit + 1e-12 and frac >= 0.999
+    return ok, {"max_abs": max_abs, "limit": limit, "frac_within": frac, "finite": finite}
+
+
+def check_routing(topk_idx, topk_w, ref_idx, ref_w, w_rtol=1e-5, w_atol=1e-6):
+    """Selected experts must be identical per token as a set (the order inside the
+    eight is not defined by torch.topk(sorted=False)); weights are compared after
+    sorting both sides by expert index."""
+    a_idx, a_ord = torch.sort(topk_idx.detach().cpu().to(torch.int64), dim=1)
+    b_idx, b_ord = torch.sort(ref_idx.detach().cpu().to(torch.int64), dim=1)
+    same = bool(torch.equal(a_idx, b_idx))
+    a_w = topk_w.detach().cpu().float().gather(1, a_ord)
+    b_w = ref_w.detach().cpu().float().gather(1, b_ord)
+    w_ok = bool(torch.allclose(a_w, b_w, rtol=w_rtol, atol=w_atol)) if same else False
+    bad = int((a_idx != b_idx).any(dim=1).sum())
+    return same and w_ok, {"idx_equal": same, "weights_close": w_ok, "tokens_differing": bad}
