@@ -115,6 +115,14 @@ int syfi_moe_check(syfi_moe_ctx* ctx, int32_t* stats4, void* stream);
 int syfi_moe_debug_read(syfi_moe_ctx* ctx, const char* name, void* dst_host, int64_t max_bytes, int64_t* bytes,
                         int32_t* row_cap);
 
+/* Per-kernel timing.  When enabled, every forward brackets each of its six kernels (router,
+ * row lists, gather, GEMM1, GEMM2, combine — in that order) with CUDA events on the stream it is
+ * enqueued on; syfi_moe_last_stage_ms() synchronises on the last event and writes the six
+ * durations in milliseconds.  Off by default.  (The reference has no timing hooks; its
+ * profiling script wraps whole calls, moe/scripts/profile_single.py:50-56.) */
+int syfi_moe_set_stage_timing(syfi_moe_ctx* ctx, int32_t enable);
+int syfi_moe_last_stage_ms(syfi_moe_ctx* ctx, float* ms6);
+
 /* Number of kernels the most recent forward enqueued (for launch accounting). */
 int syfi_moe_last_launch_count(syfi_moe_ctx* ctx);
 

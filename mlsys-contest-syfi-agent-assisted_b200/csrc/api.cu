@@ -24,6 +24,10 @@ struct syfi_moe_ctx {
   // staging buffers of syfi_moe_forward_host
   void* stage = nullptr;
   size_t stage_bytes = 0;
+  // optional per-kernel timing
+  bool timing = false;
+  bool timing_valid = false;
+  cudaEvent_t ev[7] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   std::mutex mu;
 };
 
@@ -184,18 +188,30 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
   if ((rc = make_map(&g2.tm_b1, ws.c_lo, ws.row_cap, kInter, kTokenTile))) return rc;
 
   ctx->launches = 0;
+  const bool timed = ctx->timing && ctx->ev[0] != nullptr;
+  ctx->timing_valid = false;
+#define STAGE_MARK(i) do { if (timed) CU_TRY(cudaEventRecord(ctx->ev[i], st)); } while (0)
+  STAGE_MARK(0);
   CU_TRY(launch_router(static_cast<const float*>(logits), bias, T, e_local, (int)offset, (float)scaling, ws, st));
   ctx->launches += 1;
+  STAGE_MARK(1);
   CU_TRY(launch_build_rows(T, e_local, (int)offset, ws, st));
   ctx->launches += 1;
+  STAGE_MARK(2);
   CU_TRY(launch_gather(static_cast<const uint8_t*>(hs), static_cast<const float*>(hs_scale), T, ws, st));
   ctx->launches += 1;
+  STAGE_MARK(3);
   CU_TRY(launch_gemm1(g1, static_cast<const float*>(w13_scale), ws, ctx->num_sms, st));
   ctx->launches += 1;
+  STAGE_MARK(4);
   CU_TRY(launch_gemm2(g2, static_cast<const float*>(w2_scale), ws, ctx->num_sms, st));
   ctx->launches += 1;
+  STAGE_MARK(5);
   CU_TRY(launch_combine(T, ws, out, out_is_f32, st));
   ctx->launches += 1;
+  STAGE_MARK(6);
+#undef STAGE_MARK
+  ctx->timing_valid = timed;
   return SYFI_MOE_OK;
 }
 
@@ -257,6 +273,8 @@ int syfi_moe_destroy(syfi_moe_ctx* ctx) {
     cudaDeviceSynchronize();
     free_workspace(ctx->ws);
     if (ctx->stage) cudaFree(ctx->stage);
+    for (cudaEvent_t e : ctx->ev)
+      if (e) cudaEventDestroy(e);
   }
   delete ctx;
   return SYFI_MOE_OK;
@@ -417,6 +435,26 @@ int syfi_moe_debug_read(syfi_moe_ctx* ctx, const char* name, void* dst_host, int
     }
   }
   return fail(SYFI_MOE_ERR_INVALID, "unknown workspace buffer '%s'", name);
+}
+
+int syfi_moe_set_stage_timing(syfi_moe_ctx* ctx, int32_t enable) {
+  if (!ctx) return fail(SYFI_MOE_ERR_INVALID, "context is null");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard guard(ctx->ws.device);
+  if (enable && ctx->ev[0] == nullptr)
+    for (cudaEvent_t& e : ctx->ev) CU_TRY(cudaEventCreate(&e));
+  ctx->timing = enable != 0;
+  ctx->timing_valid = false;
+  return SYFI_MOE_OK;
+}
+
+int syfi_moe_last_stage_ms(syfi_moe_ctx* ctx, float* ms6) {
+  if (!ctx || !ms6) return fail(SYFI_MOE_ERR_INVALID, "null argument");
+  if (!ctx->timing_valid) return fail(SYFI_MOE_ERR_INVALID, "no timed forward has run (enable stage timing first)");
+  DeviceGuard guard(ctx->ws.device);
+  CU_TRY(cudaEventSynchronize(ctx->ev[6]));
+  for (int i = 0; i < 6; ++i) CU_TRY(cudaEventElapsedTime(&ms6[i], ctx->ev[i], ctx->ev[i + 1]));
+  return SYFI_MOE_OK;
 }
 
 int syfi_moe_last_launch_count(syfi_moe_ctx* ctx) { return ctx ? ctx->launches : 0; }

@@ -41,6 +41,8 @@ ABI = {
     "syfi_moe_check": (ctypes.c_int, [_vp, ctypes.POINTER(_i32), _vp]),
     "syfi_moe_debug_read": (ctypes.c_int, [_vp, ctypes.c_char_p, _vp, _i64, ctypes.POINTER(_i64),
                                            ctypes.POINTER(_i32)]),
+    "syfi_moe_set_stage_timing": (ctypes.c_int, [_vp, _i32]),
+    "syfi_moe_last_stage_ms": (ctypes.c_int, [_vp, ctypes.POINTER(ctypes.c_float)]),
     "syfi_moe_last_launch_count": (ctypes.c_int, [_vp]),
     "syfi_moe_workspace_bytes": (_i64, [_vp]),
     "syfi_moe_last_error": (ctypes.c_char_p, []),
@@ -112,6 +114,17 @@ class MoeContext:
         _check(self.lib.syfi_moe_last_routing(self.handle, num_tokens, idx.data_ptr(), w.data_ptr(),
                                               _stream_ptr(stream, self.device)))
         return idx, w
+
+    STAGES = ("router", "row_lists", "gather", "gemm1", "gemm2", "combine")
+
+    def set_stage_timing(self, enable: bool):
+        _check(self.lib.syfi_moe_set_stage_timing(self.handle, 1 if enable else 0))
+
+    def last_stage_ms(self) -> dict:
+        """Durations in ms of the six kernels of the last forward (stage timing must be on)."""
+        ms = (ctypes.c_float * 6)()
+        _check(self.lib.syfi_moe_last_stage_ms(self.handle, ms))
+        return dict(zip(self.STAGES, [float(x) for x in ms]))
 
     def launch_count(self) -> int:
         return int(self.lib.syfi_moe_last_launch_count(self.handle))

@@ -1,0 +1,224 @@
+"""Parity of the CUDA path (called through the C ABI) against the oracle.  All tests need a B200."""
+import os
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+def _run(pkg, inp, dtype=torch.bfloat16):
+    out = torch.full((inp.num_tokens, 7168), float("nan"), dtype=dtype, device=inp.gemm1_weights.device)
+    pkg.run_moe(*inp.args(), out)
+    stats = pkg.get_context(0).check()
+    return out, stats
+
+
+# ------------------------------------------------------------------ routing
+@pytest.mark.parametrize("T", [1, 7, 16, 64, 1024, 8192])
+def test_routing_bit_exact(T, pkg, oracle):
+    inp = pkg.make_inputs(num_tokens=T, seed=0, e_local=1, device="cpu")
+    idx, w = pkg.route(inp.routing_logits.to(DEV), inp.routing_bias.to(DEV), 0, 2.5)
+    ridx, rw = oracle.route(inp.routing_logits, inp.routing_bias, 2.5)
+    ok, stats = oracle.check_routing(idx, w, ridx, rw)
+    assert ok, stats
+    # best-first order: weights follow the biased score, so just check indices are a permutation of the set
+    assert idx.dtype == torch.int32 and w.dtype == torch.float32
+
+
+@pytest.mark.parametrize("T", [1024, 8192])
+def test_routing_matches_published_reference_vectors(T, pkg, oracle, golden_dir):
+    g = torch.load(os.path.join(golden_dir, f"route_t{T}.pt"))
+    inp = pkg.make_inputs(num_tokens=T, seed=0, e_local=1, device="cpu")
+    idx, w = pkg.route(inp.routing_logits.to(DEV), inp.routing_bias.to(DEV), 0, 2.5)
+    a = torch.sort(idx.cpu().long(), dim=1).values
+    b = torch.sort(g["topk_idx"].long(), dim=1).values
+    assert torch.equal(a, b)
+    ok, stats = oracle.check_routing(idx[:256], w[:256], g["topk_idx"][:256].long(), g["topk_w_first256"])
+    assert ok, stats
+
+
+def test_routing_with_skewed_logits(pkg, oracle):
+    inp = pkg.make_inputs(num_tokens=4096, seed=0, e_local=1, hot_experts=16, device="cpu")
+    idx, w = pkg.route(inp.routing_logits.to(DEV), inp.routing_bias.to(DEV), 64, 1.0, num_local_experts=32)
+    ridx, rw = oracle.route(inp.routing_logits, inp.routing_bias, 1.0)
+    ok, stats = oracle.check_routing(idx, w, ridx, rw)
+    assert ok, stats
+
+
+# -------------------------------------------------------------- permutation
+@pytest.mark.parametrize("T,E,off", [(64, 32, 0), (300, 8, 0), (129, 4, 36)])
+def test_row_lists(T, E, off, pkg):
+    inp = pkg.make_inputs(num_tokens=T, seed=1, e_local=E, local_expert_offset=off, device=DEV)
+    _, stats = _run(pkg, inp)
+    ctx = pkg.get_context(0)
+    idx, _ = ctx.last_routing(T)
+    row_token, cap = ctx.debug_read("row_token", torch.int32)
+    route_row, _ = ctx.debug_read("route_row", torch.int32)
+    counts, _ = ctx.debug_read("counts", torch.int32)
+    tiles, _ = ctx.debug_read("tiles", torch.int32)
+    route_row = route_row[: T * 8].view(T, 8)
+    local = (idx >= off) & (idx < off + E)
+    assert stats["routes"] == int(local.sum())
+    assert stats["active_experts"] == int(torch.unique(idx[local]).numel())
+    exp_counts = torch.bincount((idx[local] - off).long(), minlength=32)[:E]
+    assert torch.equal(counts[:E].long(), exp_counts)
+    pad = (exp_counts + 15) // 16 * 16
+    assert stats["padded_rows"] == int(pad.sum())
+    # rows of an expert are its tokens in increasing order, then -1 padding
+    start = 0
+    for e in range(E):
+        c, cp = int(exp_counts[e]), int(pad[e])
+        toks = torch.nonzero((idx == e + off).any(1)).squeeze(1).int()
+        assert torch.equal(row_token[start:start + c], toks)
+        assert bool((row_token[start + c:start + cp] == -1).all())
+        start += cp
+    # route_row inverts row_token for local routes and is -1 elsewhere
+    assert bool((route_row[~local] == -1).all())
+    rows = route_row[local].long()
+    assert torch.equal(row_token[rows].long(), torch.nonzero(local)[:, 0])
+    # tile table covers the padded rows exactly once, tiles never straddle experts
+    nt = stats["token_tiles"]
+    tl = tiles[: nt * 4].view(nt, 4)
+    covered = torch.zeros(int(pad.sum()), dtype=torch.int32)
+    bounds = torch.cumsum(torch.cat([torch.zeros(1, dtype=torch.long), pad]), 0)
+    for e, rs, n, _ in tl.tolist():
+        assert n % 16 == 0 and 16 <= n <= 64
+        assert bounds[e] <= rs and rs + n <= bounds[e + 1]
+        covered[rs:rs + n] += 1
+    assert bool((covered == 1).all())
+
+
+# ------------------------------------------------------------ whole layer
+@pytest.mark.parametrize("T,E,off,seed", [
+    (16, 32, 0, 0),      # the CPU-runnable configuration
+    (64, 32, 0, 0),      # decode batch
+    (1, 32, 0, 3), (2, 32, 0, 4), (7, 8, 0, 5),
+    (127, 8, 8, 6), (128, 8, 8, 6), (129, 8, 8, 6),
+    (300, 4, 36, 7),
+])
+def test_layer_matches_oracle(T, E, off, seed, pkg, oracle):
+    inp = pkg.make_inputs(num_tokens=T, seed=seed, e_local=E, local_expert_offset=off, device=DEV)
+    out, stats = _run(pkg, inp)
+    ref, ridx, rw = oracle.moe_forward(*inp.to("cpu").args())
+    idx, w = pkg.get_context(0).last_routing(T)
+    ok, rstats = oracle.check_routing(idx, w, ridx, rw)
+    assert ok, rstats
+    ok, ostats = oracle.check_output(out, ref)
+    assert ok, (ostats, stats)
+
+
+def test_prefill_chunk_matches_oracle(pkg, oracle):
+    """T = 1024, 32 local experts; the oracle runs with torch on the GPU to keep the test short."""
+    inp = pkg.make_inputs(num_tokens=1024, seed=0, e_local=32, device=DEV)
+    out, stats = _run(pkg, inp)
+    ref, ridx, rw = oracle.moe_forward(*inp.args())
+    cidx, cw = oracle.route(inp.routing_logits.cpu(), inp.routing_bias.cpu(), 2.5)
+    idx, w = pkg.get_context(0).last_routing(1024)
+    ok, rstats = oracle.check_routing(idx, w, cidx, cw)
+    assert ok, rstats
+    ok, ostats = oracle.check_output(out, ref)
+    assert ok, (ostats, stats)
+
+
+@pytest.mark.parametrize("name", ["e4_off36", "e8_t16"])
+def test_layer_matches_published_reference_vectors(name, pkg, oracle, golden_dir):
+    """CPU-generated inputs, output compared with what the definition's published reference produced."""
+    g = torch.load(os.path.join(golden_dir, name + ".pt"))
+    inp = pkg.make_inputs(device="cpu", **g["make_inputs"]).to(DEV)
+    out, _ = _run(pkg, inp)
+    ok, ostats = oracle.check_output(out, g["output_bf16_bits"].view(torch.bfloat16))
+    assert ok, ostats
+    idx, w = pkg.get_context(0).last_routing(inp.num_tokens)
+    ok, rstats = oracle.check_routing(idx, w, g["topk_idx"].long(), g["topk_w"])
+    assert ok, rstats
+
+
+def test_tokens_without_local_route_get_zero(pkg):
+    inp = pkg.make_inputs(num_tokens=33, seed=9, e_local=1, local_expert_offset=200, device=DEV)
+    out, stats = _run(pkg, inp)
+    idx, _ = pkg.get_context(0).last_routing(33)
+    hit = (idx == 200).any(1)
+    assert bool((out[~hit.to(DEV)] == 0).all())
+    assert stats["routes"] == int(hit.sum())
+
+
+def test_deterministic_and_workspace_reuse(pkg):
+    inp = pkg.make_inputs(num_tokens=200, seed=11, e_local=8, device=DEV)
+    a, _ = _run(pkg, inp)
+    small = pkg.make_inputs(num_tokens=5, seed=12, e_local=8, device=DEV)
+    _run(pkg, small)                     # a different shape in between, same workspace
+    b, _ = _run(pkg, inp)
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+
+
+def test_scaling_factor_is_linear_exactly(pkg):
+    """Doubling routed_scaling_factor doubles every f32 partial exactly (power-of-two scaling
+    commutes with every rounding on the path), a size-independent property checked at T = 2048."""
+    inp = pkg.make_inputs(num_tokens=2048, seed=13, e_local=16, device=DEV)
+    a, _ = _run(pkg, inp, torch.float32)
+    inp.routed_scaling_factor = 5.0
+    b, _ = _run(pkg, inp, torch.float32)
+    assert torch.equal(b, 2.0 * a)
+    assert float(a.abs().max()) > 0
+
+
+def test_f32_partial_rounds_to_bf16_output(pkg):
+    inp = pkg.make_inputs(num_tokens=96, seed=14, e_local=8, device=DEV)
+    a, _ = _run(pkg, inp)
+    p, _ = _run(pkg, inp, torch.float32)
+    assert torch.equal(a.view(torch.int16), p.to(torch.bfloat16).view(torch.int16))
+
+
+def test_expert_slices_sum_to_full_layer(pkg, oracle):
+    """Four ranks' worth of 8-expert slices (partials summed in f32) equal one 32-expert call."""
+    inp = pkg.make_inputs(num_tokens=256, seed=15, e_local=32, device=DEV)
+    full, _ = _run(pkg, inp, torch.float32)
+    acc = torch.zeros_like(full)
+    for r in range(4):
+        sl = slice(8 * r, 8 * r + 8)
+        part = pkg.MoeInputs(inp.routing_logits, inp.routing_bias, inp.hidden_states, inp.hidden_states_scale,
+                             inp.gemm1_weights[sl].contiguous(), inp.gemm1_weights_scale[sl].contiguous(),
+                             inp.gemm2_weights[sl].contiguous(), inp.gemm2_weights_scale[sl].contiguous(),
+                             8 * r, 2.5)
+        p, _ = _run(pkg, part, torch.float32)
+        acc += p
+    assert torch.allclose(acc, full, rtol=1e-5, atol=1e-5)
+
+
+def test_host_entry_point_matches_device_entry_point(pkg):
+    inp = pkg.make_inputs(num_tokens=64, seed=16, e_local=8, device=DEV)
+    dev_out, _ = _run(pkg, inp)
+    host = [t.cpu().pin_memory() for t in (inp.routing_logits, inp.routing_bias, inp.hidden_states,
+                                           inp.hidden_states_scale)]
+    out = torch.empty(64, 7168, dtype=torch.bfloat16).pin_memory()
+    pkg.run_moe_host(*host, inp.gemm1_weights, inp.gemm1_weights_scale, inp.gemm2_weights,
+                     inp.gemm2_weights_scale, 0, 2.5, out)
+    pkg.get_context(0).check()
+    assert torch.equal(out.view(torch.int16), dev_out.cpu().view(torch.int16))
+
+
+def test_zero_tokens_is_a_no_op(pkg):
+    inp = pkg.make_inputs(num_tokens=0, seed=0, e_local=2, device=DEV)
+    out = torch.empty(0, 7168, dtype=torch.bfloat16, device=DEV)
+    assert pkg.run_moe(*inp.args(), out) is out
+
+
+def test_argument_validation(pkg):
+    inp = pkg.make_inputs(num_tokens=4, seed=0, e_local=2, device=DEV)
+    out = torch.empty(4, 7168, dtype=torch.bfloat16, device=DEV)
+    args = list(inp.args())
+    with pytest.raises(ValueError, match="output"):
+        pkg.run_moe(*args, out[:3])
+    with pytest.raises(ValueError, match="dtype"):
+        pkg.run_moe(args[0].double(), *args[1:], out)
+    with pytest.raises(ValueError, match="contiguous"):
+        pkg.run_moe(args[0], args[1], args[2], inp.hidden_states_scale.t().contiguous().t(), *args[4:], out)
+    with pytest.raises(ValueError, match="outside"):
+        pkg.run_moe(*args[:8], 255, 2.5, out)
+    with pytest.raises(ValueError, match="host tensor|must be on"):
+        pkg.run_moe(args[0].cpu(), *args[1:], out)
+    pkg.run_moe(*args, out)              # the context is still usable afterwards
+    pkg.get_context(0).check()
