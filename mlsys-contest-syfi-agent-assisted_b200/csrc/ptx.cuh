@@ -2,6 +2,7 @@
 // mbarrier (with bounded waits), TMA tiled loads, tcgen05 MMA / TMEM.
 #pragma once
 #include <cuda.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
