@@ -106,7 +106,7 @@ int syfi_moe_last_routing(syfi_moe_ctx* ctx, int64_t num_tokens, int32_t* topk_i
 int syfi_moe_check(syfi_moe_ctx* ctx, int32_t* stats4, void* stream);
 
 /* Test hook: copies a named workspace buffer of the most recent forward into HOST memory
- * ("row_token", "route_row", "tiles", "meta", "counts", "a_perm", "a_scale", "c_hi", "c_lo",
+ * ("row_token", "route_row", "expert_work", "meta", "counts", "a_perm", "a_scale", "c_hi", "c_lo",
  * "c_scale", "o_rows", "topk_idx", "topk_w").  *bytes receives the buffer's size; at most
  * max_bytes are copied (dst_host may be null to query the size); *row_cap receives the row
  * capacity, the leading dimension of the k-block-major scale arrays.  Synchronises the device.

@@ -96,8 +96,8 @@ int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uin
 }
 
 void free_workspace(Workspace& ws) {
-  void* ptrs[] = {ws.topk_idx, ws.topk_w, ws.local_mask, ws.counts, ws.meta, ws.status, ws.row_token, ws.route_row,
-                  ws.tiles, ws.a_perm, ws.a_scale, ws.c_hi, ws.c_lo, ws.c_scale, ws.o_rows};
+  void* ptrs[] = {ws.topk_idx, ws.topk_w, ws.local_mask, ws.counts, ws.meta, ws.status, ws.trace, ws.row_token, ws.route_row,
+                  ws.work, ws.a_perm, ws.a_scale, ws.c_hi, ws.c_lo, ws.c_scale, ws.o_rows};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   const int dev = ws.device;
@@ -117,8 +117,7 @@ int alloc_workspace(Workspace& ws, int64_t max_tokens) {
   free_workspace(ws);
   const int64_t T = max_tokens;
   // worst case: every one of the 8 routes of every token is local, plus per-expert padding
-  const int64_t row_cap = (8 * T + kRowPad * kMaxLocalExperts + kTokenTile - 1) / kTokenTile * kTokenTile;
-  const int64_t tile_cap = row_cap / kTokenTile + kMaxLocalExperts;
+  const int64_t row_cap = (8 * T + kRowPad * kMaxLocalExperts + kMaxTokenTile - 1) / kMaxTokenTile * kMaxTokenTile;
   if (row_cap * (int64_t)kHidden > (int64_t)1 << 40) return fail(SYFI_MOE_ERR_INVALID, "max_tokens too large");
   size_t total = 0;
   CU_TRY(dev_alloc(&ws.topk_idx, T * kTopK, &total));
@@ -127,9 +126,10 @@ int alloc_workspace(Workspace& ws, int64_t max_tokens) {
   CU_TRY(dev_alloc(&ws.counts, kMaxLocalExperts, &total));
   CU_TRY(dev_alloc(&ws.meta, kMetaInts, &total));
   CU_TRY(dev_alloc(&ws.status, 4, &total));
+  CU_TRY(dev_alloc(&ws.trace, 6 * 4096, &total));
   CU_TRY(dev_alloc(&ws.row_token, row_cap, &total));
   CU_TRY(dev_alloc(&ws.route_row, T * kTopK, &total));
-  CU_TRY(dev_alloc(&ws.tiles, tile_cap, &total));
+  CU_TRY(dev_alloc(&ws.work, kMaxLocalExperts, &total));
   CU_TRY(dev_alloc(&ws.a_perm, row_cap * kHidden, &total));
   CU_TRY(dev_alloc(&ws.a_scale, row_cap * kHBlocks, &total));
   CU_TRY(dev_alloc(&ws.c_hi, row_cap * kInter, &total));
@@ -140,7 +140,6 @@ int alloc_workspace(Workspace& ws, int64_t max_tokens) {
   CU_TRY(cudaMemset(ws.meta, 0, kMetaInts * sizeof(int)));
   ws.max_tokens = (int)T;
   ws.row_cap = (int)row_cap;
-  ws.tile_cap = (int)tile_cap;
   ws.bytes = total;
   return SYFI_MOE_OK;
 }
@@ -180,12 +179,16 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
   const int T = (int)T64;
   GemmLaunch g1, g2;
   int rc;
+  // Token tile (MMA N) of this call's GEMMs: 32 rows while the average expert sees few tokens
+  // (8 accumulator slots in flight hide the TMEM round trip), 64 rows otherwise.
+  const int token_tile = (T64 <= 256) ? 32 : 64;
+  g1.token_tile = g2.token_tile = token_tile;
   if ((rc = make_map(&g1.tm_w, w13, (uint64_t)e_local * 2 * kInter, kHidden, 128))) return rc;
-  if ((rc = make_map(&g1.tm_b0, ws.a_perm, ws.row_cap, kHidden, kTokenTile))) return rc;
+  if ((rc = make_map(&g1.tm_b0, ws.a_perm, ws.row_cap, kHidden, token_tile))) return rc;
   g1.tm_b1 = g1.tm_b0;
   if ((rc = make_map(&g2.tm_w, w2, (uint64_t)e_local * kHidden, kInter, 128))) return rc;
-  if ((rc = make_map(&g2.tm_b0, ws.c_hi, ws.row_cap, kInter, kTokenTile))) return rc;
-  if ((rc = make_map(&g2.tm_b1, ws.c_lo, ws.row_cap, kInter, kTokenTile))) return rc;
+  if ((rc = make_map(&g2.tm_b0, ws.c_hi, ws.row_cap, kInter, token_tile))) return rc;
+  if ((rc = make_map(&g2.tm_b1, ws.c_lo, ws.row_cap, kInter, token_tile))) return rc;
 
   ctx->launches = 0;
   const bool timed = ctx->timing && ctx->ev[0] != nullptr;
@@ -195,16 +198,16 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
   CU_TRY(launch_router(static_cast<const float*>(logits), bias, T, e_local, (int)offset, (float)scaling, ws, st));
   ctx->launches += 1;
   STAGE_MARK(1);
-  CU_TRY(launch_build_rows(T, e_local, (int)offset, ws, st));
+  CU_TRY(launch_build_rows(T, e_local, (int)offset, token_tile, ws, st));
   ctx->launches += 1;
   STAGE_MARK(2);
   CU_TRY(launch_gather(static_cast<const uint8_t*>(hs), static_cast<const float*>(hs_scale), T, ws, st));
   ctx->launches += 1;
   STAGE_MARK(3);
-  CU_TRY(launch_gemm1(g1, static_cast<const float*>(w13_scale), ws, ctx->num_sms, st));
+  CU_TRY(launch_gemm1(g1, static_cast<const float*>(w13_scale), e_local, ws, ctx->num_sms, st));
   ctx->launches += 1;
   STAGE_MARK(4);
-  CU_TRY(launch_gemm2(g2, static_cast<const float*>(w2_scale), ws, ctx->num_sms, st));
+  CU_TRY(launch_gemm2(g2, static_cast<const float*>(w2_scale), e_local, ws, ctx->num_sms, st));
   ctx->launches += 1;
   STAGE_MARK(5);
   CU_TRY(launch_combine(T, ws, out, out_is_f32, st));
@@ -416,11 +419,12 @@ int syfi_moe_debug_read(syfi_moe_ctx* ctx, const char* name, void* dst_host, int
   struct Entry { const char* name; void* ptr; int64_t bytes; };
   const Entry table[] = {
       {"row_token", ws.row_token, R * 4},        {"route_row", ws.route_row, T * kTopK * 4},
-      {"tiles", ws.tiles, (int64_t)ws.tile_cap * (int64_t)sizeof(TokenTile)},
+      {"expert_work", ws.work, (int64_t)kMaxLocalExperts * (int64_t)sizeof(ExpertWork)},
       {"meta", ws.meta, kMetaInts * 4},          {"counts", ws.counts, kMaxLocalExperts * 4},
       {"a_perm", ws.a_perm, R * kHidden},        {"a_scale", ws.a_scale, R * kHBlocks * 4},
       {"c_hi", ws.c_hi, R * kInter},             {"c_lo", ws.c_lo, R * kInter},
       {"c_scale", ws.c_scale, R * kIBlocks * 4}, {"o_rows", ws.o_rows, R * kHidden * 4},
+      {"trace", ws.trace, 6 * 4096 * 8},
       {"topk_idx", ws.topk_idx, T * kTopK * 4},  {"topk_w", ws.topk_w, T * kTopK * 4},
   };
   for (const Entry& e : table) {

@@ -6,7 +6,7 @@
 // (moe.cu:1718-1887).
 //
 // Orientation ("swap-AB"): the WEIGHT tile is the 128-row M operand of the MMA and the
-// expert's token rows are the N operand (16..64 columns), so an expert with a handful of
+// expert's token rows are the N operand (16..NT columns, NT = 32 or 64 chosen per launch), so an expert with a handful of
 // rows still issues full-height MMAs and the kernel streams weights at HBM speed.  In the
 // TMEM accumulator a lane is an output feature and a column is a token row.
 //
@@ -29,8 +29,10 @@
 // Pipeline per CTA (persistent over work items, 6 warps): warp 0 = TMA producer (weights
 // with an evict-first L2 policy, token-side tiles evict-last), warp 1 = MMA issuer and TMEM
 // owner, warps 2-5 = promotion/epilogue (one TMEM lane quarter each).  Shared-memory stages
-// form a ring guarded by full/empty mbarriers; the TMEM accumulator pair is double
-// buffered (tfull/tempty) so the MMAs of K block k+1 overlap the promotion of block k.
+// form a ring guarded by full/empty mbarriers; the 512 TMEM columns form a ring of
+// 512 / (2 NT) accumulator-pair slots (tfull/tempty), so the MMAs of several K blocks are in
+// flight while earlier blocks are promoted: the issue -> commit -> tcgen05.ld -> release round
+// trip costs about 1.5 us and has to be hidden behind 4 to 8 K blocks to keep up with HBM.
 // Every wait is bounded: on expiry the CTA raises an abort flag, all roles leave their
 // loops, TMEM is released and the status word reports the failure to the host.
 #include <cuda_fp16.h>
@@ -42,38 +44,29 @@ namespace syfi {
 
 namespace {
 
-constexpr int NT = kTokenTile;            // token columns per work item
 constexpr int kGemmThreads = 192;
 constexpr int kEpiThreads = 128;
 constexpr int kATile = 128 * 128;         // weight tile: 128 rows x 128 bytes of K
-constexpr int kBTile = NT * 128;          // token-side tile
-constexpr int kTmemCols = 4 * NT;         // two accumulators x two buffers
+constexpr int kTmemCols = 512;
 
-template <int MODE> struct Cfg;
-template <> struct Cfg<1> {
-  static constexpr int kKBlocks = kHBlocks;            // 56
-  static constexpr int kFeatTiles = kInter / 128;      // 16
-  static constexpr int kRowsPerExpert = 2 * kInter;    // rows of W13 per expert
-  static constexpr int kStages = 5;
-  static constexpr int kStageBytes = 2 * kATile + kBTile;
+template <int MODE, int NT> struct Cfg {
+  static constexpr int kKBlocks = MODE == 1 ? kHBlocks : kIBlocks;              // 56 / 16
+  static constexpr int kFeatTiles = MODE == 1 ? kInter / 128 : kHidden / 128;   // 16 / 56
+  static constexpr int kRowsPerExpert = MODE == 1 ? 2 * kInter : kHidden;       // weight rows per expert
+  static constexpr int kBTile = NT * 128;                                       // token-side tile bytes
+  static constexpr int kStageBytes = MODE == 1 ? 2 * kATile + kBTile : kATile + 2 * kBTile;
+  static constexpr int kStages = MODE == 1 ? 5 : (NT == 32 ? 8 : 6);
+  static constexpr int kSlots = kTmemCols / (2 * NT);                           // accumulator-pair slots
+  static constexpr int kScaleBufs = MODE == 2 ? 2 : 1;   // mode 2 prefetches the next item's scales
+  static constexpr int kSmemBytes = 1024 /* alignment slack */ + kStages * kStageBytes +
+                                    4 * (kScaleBufs * (kKBlocks * NT + 128) + 4 * NT + 2 * NT) +
+                                    8 * (2 * kStages + 2 * kSlots) +
+                                    kMaxLocalExperts * static_cast<int>(sizeof(ExpertWork)) + 16;
+  static_assert(kSmemBytes <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
 };
-template <> struct Cfg<2> {
-  static constexpr int kKBlocks = kIBlocks;            // 16
-  static constexpr int kFeatTiles = kHidden / 128;     // 56
-  static constexpr int kRowsPerExpert = kHidden;
-  static constexpr int kStages = 6;
-  static constexpr int kStageBytes = kATile + 2 * kBTile;
-};
-
-template <int MODE>
-constexpr int smem_bytes() {
-  using C = Cfg<MODE>;
-  return 1024 /* alignment slack */ + C::kStages * C::kStageBytes + 4 * (C::kKBlocks * NT + 128 + 4 * NT + 2 * NT) +
-         8 * (2 * C::kStages + 4) + 16;
-}
 
 struct GemmArgs {
-  const TokenTile* tiles;
+  const ExpertWork* work;
   const int* meta;
   const float* act_scale;   // [K blocks][row_cap] scales of the token-side operand
   const float* w_scale;     // mode 1: [E][32][56], mode 2: [E][56][16]
@@ -82,37 +75,82 @@ struct GemmArgs {
   float* c_scale;           // [16][row_cap]
   float* o_rows;            // mode 2 output [row_cap][7168]
   int row_cap;
+  int e_local;
   int* status;
+  long long* trace;         // [3][4096] timeline of CTA 0 when built with SYFI_TRACE, else unused
 };
 
-template <int MODE>
+// Optional timeline trace of CTA 0 (compile with -DSYFI_TRACE): role r appends (tag, clock) pairs.
+#ifdef SYFI_TRACE
+#define TRACE(role, tag)                                                                       \
+  do {                                                                                         \
+    if (blockIdx.x == 0 && p.trace != nullptr && trace_n < 2040) {                             \
+      p.trace[(role) * 4096 + 2 * trace_n] = (tag);                                            \
+      p.trace[(role) * 4096 + 2 * trace_n + 1] = clock64();                                    \
+      ++trace_n;                                                                               \
+    }                                                                                          \
+  } while (0)
+#else
+#define TRACE(role, tag) do { } while (0)
+#endif
+
+struct Item {
+  int expert, ft, row_start, n;
+};
+
+// Work item w -> (expert, feature tile, token tile); see ExpertWork for the numbering.
+template <int FT, int NT>
+__device__ __forceinline__ Item decode_item(const ExpertWork* s_work, int e_local, int w) {
+  Item it{0, 0, 0, 0};
+  for (int e = 0; e < e_local; ++e) {
+    const ExpertWork ew = s_work[e];
+    const int base = ew.tile_off * FT;
+    if (w < base + ew.tiles * FT) {
+      const int local = w - base;
+      const int ti = local % ew.tiles;
+      it.expert = e;
+      it.ft = local / ew.tiles;
+      it.row_start = ew.row_off + ti * NT;
+      it.n = min(NT, ew.rows_pad - ti * NT);
+      return it;
+    }
+  }
+  return it;
+}
+
+template <int MODE, int NT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_b0,
                     const __grid_constant__ CUtensorMap tm_b1, const GemmArgs p) {
-  using C = Cfg<MODE>;
+  using C = Cfg<MODE, NT>;
   constexpr int S = C::kStages;
   constexpr int KB = C::kKBlocks;
   constexpr int FT = C::kFeatTiles;
+  constexpr int SLOTS = C::kSlots;
+  constexpr int kBTile = C::kBTile;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  float* s_act = reinterpret_cast<float*>(smem + S * C::kStageBytes);   // [KB][NT]
-  float* s_ws = s_act + KB * NT;                                        // [2][64]
-  float* s_red = s_ws + 128;                                            // [4][NT]
+  constexpr int kScaleStride = KB * NT + 128;                           // one buffer: [KB][NT] + [2][64]
+  float* s_scales = reinterpret_cast<float*>(smem + S * C::kStageBytes);
+  float* s_red = s_scales + C::kScaleBufs * kScaleStride;               // [4][NT]
   float* s_cs = s_red + 4 * NT;                                         // [NT] scale
   float* s_inv = s_cs + NT;                                             // [NT] 1 / scale
   uint64_t* full = reinterpret_cast<uint64_t*>(s_inv + NT);
   uint64_t* empty = full + S;
   uint64_t* tfull = empty + S;
-  uint64_t* tempty = tfull + 2;
-  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint64_t* tempty = tfull + SLOTS;
+  ExpertWork* s_work = reinterpret_cast<ExpertWork*>(tempty + SLOTS);
+  uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_work + kMaxLocalExperts);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  int trace_n = 0;
+  (void)trace_n;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 4); }
+    for (int i = 0; i < SLOTS; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 4); }
     *s_abort = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tm_w);
@@ -122,6 +160,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   if (warp == 1) {
     tmem_alloc(s_tmem, kTmemCols);
     tmem_relinquish();
+  }
+  if (threadIdx.x >= 64 && threadIdx.x < 64 + kMaxLocalExperts) {
+    const int e = threadIdx.x - 64;
+    s_work[e] = (e < p.e_local) ? p.work[e] : ExpertWork{0, 0, 0, 0};
   }
   tc_fence_before();
   __syncthreads();
@@ -135,23 +177,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     const uint64_t pol_b = l2_policy_evict_last();
     uint32_t it = 0;
     for (int w = blockIdx.x; w < total; w += gridDim.x) {
-      const TokenTile tt = p.tiles[w / FT];
-      const int ft = w % FT;
-      const int wrow = tt.expert * C::kRowsPerExpert + ft * 128;
+      const Item im = decode_item<FT, NT>(s_work, p.e_local, w);
+      const int wrow = im.expert * C::kRowsPerExpert + im.ft * 128;
       for (int kb = 0; kb < KB; ++kb) {
         if (lane == 0) {
           const int s = it % S;
           if (mbar_wait_bounded(&empty[s], ((it / S) & 1) ^ 1, s_abort, kStatusWaitTimeoutProducer)) {
             uint8_t* st = smem + s * C::kStageBytes;
+            TRACE(0, kb);
             mbar_arrive_expect_tx(&full[s], C::kStageBytes);
             if (MODE == 1) {
               tma_load_2d(st, &tm_w, &full[s], kb * 128, wrow, pol_w);
               tma_load_2d(st + kATile, &tm_w, &full[s], kb * 128, wrow + kInter, pol_w);
-              tma_load_2d(st + 2 * kATile, &tm_b0, &full[s], kb * 128, tt.row_start, pol_b);
+              tma_load_2d(st + 2 * kATile, &tm_b0, &full[s], kb * 128, im.row_start, pol_b);
             } else {
               tma_load_2d(st, &tm_w, &full[s], kb * 128, wrow, pol_w);
-              tma_load_2d(st + kATile, &tm_b0, &full[s], kb * 128, tt.row_start, pol_b);
-              tma_load_2d(st + kATile + kBTile, &tm_b1, &full[s], kb * 128, tt.row_start, pol_b);
+              tma_load_2d(st + kATile, &tm_b0, &full[s], kb * 128, im.row_start, pol_b);
+              tma_load_2d(st + kATile + kBTile, &tm_b1, &full[s], kb * 128, im.row_start, pol_b);
             }
             ++it;
           }
@@ -170,40 +212,43 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     __syncwarp();
   } else if (warp == 1) {
     // --------------------------------------------------------------- MMA issuer
-    uint32_t it = 0, ab = 0;
+    uint32_t it = 0;
     for (int w = blockIdx.x; w < total; w += gridDim.x) {
-      const TokenTile tt = p.tiles[w / FT];
-      const uint32_t idesc = umma_idesc_e4m3_m128(static_cast<uint32_t>(tt.n));
-      for (int kb = 0; kb < KB; ++kb, ++it, ++ab) {
+      const Item im = decode_item<FT, NT>(s_work, p.e_local, w);
+      // An MMA of M = 128 occupies the tensor pipe for the same time whatever its N, so mode 2
+      // issues ONE MMA of N = 2 NT per 32 bytes of K over the adjacent hi and lo tiles (the
+      // columns past the tile's n rows hold other rows' data and are never read back) instead
+      // of one per term; mode 1 needs two because up and gate are different A tiles.
+      const uint32_t idesc = umma_idesc_e4m3_m128(MODE == 1 ? static_cast<uint32_t>(im.n) : 2u * NT);
+      for (int kb = 0; kb < KB; ++kb) {
         if (lane == 0) {
           const int s = it % S;
-          const uint32_t buf = ab & 1u;
+          const uint32_t slot = it % SLOTS;
           if (mbar_wait_bounded(&full[s], (it / S) & 1, s_abort, kStatusWaitTimeoutMma) &&
-              mbar_wait_bounded(&tempty[buf], ((ab >> 1) & 1u) ^ 1u, s_abort, kStatusWaitTimeoutMma)) {
+              mbar_wait_bounded(&tempty[slot], ((it / SLOTS) & 1u) ^ 1u, s_abort, kStatusWaitTimeoutMma)) {
             tc_fence_after();
+            TRACE(1, kb);
             const uint32_t st = smem_u32(smem + s * C::kStageBytes);
-            const uint32_t d0 = tmem_base + buf * (2 * NT);
-            const uint32_t d1 = d0 + NT;
-            uint64_t a0, a1, b0, b1;
+            const uint32_t d0 = tmem_base + slot * (2 * NT);
             if (MODE == 1) {
-              a0 = umma_smem_desc_sw128(st);
-              a1 = umma_smem_desc_sw128(st + kATile);
-              b0 = umma_smem_desc_sw128(st + 2 * kATile);
-              b1 = b0;
-            } else {
-              a0 = umma_smem_desc_sw128(st);
-              a1 = a0;
-              b0 = umma_smem_desc_sw128(st + kATile);
-              b1 = umma_smem_desc_sw128(st + kATile + kBTile);
-            }
+              const uint64_t a0 = umma_smem_desc_sw128(st);
+              const uint64_t a1 = umma_smem_desc_sw128(st + kATile);
+              const uint64_t b0 = umma_smem_desc_sw128(st + 2 * kATile);
 #pragma unroll
-            for (int k4 = 0; k4 < 4; ++k4) {
-              // 32 bytes of K per MMA: +2 in the 16-byte-unit address field
-              umma_f8(d0, a0 + 2 * k4, b0 + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
-              umma_f8(d1, a1 + 2 * k4, b1 + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
+              for (int k4 = 0; k4 < 4; ++k4) {
+                // 32 bytes of K per MMA: +2 in the 16-byte-unit address field
+                umma_f8(d0, a0 + 2 * k4, b0 + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
+                umma_f8(d0 + NT, a1 + 2 * k4, b0 + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
+              }
+            } else {
+              const uint64_t a0 = umma_smem_desc_sw128(st);
+              const uint64_t b0 = umma_smem_desc_sw128(st + kATile);   // hi rows, then lo rows
+#pragma unroll
+              for (int k4 = 0; k4 < 4; ++k4) umma_f8(d0, a0 + 2 * k4, b0 + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
             }
             umma_commit(&empty[s]);
-            umma_commit(&tfull[buf]);
+            umma_commit(&tfull[slot]);
+            ++it;
           }
         }
         __syncwarp();
@@ -217,28 +262,65 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     const int feat = q * 32 + lane;         // feature (row of the weight tile) of this thread
     const int et = threadIdx.x - 64;        // 0..127 among the epilogue threads
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-    uint32_t ab = 0;
+    uint32_t it = 0;
     bool ok = true;
+    int sbuf = 0;
+    if (MODE == 2 && static_cast<int>(blockIdx.x) < total) {
+      const Item nx = decode_item<FT, NT>(s_work, p.e_local, blockIdx.x);
+      for (int i = et; i < KB * NT; i += kEpiThreads) {
+        const int kb = i / NT, j = i % NT;
+        if (j < nx.n) cp_async_f32(s_scales + i, p.act_scale + static_cast<size_t>(kb) * p.row_cap + nx.row_start + j);
+      }
+      if (et < KB)
+        cp_async_f32(s_scales + KB * NT + et,
+                     p.w_scale + (static_cast<size_t>(nx.expert) * kHBlocks + nx.ft) * kIBlocks + et);
+    }
     // After a failed wait a warp keeps walking the work list and still joins every named
     // barrier below (doing no other work), so the four warps can never strand each other.
     for (int w = blockIdx.x; w < total; w += gridDim.x) {
-      const TokenTile tt = p.tiles[w / FT];
-      const int ft = w % FT;
-      const int n = ok ? tt.n : 0;
-      named_bar_sync(1, kEpiThreads);       // previous item's readers of the staging arrays are done
-      for (int i = et; i < KB * NT && ok; i += kEpiThreads) {
-        const int kb = i / NT, j = i % NT;
-        s_act[i] = (j < n) ? __ldg(p.act_scale + static_cast<size_t>(kb) * p.row_cap + tt.row_start + j) : 0.0f;
-      }
-      if (et < KB && ok) {
-        if (MODE == 1) {
-          s_ws[et] = __ldg(p.w_scale + (static_cast<size_t>(tt.expert) * 32 + ft) * kHBlocks + et);
-          s_ws[64 + et] = __ldg(p.w_scale + (static_cast<size_t>(tt.expert) * 32 + 16 + ft) * kHBlocks + et);
-        } else {
-          s_ws[et] = __ldg(p.w_scale + (static_cast<size_t>(tt.expert) * kHBlocks + ft) * kIBlocks + et);
+      const Item im = decode_item<FT, NT>(s_work, p.e_local, w);
+      const int ft = im.ft;
+      const int n = ok ? im.n : 0;
+      if (et == 0) TRACE(2, 1000);
+      float* s_act;
+      float* s_ws;
+      if (MODE == 1) {
+        s_act = s_scales;
+        s_ws = s_scales + KB * NT;
+        named_bar_sync(1, kEpiThreads);     // previous item's readers of the staging arrays are done
+        for (int i = et; i < KB * NT && ok; i += kEpiThreads) {
+          const int kb = i / NT, j = i % NT;
+          s_act[i] = (j < n) ? __ldg(p.act_scale + static_cast<size_t>(kb) * p.row_cap + im.row_start + j) : 0.0f;
         }
+        if (et < KB && ok) {
+          s_ws[et] = __ldg(p.w_scale + (static_cast<size_t>(im.expert) * 32 + ft) * kHBlocks + et);
+          s_ws[64 + et] = __ldg(p.w_scale + (static_cast<size_t>(im.expert) * 32 + 16 + ft) * kHBlocks + et);
+        }
+        named_bar_sync(1, kEpiThreads);
+      } else {
+        // Scales of this item were requested with cp.async while the previous item ran (the very
+        // first item's just before the loop); one barrier publishes them and retires the buffer
+        // the item before used, which then receives the next item's scales.  Columns >= n are
+        // never read, so they are not filled.
+        s_act = s_scales + sbuf * kScaleStride;
+        s_ws = s_act + KB * NT;
+        cp_async_wait_all();
+        named_bar_sync(1, kEpiThreads);
+        const int wn = w + gridDim.x;
+        if (wn < total && ok) {
+          const Item nx = decode_item<FT, NT>(s_work, p.e_local, wn);
+          float* d_act = s_scales + (sbuf ^ 1) * kScaleStride;
+          for (int i = et; i < KB * NT; i += kEpiThreads) {
+            const int kb = i / NT, j = i % NT;
+            if (j < nx.n) cp_async_f32(d_act + i, p.act_scale + static_cast<size_t>(kb) * p.row_cap + nx.row_start + j);
+          }
+          if (et < KB)
+            cp_async_f32(d_act + KB * NT + et,
+                         p.w_scale + (static_cast<size_t>(nx.expert) * kHBlocks + nx.ft) * kIBlocks + et);
+        }
+        sbuf ^= 1;
       }
-      named_bar_sync(1, kEpiThreads);
+      if (et == 0) TRACE(2, 1001);
 
       float acc0[NT];                        // mode 1: up,   mode 2: output
       float acc1[MODE == 1 ? NT : 1];        // mode 1: gate
@@ -249,39 +331,51 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         for (int j = 0; j < NT; ++j) acc1[j] = 0.0f;
       }
 
-      for (int kb = 0; kb < KB && ok; ++kb, ++ab) {
-        const uint32_t buf = ab & 1u;
-        if (!mbar_wait_bounded(&tfull[buf], (ab >> 1) & 1u, s_abort, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
+      for (int kb = 0; kb < KB && ok; ++kb, ++it) {
+        const uint32_t slot = it % SLOTS;
+        if (!mbar_wait_bounded(&tfull[slot], (it / SLOTS) & 1u, s_abort, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t t0 = lane_addr + buf * (2 * NT);
+        if (et == 0) TRACE(2, kb);
+        const uint32_t t0 = lane_addr + slot * (2 * NT);
         const float ws0 = s_ws[kb];
         const float ws1 = (MODE == 1) ? s_ws[64 + kb] : 0.0f;
         const float* sa = s_act + kb * NT;
 #pragma unroll
-        for (int c = 0; c < NT / 16; ++c) {
-          if (c * 16 < n) {
-            uint32_t v0[16], v1[16];
-            tmem_ld16(t0 + c * 16, v0);
-            tmem_ld16(t0 + NT + c * 16, v1);
+        for (int h = 0; h < NT / 32; ++h) {   // 32 columns at a time: four loads in flight, one wait
+          if (h * 32 < n) {
+            uint32_t v0[2][16], v1[2][16];
+            tmem_ld16(t0 + h * 32, v0[0]);
+            tmem_ld16(t0 + NT + h * 32, v1[0]);
+            if (h * 32 + 16 < n) {
+              tmem_ld16(t0 + h * 32 + 16, v0[1]);
+              tmem_ld16(t0 + NT + h * 32 + 16, v1[1]);
+            }
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const float a = sa[c * 16 + j];
-              if (MODE == 1) {
-                acc0[c * 16 + j] = fmaf(__uint_as_float(v0[j]), a * ws0, acc0[c * 16 + j]);
-                acc1[c * 16 + j] = fmaf(__uint_as_float(v1[j]), a * ws1, acc1[c * 16 + j]);
-              } else {
-                const float v = fmaf(__uint_as_float(v1[j]), 1.0f / kLoRatio, __uint_as_float(v0[j]));
-                acc0[c * 16 + j] = fmaf(v, a * ws0, acc0[c * 16 + j]);
+            for (int c = 0; c < 2; ++c) {
+              if (h * 32 + c * 16 < n) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  const int col = h * 32 + c * 16 + j;
+                  const float a = sa[col];
+                  if (MODE == 1) {
+                    acc0[col] = fmaf(__uint_as_float(v0[c][j]), a * ws0, acc0[col]);
+                    acc1[col] = fmaf(__uint_as_float(v1[c][j]), a * ws1, acc1[col]);
+                  } else {
+                    const float v = fmaf(__uint_as_float(v1[c][j]), 1.0f / kLoRatio, __uint_as_float(v0[c][j]));
+                    acc0[col] = fmaf(v, a * ws0, acc0[col]);
+                  }
+                }
               }
             }
           }
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tempty[buf]);
+        if (lane == 0) mbar_arrive(&tempty[slot]);
       }
       const int n_out = ok ? n : 0;           // a failed item stores nothing
+      if (et == 0) TRACE(2, 1002);
 
       if (MODE == 1) {
         // SwiGLU, then the per-row amax over the 128 features of this tile
@@ -301,11 +395,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           const float sc = fmaxf(amax * (1.0f / 448.0f), 1e-12f);
           s_cs[et] = sc;
           s_inv[et] = 1.0f / sc;
-          p.c_scale[static_cast<size_t>(ft) * p.row_cap + tt.row_start + et] = sc;
+          p.c_scale[static_cast<size_t>(ft) * p.row_cap + im.row_start + et] = sc;
         }
         named_bar_sync(2, kEpiThreads);
-        uint8_t* hi = p.c_hi + static_cast<size_t>(tt.row_start) * kInter + ft * 128 + feat;
-        uint8_t* lo = p.c_lo + static_cast<size_t>(tt.row_start) * kInter + ft * 128 + feat;
+        uint8_t* hi = p.c_hi + static_cast<size_t>(im.row_start) * kInter + ft * 128 + feat;
+        uint8_t* lo = p.c_lo + static_cast<size_t>(im.row_start) * kInter + ft * 128 + feat;
 #pragma unroll
         for (int j = 0; j < NT; j += 2) {
           if (j < n_out) {
@@ -323,7 +417,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           }
         }
       } else {
-        float* o = p.o_rows + static_cast<size_t>(tt.row_start) * kHidden + ft * 128 + feat;
+        float* o = p.o_rows + static_cast<size_t>(im.row_start) * kHidden + ft * 128 + feat;
 #pragma unroll
         for (int j = 0; j < NT; ++j)
           if (j < n_out) o[static_cast<size_t>(j) * kHidden] = acc0[j];
@@ -340,33 +434,40 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   if (threadIdx.x == 0 && *s_abort != 0) atomicExch(p.status, *s_abort);
 }
 
-template <int MODE>
+template <int MODE, int NT>
 cudaError_t launch_gemm(const GemmLaunch& g, const GemmArgs& a, int num_sms, cudaStream_t st) {
-  grouped_gemm_kernel<MODE><<<num_sms, kGemmThreads, smem_bytes<MODE>(), st>>>(g.tm_w, g.tm_b0, g.tm_b1, a);
+  grouped_gemm_kernel<MODE, NT><<<num_sms, kGemmThreads, Cfg<MODE, NT>::kSmemBytes, st>>>(g.tm_w, g.tm_b0, g.tm_b1, a);
   return cudaGetLastError();
+}
+
+template <int MODE, int NT>
+cudaError_t set_smem_attr() {
+  return cudaFuncSetAttribute(grouped_gemm_kernel<MODE, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              Cfg<MODE, NT>::kSmemBytes);
 }
 
 }  // namespace
 
 cudaError_t gemm_set_attributes() {
-  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       smem_bytes<1>());
-  if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(grouped_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              smem_bytes<2>());
+  cudaError_t e;
+  if ((e = set_smem_attr<1, 32>()) != cudaSuccess) return e;
+  if ((e = set_smem_attr<1, 64>()) != cudaSuccess) return e;
+  if ((e = set_smem_attr<2, 32>()) != cudaSuccess) return e;
+  return set_smem_attr<2, 64>();
 }
 
-cudaError_t launch_gemm1(const GemmLaunch& g, const float* w13_scale, const Workspace& ws, int num_sms,
+cudaError_t launch_gemm1(const GemmLaunch& g, const float* w13_scale, int e_local, const Workspace& ws, int num_sms,
                          cudaStream_t st) {
-  GemmArgs a{ws.tiles, ws.meta, ws.a_scale, w13_scale, ws.c_hi, ws.c_lo, ws.c_scale, nullptr, ws.row_cap,
-             ws.status};
-  return launch_gemm<1>(g, a, num_sms, st);
+  GemmArgs a{ws.work, ws.meta, ws.a_scale, w13_scale, ws.c_hi, ws.c_lo, ws.c_scale, nullptr, ws.row_cap, e_local,
+             ws.status, ws.trace};
+  return g.token_tile == 32 ? launch_gemm<1, 32>(g, a, num_sms, st) : launch_gemm<1, 64>(g, a, num_sms, st);
 }
 
-cudaError_t launch_gemm2(const GemmLaunch& g, const float* w2_scale, const Workspace& ws, int num_sms,
+cudaError_t launch_gemm2(const GemmLaunch& g, const float* w2_scale, int e_local, const Workspace& ws, int num_sms,
                          cudaStream_t st) {
-  GemmArgs a{ws.tiles, ws.meta, ws.c_scale, w2_scale, nullptr, nullptr, nullptr, ws.o_rows, ws.row_cap, ws.status};
-  return launch_gemm<2>(g, a, num_sms, st);
+  GemmArgs a{ws.work, ws.meta, ws.c_scale, w2_scale, nullptr, nullptr, nullptr, ws.o_rows, ws.row_cap, e_local,
+             ws.status, ws.trace + 3 * 4096};
+  return g.token_tile == 32 ? launch_gemm<2, 32>(g, a, num_sms, st) : launch_gemm<2, 64>(g, a, num_sms, st);
 }
 
 }  // namespace syfi

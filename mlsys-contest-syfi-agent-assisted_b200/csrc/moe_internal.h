@@ -19,7 +19,7 @@ constexpr int kMaxLocalExperts = 32;
 constexpr int kHBlocks = kHidden / kBlock;   // 56
 constexpr int kIBlocks = kInter / kBlock;    // 16
 constexpr int kRowPad = 16;                  // each expert's row range is padded to this
-constexpr int kTokenTile = 64;               // token rows per GEMM work item (MMA N)
+constexpr int kMaxTokenTile = 64;            // largest token tile (MMA N) any GEMM variant uses
 constexpr float kLoRatio = 28.0f;            // scale(hi) / scale(lo) of the two-term e4m3 intermediate
 
 // status codes written by kernels into Workspace::status[0]
@@ -36,19 +36,22 @@ enum : int {
 //   meta[3] = active local experts
 constexpr int kMetaInts = 8;
 
-// One token tile of one expert: rows [row_start, row_start + n) of the permuted row space.
-struct TokenTile {
-  int expert;
-  int row_start;
-  int n;       // multiple of 16, <= kTokenTile
-  int pad;
+// Per local expert: its rows [row_off, row_off + rows_pad) of the permuted row space
+// (rows_pad is a multiple of 16) cut into `tiles` token tiles of the launch's tile size;
+// tile_off is the number of token tiles of all earlier experts.  A GEMM work item is
+// (expert, feature tile, token tile); items are numbered expert-major, then feature tile,
+// then token tile, so the CTAs that run side by side share a weight tile through L2.
+struct ExpertWork {
+  int row_off;
+  int rows_pad;
+  int tile_off;
+  int tiles;
 };
 
 struct Workspace {
   int device = -1;
   int max_tokens = 0;
   int row_cap = 0;        // capacity of the permuted row space
-  int tile_cap = 0;
   // routing
   int* topk_idx = nullptr;        // [T, 8] global expert ids
   float* topk_w = nullptr;        // [T, 8]
@@ -56,10 +59,11 @@ struct Workspace {
   int* counts = nullptr;          // [32] rows per local expert
   int* meta = nullptr;            // [kMetaInts]
   int* status = nullptr;          // [4]
+  long long* trace = nullptr;     // [2][3][4096] GEMM1 / GEMM2 timeline of CTA 0 (only written by SYFI_TRACE builds)
   // permutation
   int* row_token = nullptr;       // [row_cap] token of each row, -1 for padding
   int* route_row = nullptr;       // [T, 8] row of each (token, k) route, -1 when the expert is not local
-  TokenTile* tiles = nullptr;     // [tile_cap]
+  ExpertWork* work = nullptr;     // [32]
   // operands
   uint8_t* a_perm = nullptr;      // [row_cap, 7168] e4m3 gathered activations
   float* a_scale = nullptr;       // [56, row_cap]
@@ -72,19 +76,21 @@ struct Workspace {
 
 struct GemmLaunch {
   CUtensorMap tm_w;    // weights, 2-D [E * rows_per_expert, K], box 128 x 128
-  CUtensorMap tm_b0;   // token-side operand, box kTokenTile x 128 (GEMM1: a_perm; GEMM2: c_hi)
+  CUtensorMap tm_b0;   // token-side operand, box token_tile x 128 (GEMM1: a_perm; GEMM2: c_hi)
   CUtensorMap tm_b1;   // GEMM2: c_lo (unused by GEMM1)
+  int token_tile;      // 32 or 64: token rows per work item, must match the row-list kernel's
 };
 
 // launchers (each returns the cudaGetLastError() of its launches)
 cudaError_t launch_router(const float* logits, const void* bias_bf16, int T, int e_local, int expert_offset,
                           float scaling, const Workspace& ws, cudaStream_t st);
-cudaError_t launch_build_rows(int T, int e_local, int expert_offset, const Workspace& ws, cudaStream_t st);
+cudaError_t launch_build_rows(int T, int e_local, int expert_offset, int token_tile, const Workspace& ws,
+                              cudaStream_t st);
 cudaError_t launch_gather(const uint8_t* hidden, const float* hidden_scale, int T, const Workspace& ws,
                           cudaStream_t st);
-cudaError_t launch_gemm1(const GemmLaunch& g, const float* w13_scale, const Workspace& ws, int num_sms,
+cudaError_t launch_gemm1(const GemmLaunch& g, const float* w13_scale, int e_local, const Workspace& ws, int num_sms,
                          cudaStream_t st);
-cudaError_t launch_gemm2(const GemmLaunch& g, const float* w2_scale, const Workspace& ws, int num_sms,
+cudaError_t launch_gemm2(const GemmLaunch& g, const float* w2_scale, int e_local, const Workspace& ws, int num_sms,
                          cudaStream_t st);
 cudaError_t launch_combine(int T, const Workspace& ws, void* out, int out_is_f32, cudaStream_t st);
 cudaError_t gemm_set_attributes();

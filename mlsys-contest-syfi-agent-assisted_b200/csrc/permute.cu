@@ -21,8 +21,8 @@ constexpr int kBuildThreads = 256;
 __global__ void __launch_bounds__(kBuildThreads)
 build_rows_kernel(int T, int e_local, int expert_offset, const uint32_t* __restrict__ local_mask,
                   const int* __restrict__ counts, const int* __restrict__ topk_idx, int* __restrict__ row_token,
-                  int* __restrict__ route_row, TokenTile* __restrict__ tiles, int* __restrict__ meta, int row_cap,
-                  int tile_cap, int* __restrict__ status) {
+                  int* __restrict__ route_row, ExpertWork* __restrict__ work, int* __restrict__ meta, int row_cap,
+                  int token_tile, int* __restrict__ status) {
   __shared__ int s_warp[kBuildThreads / 32];
   const int e = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -31,13 +31,13 @@ build_rows_kernel(int T, int e_local, int expert_offset, const uint32_t* __restr
   for (int i = 0; i < e_local; ++i) {
     const int c = counts[i];
     const int cp = (c + kRowPad - 1) / kRowPad * kRowPad;
-    const int nt = (cp + kTokenTile - 1) / kTokenTile;
+    const int nt = (cp + token_tile - 1) / token_tile;
     if (i < e) { row_off += cp; tile_off += nt; }
     if (i == e) cnt = c;
     rows_total += cp; tiles_total += nt; routed += c; active += (c > 0);
   }
   const int cnt_pad = (cnt + kRowPad - 1) / kRowPad * kRowPad;
-  if (rows_total > row_cap || tiles_total > tile_cap) {  // sizing bug: refuse to write out of bounds
+  if (rows_total > row_cap) {  // sizing bug: refuse to write out of bounds
     if (tid == 0) { atomicExch(status, kStatusBadIndex); if (e == 0) { meta[0] = 0; meta[1] = 0; meta[2] = 0; meta[3] = 0; } }
     return;
   }
@@ -68,14 +68,13 @@ build_rows_kernel(int T, int e_local, int expert_offset, const uint32_t* __restr
     __syncthreads();
   }
   for (int r = cnt + tid; r < cnt_pad; r += kBuildThreads) row_token[row_off + r] = -1;
-  const int nt_e = (cnt_pad + kTokenTile - 1) / kTokenTile;
-  for (int i = tid; i < nt_e; i += kBuildThreads) {
-    TokenTile tt;
-    tt.expert = e;
-    tt.row_start = row_off + i * kTokenTile;
-    tt.n = min(kTokenTile, cnt_pad - i * kTokenTile);
-    tt.pad = 0;
-    tiles[tile_off + i] = tt;
+  if (tid == 0) {
+    ExpertWork ew;
+    ew.row_off = row_off;
+    ew.rows_pad = cnt_pad;
+    ew.tile_off = tile_off;
+    ew.tiles = (cnt_pad + token_tile - 1) / token_tile;
+    work[e] = ew;
   }
   if (e == 0 && tid == 0) {
     meta[0] = tiles_total; meta[1] = rows_total; meta[2] = routed; meta[3] = active;
@@ -110,10 +109,11 @@ gather_rows_kernel(const uint8_t* __restrict__ hidden, const float* __restrict__
 
 }  // namespace
 
-cudaError_t launch_build_rows(int T, int e_local, int expert_offset, const Workspace& ws, cudaStream_t st) {
+cudaError_t launch_build_rows(int T, int e_local, int expert_offset, int token_tile, const Workspace& ws,
+                              cudaStream_t st) {
   build_rows_kernel<<<e_local, kBuildThreads, 0, st>>>(T, e_local, expert_offset, ws.local_mask, ws.counts,
-                                                       ws.topk_idx, ws.row_token, ws.route_row, ws.tiles, ws.meta,
-                                                       ws.row_cap, ws.tile_cap, ws.status);
+                                                       ws.topk_idx, ws.row_token, ws.route_row, ws.work, ws.meta,
+                                                       ws.row_cap, token_tile, ws.status);
   return cudaGetLastError();
 }
 

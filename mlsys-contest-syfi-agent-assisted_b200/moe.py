@@ -62,7 +62,9 @@ def load_library():
     global _lib
     with _lib_lock:
         if _lib is None:
-            path = _build.build_library() if _build.needs_build() else _build.LIB
+            # SYFI_MOE_LIBRARY points at an alternative build of the same sources (e.g. a tracing build)
+            path = os.environ.get("SYFI_MOE_LIBRARY") or (
+                _build.build_library() if _build.needs_build() else _build.LIB)
             lib = ctypes.CDLL(path)
             for name, (res, args) in ABI.items():
                 fn = getattr(lib, name)

@@ -58,7 +58,6 @@ def test_row_lists(T, E, off, pkg):
     row_token, cap = ctx.debug_read("row_token", torch.int32)
     route_row, _ = ctx.debug_read("route_row", torch.int32)
     counts, _ = ctx.debug_read("counts", torch.int32)
-    tiles, _ = ctx.debug_read("tiles", torch.int32)
     route_row = route_row[: T * 8].view(T, 8)
     local = (idx >= off) & (idx < off + E)
     assert stats["routes"] == int(local.sum())
@@ -79,16 +78,17 @@ def test_row_lists(T, E, off, pkg):
     assert bool((route_row[~local] == -1).all())
     rows = route_row[local].long()
     assert torch.equal(row_token[rows].long(), torch.nonzero(local)[:, 0])
-    # tile table covers the padded rows exactly once, tiles never straddle experts
-    nt = stats["token_tiles"]
-    tl = tiles[: nt * 4].view(nt, 4)
-    covered = torch.zeros(int(pad.sum()), dtype=torch.int32)
+    # per-expert work table: row ranges tile the padded row space, token tiles are counted consistently
+    work, _ = ctx.debug_read("expert_work", torch.int32)
+    work = work.view(32, 4)[:E]
+    tile = 32 if T <= 256 else 64
     bounds = torch.cumsum(torch.cat([torch.zeros(1, dtype=torch.long), pad]), 0)
-    for e, rs, n, _ in tl.tolist():
-        assert n % 16 == 0 and 16 <= n <= 64
-        assert bounds[e] <= rs and rs + n <= bounds[e + 1]
-        covered[rs:rs + n] += 1
-    assert bool((covered == 1).all())
+    tile_off = 0
+    for e, (row_off, rows_pad, t_off, tiles) in enumerate(work.tolist()):
+        assert row_off == int(bounds[e]) and rows_pad == int(pad[e])
+        assert tiles == (rows_pad + tile - 1) // tile and t_off == tile_off
+        tile_off += tiles
+    assert stats["token_tiles"] == tile_off
 
 
 # ------------------------------------------------------------ whole layer
