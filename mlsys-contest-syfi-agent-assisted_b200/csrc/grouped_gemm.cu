@@ -54,15 +54,22 @@ template <int MODE, int NT> struct Cfg {
   static constexpr int kFeatTiles = MODE == 1 ? kInter / 128 : kHidden / 128;   // 16 / 56
   static constexpr int kRowsPerExpert = MODE == 1 ? 2 * kInter : kHidden;       // weight rows per expert
   static constexpr int kBTile = NT * 128;                                       // token-side tile bytes
-  static constexpr int kStageBytes = MODE == 1 ? 2 * kATile + kBTile : kATile + 2 * kBTile;
-  static constexpr int kStages = MODE == 1 ? 5 : (NT == 32 ? 8 : 6);
+  static constexpr int kStageBytes = MODE == 1 ? 2 * kATile + kBTile : kATile + 2 * kBTile;  // one K block
+  // K blocks per pipeline step.  One thread issues every MMA (about 50 cycles each) and every
+  // tcgen05.commit (about 90 cycles), so with small N the issue loop, not the tensor pipe, sets
+  // the pace; handing over two K blocks per barrier round halves the waits and commits per byte.
+  static constexpr int kKps = NT == 32 ? 2 : 1;
+  static constexpr int kGroups = MODE == 1 ? (NT == 32 ? 3 : 5) : (NT == 32 ? 4 : 6);   // smem ring depth
+  static constexpr int kGroupBytes = kKps * kStageBytes;
   static constexpr int kSlots = kTmemCols / (2 * NT);                           // accumulator-pair slots
+  static constexpr int kPairs = kSlots / kKps;                                  // slot groups signalled together
   static constexpr int kScaleBufs = MODE == 2 ? 2 : 1;   // mode 2 prefetches the next item's scales
-  static constexpr int kSmemBytes = 1024 /* alignment slack */ + kStages * kStageBytes +
+  static constexpr int kSmemBytes = 1024 /* alignment slack */ + kGroups * kGroupBytes +
                                     4 * (kScaleBufs * (kKBlocks * NT + 128) + 4 * NT + 2 * NT) +
-                                    8 * (2 * kStages + 2 * kSlots) +
+                                    8 * (2 * kGroups + 2 * kPairs) +
                                     kMaxLocalExperts * static_cast<int>(sizeof(ExpertWork)) + 16;
   static_assert(kSmemBytes <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
+  static_assert(kKBlocks % kKps == 0 && kSlots % kKps == 0, "steps must tile the K blocks and the slots");
 };
 
 struct GemmArgs {
@@ -123,24 +130,26 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_b0,
                     const __grid_constant__ CUtensorMap tm_b1, const GemmArgs p) {
   using C = Cfg<MODE, NT>;
-  constexpr int S = C::kStages;
+  constexpr int G = C::kGroups;           // smem ring entries, each kKps K blocks
+  constexpr int KPS = C::kKps;
   constexpr int KB = C::kKBlocks;
+  constexpr int STEPS = KB / KPS;
   constexpr int FT = C::kFeatTiles;
-  constexpr int SLOTS = C::kSlots;
+  constexpr int PAIRS = C::kPairs;        // TMEM ring entries, each kKps accumulator-pair slots
   constexpr int kBTile = C::kBTile;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   constexpr int kScaleStride = KB * NT + 128;                           // one buffer: [KB][NT] + [2][64]
-  float* s_scales = reinterpret_cast<float*>(smem + S * C::kStageBytes);
+  float* s_scales = reinterpret_cast<float*>(smem + G * C::kGroupBytes);
   float* s_red = s_scales + C::kScaleBufs * kScaleStride;               // [4][NT]
   float* s_cs = s_red + 4 * NT;                                         // [NT] scale
   float* s_inv = s_cs + NT;                                             // [NT] 1 / scale
   uint64_t* full = reinterpret_cast<uint64_t*>(s_inv + NT);
-  uint64_t* empty = full + S;
-  uint64_t* tfull = empty + S;
-  uint64_t* tempty = tfull + SLOTS;
-  ExpertWork* s_work = reinterpret_cast<ExpertWork*>(tempty + SLOTS);
+  uint64_t* empty = full + G;
+  uint64_t* tfull = empty + G;
+  uint64_t* tempty = tfull + PAIRS;
+  ExpertWork* s_work = reinterpret_cast<ExpertWork*>(tempty + PAIRS);
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_work + kMaxLocalExperts);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
 
@@ -149,8 +158,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   (void)trace_n;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < S; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
-    for (int i = 0; i < SLOTS; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 4); }
+    for (int i = 0; i < G; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+    for (int i = 0; i < PAIRS; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 4); }
     *s_abort = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tm_w);
@@ -172,64 +181,63 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   const int total = p.meta[0] * FT;
 
   if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
-    const uint64_t pol_w = l2_policy_evict_first();
-    const uint64_t pol_b = l2_policy_evict_last();
-    uint32_t it = 0;
-    for (int w = blockIdx.x; w < total; w += gridDim.x) {
-      const Item im = decode_item<FT, NT>(s_work, p.e_local, w);
-      const int wrow = im.expert * C::kRowsPerExpert + im.ft * 128;
-      for (int kb = 0; kb < KB; ++kb) {
-        if (lane == 0) {
-          const int s = it % S;
-          if (mbar_wait_bounded(&empty[s], ((it / S) & 1) ^ 1, s_abort, kStatusWaitTimeoutProducer)) {
-            uint8_t* st = smem + s * C::kStageBytes;
-            TRACE(0, kb);
-            mbar_arrive_expect_tx(&full[s], C::kStageBytes);
-            if (MODE == 1) {
-              tma_load_2d(st, &tm_w, &full[s], kb * 128, wrow, pol_w);
-              tma_load_2d(st + kATile, &tm_w, &full[s], kb * 128, wrow + kInter, pol_w);
-              tma_load_2d(st + 2 * kATile, &tm_b0, &full[s], kb * 128, im.row_start, pol_b);
-            } else {
-              tma_load_2d(st, &tm_w, &full[s], kb * 128, wrow, pol_w);
-              tma_load_2d(st + kATile, &tm_b0, &full[s], kb * 128, im.row_start, pol_b);
-              tma_load_2d(st + kATile + kBTile, &tm_b1, &full[s], kb * 128, im.row_start, pol_b);
-            }
-            ++it;
-          }
-        }
-        __syncwarp();
-        if (*s_abort) break;
-      }
-      if (*s_abort) break;
-    }
-    // drain: every stage this warp armed must have landed before the CTA may exit
+    // ------------------------------------------------------------ TMA producer (one thread)
     if (lane == 0) {
-      const uint32_t first = it > static_cast<uint32_t>(S) ? it - S : 0;
+      const uint64_t pol_w = l2_policy_evict_first();
+      const uint64_t pol_b = l2_policy_evict_last();
+      uint32_t it = 0, g = 0, ph = 0;      // step counter, ring entry, its phase
+      bool alive = true;
+      for (int w = blockIdx.x; w < total && alive; w += gridDim.x) {
+        const Item im = decode_item<FT, NT>(s_work, p.e_local, w);
+        const int wrow = im.expert * C::kRowsPerExpert + im.ft * 128;
+        for (int step = 0; step < STEPS; ++step) {
+          if (!mbar_wait_bounded(&empty[g], ph ^ 1u, s_abort, kStatusWaitTimeoutProducer)) { alive = false; break; }
+          TRACE(0, step);
+          mbar_arrive_expect_tx(&full[g], C::kGroupBytes);
+#pragma unroll
+          for (int k = 0; k < KPS; ++k) {
+            uint8_t* st = smem + g * C::kGroupBytes + k * C::kStageBytes;
+            const int x = (step * KPS + k) * 128;
+            if (MODE == 1) {
+              tma_load_2d(st, &tm_w, &full[g], x, wrow, pol_w);
+              tma_load_2d(st + kATile, &tm_w, &full[g], x, wrow + kInter, pol_w);
+              tma_load_2d(st + 2 * kATile, &tm_b0, &full[g], x, im.row_start, pol_b);
+            } else {
+              tma_load_2d(st, &tm_w, &full[g], x, wrow, pol_w);
+              tma_load_2d(st + kATile, &tm_b0, &full[g], x, im.row_start, pol_b);
+              tma_load_2d(st + kATile + kBTile, &tm_b1, &full[g], x, im.row_start, pol_b);
+            }
+          }
+          ++it;
+          if (++g == G) { g = 0; ph ^= 1u; }
+        }
+      }
+      // drain: every ring entry this thread armed must have landed before the CTA may exit
+      const uint32_t first = it > static_cast<uint32_t>(G) ? it - G : 0;
       for (uint32_t i = first; i < it; ++i)
-        mbar_wait_bounded(&full[i % S], (i / S) & 1, s_abort, kStatusWaitTimeoutProducer, 1ll << 28);
+        mbar_wait_bounded(&full[i % G], (i / G) & 1, s_abort, kStatusWaitTimeoutProducer, 1ll << 28);
     }
     __syncwarp();
   } else if (warp == 1) {
-    // --------------------------------------------------------------- MMA issuer
-    uint32_t it = 0;
-    for (int w = blockIdx.x; w < total; w += gridDim.x) {
-      const Item im = decode_item<FT, NT>(s_work, p.e_local, w);
-      // An MMA of M = 128 occupies the tensor pipe for the same time whatever its N, so mode 2
-      // issues ONE MMA of N = 2 NT per 32 bytes of K over the adjacent hi and lo tiles (the
-      // columns past the tile's n rows hold other rows' data and are never read back) instead
-      // of one per term; mode 1 needs two because up and gate are different A tiles.
-      const uint32_t idesc = umma_idesc_e4m3_m128(MODE == 1 ? static_cast<uint32_t>(im.n) : 2u * NT);
-      for (int kb = 0; kb < KB; ++kb) {
-        if (lane == 0) {
-          const int s = it % S;
-          const uint32_t slot = it % SLOTS;
-          if (mbar_wait_bounded(&full[s], (it / S) & 1, s_abort, kStatusWaitTimeoutMma) &&
-              mbar_wait_bounded(&tempty[slot], ((it / SLOTS) & 1u) ^ 1u, s_abort, kStatusWaitTimeoutMma)) {
-            tc_fence_after();
-            TRACE(1, kb);
-            const uint32_t st = smem_u32(smem + s * C::kStageBytes);
-            const uint32_t d0 = tmem_base + slot * (2 * NT);
+    // --------------------------------------------------------------- MMA issuer (one thread)
+    if (lane == 0) {
+      uint32_t g = 0, ph = 0, pr = 0, pph = 0;   // smem ring entry / phase, TMEM ring entry / phase
+      bool alive = true;
+      for (int w = blockIdx.x; w < total && alive; w += gridDim.x) {
+        const Item im = decode_item<FT, NT>(s_work, p.e_local, w);
+        // Mode 2 issues ONE MMA of N = 2 NT per 32 bytes of K over the adjacent hi and lo tiles
+        // (the columns past the tile's n rows hold other rows' data and are never read back)
+        // instead of one per term; mode 1 needs two because up and gate are different A tiles.
+        const uint32_t idesc = umma_idesc_e4m3_m128(MODE == 1 ? static_cast<uint32_t>(im.n) : 2u * NT);
+        for (int step = 0; step < STEPS; ++step) {
+          if (!mbar_wait_bounded(&full[g], ph, s_abort, kStatusWaitTimeoutMma) ||
+              !mbar_wait_bounded(&tempty[pr], pph ^ 1u, s_abort, kStatusWaitTimeoutMma)) { alive = false; break; }
+          tc_fence_after();
+          TRACE(1, step);
+#pragma unroll
+          for (int k = 0; k < KPS; ++k) {
+            const uint32_t st = smem_u32(smem + g * C::kGroupBytes + k * C::kStageBytes);
+            const uint32_t d0 = tmem_base + (pr * KPS + k) * (2 * NT);
             if (MODE == 1) {
               const uint64_t a0 = umma_smem_desc_sw128(st);
               const uint64_t a1 = umma_smem_desc_sw128(st + kATile);
@@ -246,23 +254,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 #pragma unroll
               for (int k4 = 0; k4 < 4; ++k4) umma_f8(d0, a0 + 2 * k4, b0 + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
             }
-            umma_commit(&empty[s]);
-            umma_commit(&tfull[slot]);
-            ++it;
           }
+          umma_commit(&empty[g]);
+          umma_commit(&tfull[pr]);
+          if (++g == G) { g = 0; ph ^= 1u; }
+          if (++pr == PAIRS) { pr = 0; pph ^= 1u; }
         }
-        __syncwarp();
-        if (*s_abort) break;
       }
-      if (*s_abort) break;
     }
+    __syncwarp();
   } else {
     // ------------------------------------------------ promotion + epilogue warps
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     const int feat = q * 32 + lane;         // feature (row of the weight tile) of this thread
     const int et = threadIdx.x - 64;        // 0..127 among the epilogue threads
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-    uint32_t it = 0;
+    uint32_t pr = 0, pph = 0;               // TMEM ring entry and its phase
     bool ok = true;
     int sbuf = 0;
     if (MODE == 2 && static_cast<int>(blockIdx.x) < total) {
@@ -331,39 +338,42 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         for (int j = 0; j < NT; ++j) acc1[j] = 0.0f;
       }
 
-      for (int kb = 0; kb < KB && ok; ++kb, ++it) {
-        const uint32_t slot = it % SLOTS;
-        if (!mbar_wait_bounded(&tfull[slot], (it / SLOTS) & 1u, s_abort, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
+      for (int step = 0; step < STEPS && ok; ++step) {
+        if (!mbar_wait_bounded(&tfull[pr], pph, s_abort, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
         tc_fence_after();
-        if (et == 0) TRACE(2, kb);
-        const uint32_t t0 = lane_addr + slot * (2 * NT);
-        const float ws0 = s_ws[kb];
-        const float ws1 = (MODE == 1) ? s_ws[64 + kb] : 0.0f;
-        const float* sa = s_act + kb * NT;
+        if (et == 0) TRACE(2, step);
 #pragma unroll
-        for (int h = 0; h < NT / 32; ++h) {   // 32 columns at a time: four loads in flight, one wait
-          if (h * 32 < n) {
-            uint32_t v0[2][16], v1[2][16];
-            tmem_ld16(t0 + h * 32, v0[0]);
-            tmem_ld16(t0 + NT + h * 32, v1[0]);
-            if (h * 32 + 16 < n) {
-              tmem_ld16(t0 + h * 32 + 16, v0[1]);
-              tmem_ld16(t0 + NT + h * 32 + 16, v1[1]);
-            }
-            tmem_ld_wait();
+        for (int k = 0; k < KPS; ++k) {
+          const int kb = step * KPS + k;
+          const uint32_t t0 = lane_addr + (pr * KPS + k) * (2 * NT);
+          const float ws0 = s_ws[kb];
+          const float ws1 = (MODE == 1) ? s_ws[64 + kb] : 0.0f;
+          const float* sa = s_act + kb * NT;
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-              if (h * 32 + c * 16 < n) {
+          for (int h = 0; h < NT / 32; ++h) {   // 32 columns at a time: four loads in flight, one wait
+            if (h * 32 < n) {
+              uint32_t v0[2][16], v1[2][16];
+              tmem_ld16(t0 + h * 32, v0[0]);
+              tmem_ld16(t0 + NT + h * 32, v1[0]);
+              if (h * 32 + 16 < n) {
+                tmem_ld16(t0 + h * 32 + 16, v0[1]);
+                tmem_ld16(t0 + NT + h * 32 + 16, v1[1]);
+              }
+              tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                  const int col = h * 32 + c * 16 + j;
-                  const float a = sa[col];
-                  if (MODE == 1) {
-                    acc0[col] = fmaf(__uint_as_float(v0[c][j]), a * ws0, acc0[col]);
-                    acc1[col] = fmaf(__uint_as_float(v1[c][j]), a * ws1, acc1[col]);
-                  } else {
-                    const float v = fmaf(__uint_as_float(v1[c][j]), 1.0f / kLoRatio, __uint_as_float(v0[c][j]));
-                    acc0[col] = fmaf(v, a * ws0, acc0[col]);
+              for (int c = 0; c < 2; ++c) {
+                if (h * 32 + c * 16 < n) {
+#pragma unroll
+                  for (int j = 0; j < 16; ++j) {
+                    const int col = h * 32 + c * 16 + j;
+                    const float a = sa[col];
+                    if (MODE == 1) {
+                      acc0[col] = fmaf(__uint_as_float(v0[c][j]), a * ws0, acc0[col]);
+                      acc1[col] = fmaf(__uint_as_float(v1[c][j]), a * ws1, acc1[col]);
+                    } else {
+                      const float v = fmaf(__uint_as_float(v1[c][j]), 1.0f / kLoRatio, __uint_as_float(v0[c][j]));
+                      acc0[col] = fmaf(v, a * ws0, acc0[col]);
+                    }
                   }
                 }
               }
@@ -372,7 +382,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&tempty[slot]);
+        if (lane == 0) mbar_arrive(&tempty[pr]);
+        if (++pr == PAIRS) { pr = 0; pph ^= 1u; }
       }
       const int n_out = ok ? n : 0;           // a failed item stores nothing
       if (et == 0) TRACE(2, 1002);
