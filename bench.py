@@ -220,25 +220,12 @@ def main():
             pkg.run_moe(*inp.args(), out)
         n_tok_layer = T
     else:
-        NT = T * world
-        g_logits = torch.empty(NT, 256, dtype=torch.float32, device=dev)
-        g_hs = torch.empty(NT, H, dtype=torch.uint8, device=dev)
-        g_sc = torch.empty(world, H // 128, T, dtype=torch.float32, device=dev)
-        part = torch.empty(NT, H, dtype=torch.float32, device=dev)
-        mine = torch.empty(T, H, dtype=torch.float32, device=dev)
-        hs_u8 = inp.hidden_states.view(torch.uint8)
+        ep = pkg.ExpertParallelMoe(inp.gemm1_weights, inp.gemm1_weights_scale, inp.gemm2_weights,
+                                   inp.gemm2_weights_scale, inp.local_expert_offset, inp.routed_scaling_factor)
 
         def step():
-            dist.all_gather_into_tensor(g_logits, inp.routing_logits)
-            dist.all_gather_into_tensor(g_hs, hs_u8)
-            dist.all_gather_into_tensor(g_sc, inp.hidden_states_scale)
-            sc = g_sc.permute(1, 0, 2).reshape(H // 128, NT).contiguous()
-            pkg.run_moe(g_logits, inp.routing_bias, g_hs.view(torch.float8_e4m3fn), sc, inp.gemm1_weights,
-                        inp.gemm1_weights_scale, inp.gemm2_weights, inp.gemm2_weights_scale,
-                        inp.local_expert_offset, inp.routed_scaling_factor, part)
-            dist.reduce_scatter_tensor(mine, part)
-            out.copy_(mine)
-        n_tok_layer = NT
+            ep.forward_sharded(inp.routing_logits, inp.routing_bias, inp.hidden_states, inp.hidden_states_scale, out)
+        n_tok_layer = T * world
 
     def barrier():
         if dist is not None:

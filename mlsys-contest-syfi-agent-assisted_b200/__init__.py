@@ -6,7 +6,8 @@ generator in :mod:`workloads`.
 """
 from .moe import (ABI, MoeContext, MoeError, get_context, library_path, load_library, release_contexts, route,
                   run_moe, run_moe_host)
+from .parallel import ExpertParallelMoe, expert_slice
 from .workloads import MoeInputs, algorithmic_work, make_inputs
 
-__all__ = ["ABI", "MoeContext", "MoeError", "MoeInputs", "algorithmic_work", "get_context", "library_path",
+__all__ = ["ABI", "ExpertParallelMoe", "expert_slice", "MoeContext", "MoeError", "MoeInputs", "algorithmic_work", "get_context", "library_path",
            "load_library", "make_inputs", "release_contexts", "route", "run_moe", "run_moe_host"]

@@ -1,0 +1,125 @@
+"""Expert parallelism over ``torch.distributed`` (one process per GPU, NCCL over NVLink).
+
+The reference has no multi-GPU code; its only hook is ``local_expert_offset``
+(moe/solution/cuda/moe.cu:182-185, 250-256): a call computes the contribution of
+experts [offset, offset + E_local) and nothing else.  The layer therefore shards by
+expert with one exchange step, the sum of the ranks' partial outputs:
+
+* ``forward_replicated`` — every rank holds the same T tokens (the large-prefill
+  configuration): each rank computes an f32 partial [T, 7168] for its experts, the
+  partials are all-reduced (or reduce-scattered by rows) and rounded to bf16 once.
+* ``forward_sharded`` — every rank brings its own T tokens (the serving layout:
+  data-parallel attention, expert-parallel MoE): token-side tensors are all-gathered,
+  each rank runs its experts over the W*T gathered tokens, and a reduce-scatter returns
+  to each rank the summed rows of its own tokens.
+
+``layer_fn`` computes one rank's f32 partial and defaults to the CUDA operator; tests of
+the plumbing on CPU ranks (gloo) pass a stand-in.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+def _reduce_scatter_rows(out, inp, group):
+    """Sum ``inp`` [W*R, H] over ranks and leave this rank's R rows in ``out``.  NCCL does it in one
+    collective; backends without reduce-scatter (gloo, used by the CPU tests) all-reduce and slice."""
+    if dist.get_backend(group) == "nccl":
+        dist.reduce_scatter_tensor(out, inp, group=group)
+        return
+    dist.all_reduce(inp, group=group)
+    r = dist.get_rank(group)
+    out.copy_(inp[r * out.shape[0]:(r + 1) * out.shape[0]])
+
+
+def expert_slice(rank: int, world: int, num_experts: int = 32, base_offset: int = 0):
+    """Contiguous slice of ``num_experts`` owned by ``rank``: (global offset, count).
+    ``num_experts`` must divide evenly (32 experts over 2/4/8 ranks -> 16/8/4 each)."""
+    if world < 1 or not (0 <= rank < world):
+        raise ValueError(f"rank {rank} outside world of {world}")
+    if num_experts % world != 0:
+        raise ValueError(f"{num_experts} experts do not split evenly over {world} ranks")
+    per = num_experts // world
+    return base_offset + rank * per, per
+
+
+def _cuda_layer(logits, bias, hs, hs_scale, w13, w13_s, w2, w2_s, offset, scaling, out_f32):
+    from .moe import run_moe
+    return run_moe(logits, bias, hs, hs_scale, w13, w13_s, w2, w2_s, offset, scaling, out_f32)
+
+
+class ExpertParallelMoe:
+    """One rank's experts plus the collectives that combine the ranks."""
+
+    def __init__(self, gemm1_weights, gemm1_weights_scale, gemm2_weights, gemm2_weights_scale,
+                 local_expert_offset: int, routed_scaling_factor: float, group=None, layer_fn=None):
+        self.w13, self.w13_s = gemm1_weights, gemm1_weights_scale
+        self.w2, self.w2_s = gemm2_weights, gemm2_weights_scale
+        self.offset = int(local_expert_offset)
+        self.scaling = float(routed_scaling_factor)
+        self.group = group
+        self.layer_fn = layer_fn or _cuda_layer
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self._buf = {}
+
+    def _buffer(self, name, shape, dtype, device):
+        key = (name, tuple(shape), dtype, str(device))
+        b = self._buf.get(key)
+        if b is None:
+            b = torch.empty(shape, dtype=dtype, device=device)
+            self._buf[key] = b
+        return b
+
+    def partial(self, logits, bias, hs, hs_scale, out_f32=None):
+        """This rank's un-rounded contribution, f32 [T, 7168]."""
+        T, H = hs.shape
+        if out_f32 is None:
+            out_f32 = self._buffer("partial", (T, H), torch.float32, logits.device)
+        self.layer_fn(logits, bias, hs, hs_scale, self.w13, self.w13_s, self.w2, self.w2_s, self.offset,
+                      self.scaling, out_f32)
+        return out_f32
+
+    def forward_replicated(self, logits, bias, hs, hs_scale, out_bf16=None, scatter_rows: bool = False):
+        """Tokens replicated on every rank.  Returns bf16 [T, 7168] on every rank, or with
+        ``scatter_rows`` this rank's T/W rows of it (T must divide by the world size)."""
+        T = logits.shape[0]
+        part = self.partial(logits, bias, hs, hs_scale)
+        if self.world == 1:
+            res = part
+        elif scatter_rows:
+            if T % self.world != 0:
+                raise ValueError(f"{T} tokens do not split evenly over {self.world} ranks")
+            res = self._buffer("rows", (T // self.world, part.shape[1]), torch.float32, part.device)
+            _reduce_scatter_rows(res, part, self.group)
+        else:
+            dist.all_reduce(part, group=self.group)
+            res = part
+        if out_bf16 is None:
+            return res.to(torch.bfloat16)
+        out_bf16.copy_(res)
+        return out_bf16
+
+    def forward_sharded(self, logits, bias, hs, hs_scale, out_bf16=None):
+        """Each rank passes its OWN T tokens (same T on every rank); returns their bf16 outputs
+        summed over all ranks' experts."""
+        T = logits.shape[0]
+        W = self.world
+        if W == 1:
+            return self.forward_replicated(logits, bias, hs, hs_scale, out_bf16)
+        dev = logits.device
+        g_logits = self._buffer("g_logits", (W * T, logits.shape[1]), logits.dtype, dev)
+        g_hs = self._buffer("g_hs", (W * T, hs.shape[1]), torch.uint8, dev)
+        g_sc = self._buffer("g_sc", (W * hs_scale.shape[0], T), hs_scale.dtype, dev)
+        dist.all_gather_into_tensor(g_logits, logits.contiguous(), group=self.group)
+        dist.all_gather_into_tensor(g_hs, hs.view(torch.uint8).contiguous(), group=self.group)
+        dist.all_gather_into_tensor(g_sc, hs_scale.contiguous(), group=self.group)
+        # scales are stored [K/128, tokens]: put the gathered ranks side by side along the token axis
+        sc = g_sc.view(W, hs_scale.shape[0], T).permute(1, 0, 2).reshape(hs_scale.shape[0], W * T).contiguous()
+        part = self.partial(g_logits, bias, g_hs.view(hs.dtype), sc)
+        mine = self._buffer("mine", (T, part.shape[1]), torch.float32, dev)
+        _reduce_scatter_rows(mine, part, self.group)
+        if out_bf16 is None:
+            return mine.to(torch.bfloat16)
+        out_bf16.copy_(mine)
+        return out_bf16

@@ -1,0 +1,77 @@
+"""Expert parallelism with the CUDA operator over NCCL (needs at least two GPUs; skipped otherwise)."""
+import importlib
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PKG = "mlsys-contest-syfi-agent-assisted_b200"
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        pkg = importlib.import_module(PKG)
+        oracle = importlib.import_module("oracle.moe_oracle")
+        # config-3 style: one 32-expert layer (seed 0) sharded over the ranks, tokens replicated
+        full = pkg.make_inputs(num_tokens=256, seed=0, e_local=32, device="cpu")
+        off, per = pkg.expert_slice(rank, world, 32)
+        ep = pkg.ExpertParallelMoe(full.gemm1_weights[off:off + per].to(dev), full.gemm1_weights_scale[off:off + per].to(dev),
+                                   full.gemm2_weights[off:off + per].to(dev), full.gemm2_weights_scale[off:off + per].to(dev),
+                                   off, 2.5)
+        tok = [t.to(dev) for t in (full.routing_logits, full.routing_bias, full.hidden_states, full.hidden_states_scale)]
+        out = ep.forward_replicated(*tok)
+        rows = ep.forward_replicated(*tok, scatter_rows=True)
+        pkg.get_context(rank).check()
+        ref, _, _ = oracle.moe_forward(*full.to(dev).args())
+        ok1, s1 = oracle.check_output(out, ref)
+        r = 256 // world
+        ok2, s2 = oracle.check_output(rows, ref[rank * r:(rank + 1) * r])
+        # serving layout: own tokens per rank
+        mine = pkg.make_inputs(num_tokens=32, seed=20 + rank, e_local=1, device="cpu")
+        o3 = ep.forward_sharded(mine.routing_logits.to(dev), tok[1], mine.hidden_states.to(dev),
+                                mine.hidden_states_scale.to(dev))
+        pkg.get_context(rank).check()
+        fd = full.to(dev)
+        ref3, _, _ = oracle.moe_forward(mine.routing_logits.to(dev), tok[1], mine.hidden_states.to(dev),
+                                        mine.hidden_states_scale.to(dev), fd.gemm1_weights, fd.gemm1_weights_scale,
+                                        fd.gemm2_weights, fd.gemm2_weights_scale, 0, 2.5)
+        ok3, s3 = oracle.check_output(o3, ref3)
+        q.put((rank, ok1 and ok2 and ok3, (s1, s2, s3)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_expert_parallel_two_gpus():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    env = {"NCCL_NVLS_ENABLE": "0"}
+    os.environ.update(env)
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=600) for _ in procs]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert all(ok for _, ok, _ in results), results
