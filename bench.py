@@ -274,7 +274,7 @@ def main():
     achieved = gemm1_bytes / (stage_ms["gemm1"] * 1e-3) / 1e9
     roofline = {"kernel": "grouped_gemm_kernel<1> (GEMM1 + SwiGLU + requantisation)", "bound": "hbm",
                 "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": GEMM1_NCU_TRAFFIC_BYTES, "algorithmic_bytes": gemm1_bytes,
+                "traffic": (GEMM1_NCU_TRAFFIC_BYTES if (world == 1 and T == 64) else None), "algorithmic_bytes": gemm1_bytes,
                 "launch_ms": stage_ms["gemm1"], "peak_source": peak_src, "timed_steps": Ks,
                 "stage_ms": stage_ms}
     flops, layer_bytes = pkg.algorithmic_work(rows, active, n_tok_layer)
