@@ -94,6 +94,22 @@ int syfi_moe_route(syfi_moe_ctx* ctx, const void* routing_logits, const void* ro
                    int32_t num_local_experts, int64_t local_expert_offset, double routed_scaling_factor,
                    int32_t* topk_idx, float* topk_weights, void* stream);
 
+/* Router for callers that cannot allocate device memory (no counterpart in the reference, which
+ * allocates its workspace with cudaMalloc on first use, moe.cu:2863-2926).  Same result as
+ * syfi_moe_route, but it needs no context and calls no cudaMalloc / cudaFree or any other allocating
+ * routine: the scratch it needs sits in a fixed array inside the library image (about 145 KB of device
+ * memory on every GPU that loads the library, held until the process exits), which limits a call to
+ * SYFI_MOE_NOALLOC_MAX_TOKENS tokens; larger batches are rejected with SYFI_MOE_ERR_INVALID.
+ * It works on the CURRENT device.  The first call on a device looks up the array's device address
+ * (one cudaGetSymbolAddress); make that first call before any stream capture begins.  All calls on a
+ * device share the array, so calls that overlap on the GPU (different streams, no dependency) race;
+ * keep them on one stream or order them with events.  Outputs are caller-supplied DEVICE buffers:
+ * topk_idx int32 [T, 8], topk_weights f32 [T, 8]. */
+#define SYFI_MOE_NOALLOC_MAX_TOKENS 4096
+int syfi_moe_route_noalloc(const void* routing_logits, const void* routing_bias, int64_t num_tokens,
+                           int32_t num_local_experts, int64_t local_expert_offset, double routed_scaling_factor,
+                           int32_t* topk_idx, float* topk_weights, void* stream);
+
 /* Copies the routing result of the most recent forward on this context into HOST buffers
  * (either may be null): topk_idx int32 [T, 8], topk_weights f32 [T, 8].  Synchronises `stream`. */
 int syfi_moe_last_routing(syfi_moe_ctx* ctx, int64_t num_tokens, int32_t* topk_idx_host, float* topk_weights_host,

@@ -235,6 +235,13 @@ int forward_common(syfi_moe_ctx* ctx, const void* logits, const void* bias, cons
 
 }  // namespace
 
+namespace syfi {
+int set_last_error(int code, const char* msg) {
+  g_err = msg ? msg : "";
+  return code;
+}
+}  // namespace syfi
+
 extern "C" {
 
 const char* syfi_moe_last_error(void) { return g_err.c_str(); }

@@ -95,4 +95,7 @@ cudaError_t launch_gemm2(const GemmLaunch& g, const float* w2_scale, int e_local
 cudaError_t launch_combine(int T, const Workspace& ws, void* out, int out_is_f32, cudaStream_t st);
 cudaError_t gemm_set_attributes();
 
+// Records `msg` as the calling thread's last error (what syfi_moe_last_error() returns) and returns `code`.
+int set_last_error(int code, const char* msg);
+
 }  // namespace syfi

@@ -13,6 +13,10 @@
 #include <cuda_bf16.h>
 #include <math_constants.h>
 
+#include <cstdio>
+#include <mutex>
+
+#include "../../include/syfi_moe.h"
 #include "moe_internal.h"
 
 namespace syfi {
@@ -143,3 +147,103 @@ cudaError_t launch_router(const float* logits, const void* bias_bf16, int T, int
 }
 
 }  // namespace syfi
+
+// ---------------------------------------------------------------------------------------------
+// Router entry point for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc on the path that runs the router: a serving
+// process whose memory pool owns the whole device, a plugin loaded into a framework that forbids
+// allocation inside its execution callbacks, or code that runs while other threads capture CUDA
+// graphs (an allocation there would invalidate the capture).  For them the router's scratch (the
+// per-token expert mask, the per-route row slots and the per-expert counters that the context-based
+// entry point keeps in its cudaMalloc'ed workspace) lives in a fixed array inside the library image.
+// The array costs kNoAllocScratchBytes of device memory on every GPU that loads the library, until
+// the process exits, and bounds the batch at SYFI_MOE_NOALLOC_MAX_TOKENS tokens per call.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+constexpr int kNoAllocMaxTokens = SYFI_MOE_NOALLOC_MAX_TOKENS;
+constexpr size_t kNoAllocMaskBytes = sizeof(uint32_t) * kNoAllocMaxTokens;               // local_mask
+constexpr size_t kNoAllocRowBytes = sizeof(int) * kNoAllocMaxTokens * syfi::kTopK;       // route_row
+constexpr size_t kNoAllocCountBytes = 256;                                               // counts (32 ints, padded)
+constexpr size_t kNoAllocScratchBytes = kNoAllocMaskBytes + kNoAllocRowBytes + kNoAllocCountBytes;
+
+// In host code this name is only a handle for the runtime, never an address to hand to a kernel:
+// the device address is looked up once per device with cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mu;
+unsigned char* g_noalloc_ptr[kMaxDevices] = {nullptr};
+
+}  // namespace
+
+extern "C" int syfi_moe_route_noalloc(const void* routing_logits, const void* routing_bias, int64_t num_tokens,
+                                      int32_t num_local_experts, int64_t local_expert_offset,
+                                      double routed_scaling_factor, int32_t* topk_idx, float* topk_weights,
+                                      void* stream) {
+  using namespace syfi;
+  char msg[256];
+  if (num_tokens < 0 || num_tokens > kNoAllocMaxTokens) {
+    snprintf(msg, sizeof(msg),
+             "syfi_moe_route_noalloc handles at most %d tokens per call (its scratch is a fixed array); got %lld",
+             kNoAllocMaxTokens, (long long)num_tokens);
+    return set_last_error(SYFI_MOE_ERR_INVALID, msg);
+  }
+  if (num_local_experts < 1 || num_local_experts > kMaxLocalExperts || local_expert_offset < 0 ||
+      local_expert_offset + num_local_experts > kExpertsGlobal)
+    return set_last_error(SYFI_MOE_ERR_INVALID, "local expert range outside [0, 256) or more than 32 experts");
+  if (!(routed_scaling_factor == routed_scaling_factor) || routed_scaling_factor > 3.0e38 ||
+      routed_scaling_factor < -3.0e38)
+    return set_last_error(SYFI_MOE_ERR_INVALID, "routed_scaling_factor is not a finite float");
+  if (num_tokens == 0) return SYFI_MOE_OK;
+  if (!routing_logits || !routing_bias || !topk_idx || !topk_weights)
+    return set_last_error(SYFI_MOE_ERR_INVALID, "null tensor argument");
+  if ((reinterpret_cast<uintptr_t>(routing_logits) | reinterpret_cast<uintptr_t>(routing_bias)) & 15u)
+    return set_last_error(SYFI_MOE_ERR_INVALID, "routing_logits and routing_bias must be 16-byte aligned");
+
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    snprintf(msg, sizeof(msg), "cannot identify the current device: %s", cudaGetErrorString(e));
+    return set_last_error(SYFI_MOE_ERR_CUDA, msg);
+  }
+  unsigned char* base = nullptr;
+  {
+    // Set-up, once per device, with that device current: resolve the device address of the array.
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (g_noalloc_ptr[dev] == nullptr) {
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+      if (e != cudaSuccess || p == nullptr) {
+        snprintf(msg, sizeof(msg), "cudaGetSymbolAddress(scratch) failed on device %d: %s", dev,
+                 cudaGetErrorString(e));
+        return set_last_error(SYFI_MOE_ERR_CUDA, msg);
+      }
+      g_noalloc_ptr[dev] = static_cast<unsigned char*>(p);
+    }
+    base = g_noalloc_ptr[dev];
+  }
+  uint32_t* local_mask = reinterpret_cast<uint32_t*>(base);
+  int* route_row = reinterpret_cast<int*>(base + kNoAllocMaskBytes);
+  int* counts = reinterpret_cast<int*>(base + kNoAllocMaskBytes + kNoAllocRowBytes);
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int T = static_cast<int>(num_tokens);
+  // The array keeps whatever the previous call left; only the counters must start at zero.
+  e = cudaMemsetAsync(counts, 0, sizeof(int) * kMaxLocalExperts, st);
+  if (e == cudaSuccess) {
+    const int blocks = (T + kWarpsPerBlock - 1) / kWarpsPerBlock;
+    route_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>(
+        static_cast<const float*>(routing_logits), static_cast<const __nv_bfloat16*>(routing_bias), T,
+        num_local_experts, static_cast<int>(local_expert_offset), static_cast<float>(routed_scaling_factor),
+        topk_idx, topk_weights, local_mask, route_row, counts);
+    e = cudaGetLastError();
+  }
+  if (e != cudaSuccess) {
+    snprintf(msg, sizeof(msg), "router launch failed: %s", cudaGetErrorString(e));
+    return set_last_error(SYFI_MOE_ERR_CUDA, msg);
+  }
+  return SYFI_MOE_OK;
+}
+

@@ -37,6 +37,7 @@ ABI = {
     "syfi_moe_forward_partial_f32": (ctypes.c_int, [_vp] + [_vp] * 8 + [_i64, _i32, _i64, _f64, _vp, _vp]),
     "syfi_moe_forward_host": (ctypes.c_int, [_vp] + [_vp] * 8 + [_i64, _i32, _i64, _f64, _vp, _vp]),
     "syfi_moe_route": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i32, _i64, _f64, _vp, _vp, _vp]),
+    "syfi_moe_route_noalloc": (ctypes.c_int, [_vp, _vp, _i64, _i32, _i64, _f64, _vp, _vp, _vp]),
     "syfi_moe_last_routing": (ctypes.c_int, [_vp, _i64, _vp, _vp, _vp]),
     "syfi_moe_check": (ctypes.c_int, [_vp, ctypes.POINTER(_i32), _vp]),
     "syfi_moe_debug_read": (ctypes.c_int, [_vp, ctypes.c_char_p, _vp, _i64, ctypes.POINTER(_i64),
