@@ -21,6 +21,7 @@ struct syfi_moe_ctx {
   Workspace ws;
   int num_sms = 0;
   int launches = 0;
+  int epoch = 0;          // bumped for every GEMM launch: tags the split-item hand-off flags
   // staging buffers of syfi_moe_forward_host
   void* stage = nullptr;
   size_t stage_bytes = 0;
@@ -97,7 +98,7 @@ int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uin
 
 void free_workspace(Workspace& ws) {
   void* ptrs[] = {ws.topk_idx, ws.topk_w, ws.local_mask, ws.counts, ws.meta, ws.status, ws.trace, ws.row_token, ws.route_row,
-                  ws.work, ws.a_perm, ws.a_scale, ws.c_hi, ws.c_lo, ws.c_scale, ws.o_rows};
+                  ws.work, ws.a_perm, ws.a_scale, ws.c_hi, ws.c_lo, ws.c_scale, ws.o_rows, ws.partial, ws.flags};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   const int dev = ws.device;
@@ -126,7 +127,7 @@ int alloc_workspace(Workspace& ws, int64_t max_tokens) {
   CU_TRY(dev_alloc(&ws.counts, kMaxLocalExperts, &total));
   CU_TRY(dev_alloc(&ws.meta, kMetaInts, &total));
   CU_TRY(dev_alloc(&ws.status, 4, &total));
-  CU_TRY(dev_alloc(&ws.trace, 6 * 4096, &total));
+  CU_TRY(dev_alloc(&ws.trace, 8 * 4096, &total));
   CU_TRY(dev_alloc(&ws.row_token, row_cap, &total));
   CU_TRY(dev_alloc(&ws.route_row, T * kTopK, &total));
   CU_TRY(dev_alloc(&ws.work, kMaxLocalExperts, &total));
@@ -136,6 +137,9 @@ int alloc_workspace(Workspace& ws, int64_t max_tokens) {
   CU_TRY(dev_alloc(&ws.c_lo, row_cap * kInter, &total));
   CU_TRY(dev_alloc(&ws.c_scale, row_cap * kIBlocks, &total));
   CU_TRY(dev_alloc(&ws.o_rows, row_cap * kHidden, &total));
+  CU_TRY(dev_alloc(&ws.partial, (size_t)kMaxGrid * 2 * kMaxTokenTile * 128, &total));
+  CU_TRY(dev_alloc(&ws.flags, kMaxGrid, &total));
+  CU_TRY(cudaMemset(ws.flags, 0, kMaxGrid * sizeof(int)));
   CU_TRY(cudaMemset(ws.status, 0, 4 * sizeof(int)));
   CU_TRY(cudaMemset(ws.meta, 0, kMetaInts * sizeof(int)));
   ws.max_tokens = (int)T;
@@ -190,6 +194,8 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
   if ((rc = make_map(&g2.tm_b0, ws.c_hi, ws.row_cap, kInter, token_tile))) return rc;
   if ((rc = make_map(&g2.tm_b1, ws.c_lo, ws.row_cap, kInter, token_tile))) return rc;
 
+  const int grid = ctx->num_sms < kMaxGrid ? ctx->num_sms : kMaxGrid;
+  if (ctx->epoch > (1 << 30)) ctx->epoch = 0;   // flags hold older epochs only; any fresh value works
   ctx->launches = 0;
   const bool timed = ctx->timing && ctx->ev[0] != nullptr;
   ctx->timing_valid = false;
@@ -204,10 +210,10 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
   CU_TRY(launch_gather(static_cast<const uint8_t*>(hs), static_cast<const float*>(hs_scale), T, ws, st));
   ctx->launches += 1;
   STAGE_MARK(3);
-  CU_TRY(launch_gemm1(g1, static_cast<const float*>(w13_scale), e_local, ws, ctx->num_sms, st));
+  CU_TRY(launch_gemm1(g1, static_cast<const float*>(w13_scale), e_local, ws, grid, ++ctx->epoch, st));
   ctx->launches += 1;
   STAGE_MARK(4);
-  CU_TRY(launch_gemm2(g2, static_cast<const float*>(w2_scale), e_local, ws, ctx->num_sms, st));
+  CU_TRY(launch_gemm2(g2, static_cast<const float*>(w2_scale), e_local, ws, grid, ++ctx->epoch, st));
   ctx->launches += 1;
   STAGE_MARK(5);
   CU_TRY(launch_combine(T, ws, out, out_is_f32, st));
@@ -431,7 +437,7 @@ int syfi_moe_debug_read(syfi_moe_ctx* ctx, const char* name, void* dst_host, int
       {"a_perm", ws.a_perm, R * kHidden},        {"a_scale", ws.a_scale, R * kHBlocks * 4},
       {"c_hi", ws.c_hi, R * kInter},             {"c_lo", ws.c_lo, R * kInter},
       {"c_scale", ws.c_scale, R * kIBlocks * 4}, {"o_rows", ws.o_rows, R * kHidden * 4},
-      {"trace", ws.trace, 6 * 4096 * 8},
+      {"trace", ws.trace, 8 * 4096 * 8},
       {"topk_idx", ws.topk_idx, T * kTopK * 4},  {"topk_w", ws.topk_w, T * kTopK * 4},
   };
   for (const Entry& e : table) {

@@ -85,6 +85,10 @@ struct GemmArgs {
   int e_local;
   int* status;
   long long* trace;         // [3][4096] timeline of CTA 0 when built with SYFI_TRACE, else unused
+  long long* trace_cta;     // [grid][5] per-CTA start/end (globaltimer, clock64) and SM id, SYFI_TRACE only
+  float* partial;           // [grid][2 * NT * 128] split-item partial sums, one slot per CTA
+  int* flags;               // [grid] flags[c] == epoch once CTA c published its partial
+  int epoch;                // distinct for every launch that shares partial/flags
 };
 
 // Optional timeline trace of CTA 0 (compile with -DSYFI_TRACE): role r appends (tag, clock) pairs.
@@ -125,6 +129,32 @@ __device__ __forceinline__ Item decode_item(const ExpertWork* s_work, int e_loca
   return it;
 }
 
+// Work is cut at K-step granularity ("stream-K"): the launch's items x steps units are dealt to the
+// CTAs in contiguous, equal ranges, so every SM streams weights until the very end even when the
+// item count does not divide by the grid.  A CTA's range is a sequence of segments (item, first
+// step, last step); a segment that does not start at step 0 is a CONTRIBUTION: its partial sums go
+// to the CTA's slot in global memory.  The CTA whose range holds an item's step 0 OWNS the item: if
+// its segment stops early it adds the contributions of the following CTAs before the epilogue.  An
+// owner meets a split item only at the END of its range while contributors handle it FIRST, so the
+// owner practically never waits; the wait is bounded all the same.
+struct UnitSplit {
+  int base, rem;            // CTA c owns base + (c < rem) units
+  __device__ __forceinline__ int start(int c) const { return c * base + min(c, rem); }
+  __device__ __forceinline__ int cta_of(int u) const {
+    const int big = rem * (base + 1);
+    return u < big ? u / (base + 1) : rem + (base > 0 ? (u - big) / base : 0);
+  }
+};
+
+__device__ __forceinline__ int ld_acquire(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release(int* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 template <int MODE, int NT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_b0,
@@ -156,6 +186,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int trace_n = 0;
   (void)trace_n;
+#ifdef SYFI_TRACE
+  if (threadIdx.x == 0 && p.trace_cta != nullptr) {
+    unsigned long long gt; unsigned smid;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
+    asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+    p.trace_cta[blockIdx.x * 5 + 0] = static_cast<long long>(gt);
+    p.trace_cta[blockIdx.x * 5 + 2] = clock64();
+    p.trace_cta[blockIdx.x * 5 + 4] = smid;
+  }
+#endif
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < G; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
@@ -178,7 +218,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *s_tmem;
-  const int total = p.meta[0] * FT;
+  const int total = p.meta[0] * FT;                 // work items
+  const int units = total * STEPS;
+  const UnitSplit split{units / static_cast<int>(gridDim.x), units % static_cast<int>(gridDim.x)};
+  const int u_begin = split.start(blockIdx.x), u_end = split.start(blockIdx.x + 1);
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (one thread)
@@ -187,10 +230,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       const uint64_t pol_b = l2_policy_evict_last();
       uint32_t it = 0, g = 0, ph = 0;      // step counter, ring entry, its phase
       bool alive = true;
-      for (int w = blockIdx.x; w < total && alive; w += gridDim.x) {
+      for (int u = u_begin; u < u_end && alive;) {
+        const int w = u / STEPS, s_first = u % STEPS, s_last = min(STEPS, s_first + (u_end - u));
+        u += s_last - s_first;
         const Item im = decode_item<FT, NT>(s_work, p.e_local, w);
         const int wrow = im.expert * C::kRowsPerExpert + im.ft * 128;
-        for (int step = 0; step < STEPS; ++step) {
+        for (int step = s_first; step < s_last; ++step) {
           if (!mbar_wait_bounded(&empty[g], ph ^ 1u, s_abort, kStatusWaitTimeoutProducer)) { alive = false; break; }
           TRACE(0, step);
           mbar_arrive_expect_tx(&full[g], C::kGroupBytes);
@@ -223,13 +268,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     if (lane == 0) {
       uint32_t g = 0, ph = 0, pr = 0, pph = 0;   // smem ring entry / phase, TMEM ring entry / phase
       bool alive = true;
-      for (int w = blockIdx.x; w < total && alive; w += gridDim.x) {
+      for (int u = u_begin; u < u_end && alive;) {
+        const int w = u / STEPS, s_first = u % STEPS, s_last = min(STEPS, s_first + (u_end - u));
+        u += s_last - s_first;
         const Item im = decode_item<FT, NT>(s_work, p.e_local, w);
         // Mode 2 issues ONE MMA of N = 2 NT per 32 bytes of K over the adjacent hi and lo tiles
         // (the columns past the tile's n rows hold other rows' data and are never read back)
         // instead of one per term; mode 1 needs two because up and gate are different A tiles.
         const uint32_t idesc = umma_idesc_e4m3_m128(MODE == 1 ? static_cast<uint32_t>(im.n) : 2u * NT);
-        for (int step = 0; step < STEPS; ++step) {
+        for (int step = s_first; step < s_last; ++step) {
           if (!mbar_wait_bounded(&full[g], ph, s_abort, kStatusWaitTimeoutMma) ||
               !mbar_wait_bounded(&tempty[pr], pph ^ 1u, s_abort, kStatusWaitTimeoutMma)) { alive = false; break; }
           tc_fence_after();
@@ -272,8 +319,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     uint32_t pr = 0, pph = 0;               // TMEM ring entry and its phase
     bool ok = true;
     int sbuf = 0;
-    if (MODE == 2 && static_cast<int>(blockIdx.x) < total) {
-      const Item nx = decode_item<FT, NT>(s_work, p.e_local, blockIdx.x);
+    int cached_row_start = -1;              // token tile whose activation scales sit in shared memory (mode 1)
+    if (MODE == 2 && u_begin < u_end) {
+      const Item nx = decode_item<FT, NT>(s_work, p.e_local, u_begin / STEPS);
       for (int i = et; i < KB * NT; i += kEpiThreads) {
         const int kb = i / NT, j = i % NT;
         if (j < nx.n) cp_async_f32(s_scales + i, p.act_scale + static_cast<size_t>(kb) * p.row_cap + nx.row_start + j);
@@ -284,7 +332,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     }
     // After a failed wait a warp keeps walking the work list and still joins every named
     // barrier below (doing no other work), so the four warps can never strand each other.
-    for (int w = blockIdx.x; w < total; w += gridDim.x) {
+    for (int u = u_begin; u < u_end;) {
+      const int w = u / STEPS, s_first = u % STEPS, s_last = min(STEPS, s_first + (u_end - u));
+      u += s_last - s_first;
       const Item im = decode_item<FT, NT>(s_work, p.e_local, w);
       const int ft = im.ft;
       const int n = ok ? im.n : 0;
@@ -295,9 +345,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         s_act = s_scales;
         s_ws = s_scales + KB * NT;
         named_bar_sync(1, kEpiThreads);     // previous item's readers of the staging arrays are done
-        for (int i = et; i < KB * NT && ok; i += kEpiThreads) {
-          const int kb = i / NT, j = i % NT;
-          s_act[i] = (j < n) ? __ldg(p.act_scale + static_cast<size_t>(kb) * p.row_cap + im.row_start + j) : 0.0f;
+        // the activation scales depend on the token tile only: consecutive items of a CTA mostly
+        // share it (same expert, next feature tile), so they are reloaded only when it changes
+        if (im.row_start != cached_row_start) {
+          for (int i = et; i < KB * NT && ok; i += kEpiThreads) {
+            const int kb = i / NT, j = i % NT;
+            s_act[i] = (j < n) ? __ldg(p.act_scale + static_cast<size_t>(kb) * p.row_cap + im.row_start + j) : 0.0f;
+          }
+          cached_row_start = ok ? im.row_start : -1;
         }
         if (et < KB && ok) {
           s_ws[et] = __ldg(p.w_scale + (static_cast<size_t>(im.expert) * 32 + ft) * kHBlocks + et);
@@ -313,9 +368,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         s_ws = s_act + KB * NT;
         cp_async_wait_all();
         named_bar_sync(1, kEpiThreads);
-        const int wn = w + gridDim.x;
-        if (wn < total && ok) {
-          const Item nx = decode_item<FT, NT>(s_work, p.e_local, wn);
+        if (u < u_end && ok) {                // u already points at the next segment
+          const Item nx = decode_item<FT, NT>(s_work, p.e_local, u / STEPS);
           float* d_act = s_scales + (sbuf ^ 1) * kScaleStride;
           for (int i = et; i < KB * NT; i += kEpiThreads) {
             const int kb = i / NT, j = i % NT;
@@ -338,7 +392,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         for (int j = 0; j < NT; ++j) acc1[j] = 0.0f;
       }
 
-      for (int step = 0; step < STEPS && ok; ++step) {
+      for (int step = s_first; step < s_last && ok; ++step) {
         if (!mbar_wait_bounded(&tfull[pr], pph, s_abort, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
         tc_fence_after();
         if (et == 0) TRACE(2, step);
@@ -385,8 +439,52 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         if (lane == 0) mbar_arrive(&tempty[pr]);
         if (++pr == PAIRS) { pr = 0; pph ^= 1u; }
       }
-      const int n_out = ok ? n : 0;           // a failed item stores nothing
       if (et == 0) TRACE(2, 1002);
+      if (s_first > 0) {
+        // contribution: publish the partial sums of this segment, then signal the owner
+        // slot layout [accumulator][feature][column]: each thread owns NT contiguous floats
+        float4* slot = reinterpret_cast<float4*>(p.partial + static_cast<size_t>(blockIdx.x) * (2 * NT * 128) + feat * NT);
+#pragma unroll
+        for (int j = 0; j < NT; j += 4) {
+          if (j < n) {
+            __stcg(slot + j / 4, make_float4(acc0[j], acc0[j + 1], acc0[j + 2], acc0[j + 3]));
+            if (MODE == 1) __stcg(slot + (NT * 128 + j) / 4, make_float4(acc1[j], acc1[j + 1], acc1[j + 2], acc1[j + 3]));
+          }
+        }
+        __threadfence();
+        named_bar_sync(3, kEpiThreads);
+        if (et == 0 && ok) st_release(p.flags + blockIdx.x, p.epoch);
+        continue;                             // no epilogue: the owner runs it
+      }
+      if (s_last < STEPS) {
+        // owner of a split item: add what the following CTAs computed for steps s_last .. STEPS-1
+        const int c_last = split.cta_of((w + 1) * STEPS - 1);
+        for (int cc = blockIdx.x + 1; cc <= c_last; ++cc) {
+          if (et == 0 && ok) {
+            const long long t0 = clock64();
+            while (ld_acquire(p.flags + cc) != p.epoch) {
+              if (*s_abort != 0) break;
+              if (clock64() - t0 > (1ll << 32)) { *s_abort = kStatusWaitTimeoutEpilogue; break; }
+              __nanosleep(64);
+            }
+          }
+          named_bar_sync(3, kEpiThreads);
+          if (*s_abort != 0) ok = false;
+          const float4* slot = reinterpret_cast<const float4*>(p.partial + static_cast<size_t>(cc) * (2 * NT * 128) + feat * NT);
+#pragma unroll
+          for (int j = 0; j < NT; j += 4) {
+            if (j < n && ok) {
+              const float4 a = __ldcg(slot + j / 4);
+              acc0[j] += a.x; acc0[j + 1] += a.y; acc0[j + 2] += a.z; acc0[j + 3] += a.w;
+              if (MODE == 1) {
+                const float4 b = __ldcg(slot + (NT * 128 + j) / 4);
+                acc1[j] += b.x; acc1[j + 1] += b.y; acc1[j + 2] += b.z; acc1[j + 3] += b.w;
+              }
+            }
+          }
+        }
+      }
+      const int n_out = ok ? n : 0;           // a failed item stores nothing
 
       if (MODE == 1) {
         // SwiGLU, then the per-row amax over the 128 features of this tile
@@ -409,29 +507,46 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           p.c_scale[static_cast<size_t>(ft) * p.row_cap + im.row_start + et] = sc;
         }
         named_bar_sync(2, kEpiThreads);
-        uint8_t* hi = p.c_hi + static_cast<size_t>(im.row_start) * kInter + ft * 128 + feat;
-        uint8_t* lo = p.c_lo + static_cast<size_t>(im.row_start) * kInter + ft * 128 + feat;
+        // Quantise four token rows at a time into packed bytes, transpose across the lane quad so a
+        // lane holds four adjacent features of ONE row, and store 4 bytes per lane: n/4 store
+        // instructions per tensor instead of n byte stores.
+        const int qrow = lane & 3;              // which of the four rows this lane stores
+        const size_t qoff = static_cast<size_t>(ft) * 128 + q * 32 + (lane >> 2) * 4;
 #pragma unroll
-        for (int j = 0; j < NT; j += 2) {
+        for (int j = 0; j < NT; j += 4) {
           if (j < n_out) {
-            const float sc0 = s_cs[j], sc1 = s_cs[j + 1];
-            const float in0 = s_inv[j], in1 = s_inv[j + 1];
-            const float c0 = acc0[j], c1 = acc0[j + 1];
-            const uint16_t h = cvt_e4m3x2(c0 * in0, c1 * in1);
-            const float2 hb = e4m3x2_to_float2(h);
-            const float r0 = fmaf(-hb.x, sc0, c0), r1 = fmaf(-hb.y, sc1, c1);
-            const uint16_t l = cvt_e4m3x2(r0 * in0 * kLoRatio, r1 * in1 * kLoRatio);
-            hi[static_cast<size_t>(j) * kInter] = static_cast<uint8_t>(h & 0xff);
-            hi[static_cast<size_t>(j + 1) * kInter] = static_cast<uint8_t>(h >> 8);
-            lo[static_cast<size_t>(j) * kInter] = static_cast<uint8_t>(l & 0xff);
-            lo[static_cast<size_t>(j + 1) * kInter] = static_cast<uint8_t>(l >> 8);
+            uint32_t hp = 0, lp = 0;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int c = j + 2 * h;
+              const float sc0 = s_cs[c], sc1 = s_cs[c + 1];
+              const float in0 = s_inv[c], in1 = s_inv[c + 1];
+              const float c0 = acc0[c], c1 = acc0[c + 1];
+              const uint16_t hh = cvt_e4m3x2(c0 * in0, c1 * in1);
+              const float2 hb = e4m3x2_to_float2(hh);
+              const float r0 = fmaf(-hb.x, sc0, c0), r1 = fmaf(-hb.y, sc1, c1);
+              const uint16_t ll = cvt_e4m3x2(r0 * in0 * kLoRatio, r1 * in1 * kLoRatio);
+              hp |= static_cast<uint32_t>(hh) << (16 * h);
+              lp |= static_cast<uint32_t>(ll) << (16 * h);
+            }
+            hp = quad_transpose_bytes(hp, lane);
+            lp = quad_transpose_bytes(lp, lane);
+            const size_t off = static_cast<size_t>(im.row_start + j + qrow) * kInter + qoff;
+            *reinterpret_cast<uint32_t*>(p.c_hi + off) = hp;
+            *reinterpret_cast<uint32_t*>(p.c_lo + off) = lp;
           }
         }
       } else {
-        float* o = p.o_rows + static_cast<size_t>(im.row_start) * kHidden + ft * 128 + feat;
+        const int qrow = lane & 3;
+        float* o = p.o_rows + static_cast<size_t>(im.row_start + qrow) * kHidden + ft * 128 + q * 32 + (lane >> 2) * 4;
 #pragma unroll
-        for (int j = 0; j < NT; ++j)
-          if (j < n_out) o[static_cast<size_t>(j) * kHidden] = acc0[j];
+        for (int j = 0; j < NT; j += 4) {
+          if (j < n_out) {
+            float a0 = acc0[j], a1 = acc0[j + 1], a2 = acc0[j + 2], a3 = acc0[j + 3];
+            quad_transpose_f32(a0, a1, a2, a3, lane);   // now: row j + qrow, four adjacent features
+            *reinterpret_cast<float4*>(o + static_cast<size_t>(j) * kHidden) = make_float4(a0, a1, a2, a3);
+          }
+        }
       }
     }
   }
@@ -443,6 +558,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     tmem_dealloc(tmem_base, kTmemCols);
   }
   if (threadIdx.x == 0 && *s_abort != 0) atomicExch(p.status, *s_abort);
+#ifdef SYFI_TRACE
+  if (threadIdx.x == 0 && p.trace_cta != nullptr) {
+    unsigned long long gt;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gt));
+    p.trace_cta[blockIdx.x * 5 + 1] = static_cast<long long>(gt);
+    p.trace_cta[blockIdx.x * 5 + 3] = clock64();
+  }
+#endif
 }
 
 template <int MODE, int NT>
@@ -468,16 +591,16 @@ cudaError_t gemm_set_attributes() {
 }
 
 cudaError_t launch_gemm1(const GemmLaunch& g, const float* w13_scale, int e_local, const Workspace& ws, int num_sms,
-                         cudaStream_t st) {
+                         int epoch, cudaStream_t st) {
   GemmArgs a{ws.work, ws.meta, ws.a_scale, w13_scale, ws.c_hi, ws.c_lo, ws.c_scale, nullptr, ws.row_cap, e_local,
-             ws.status, ws.trace};
+             ws.status, ws.trace, ws.trace + 6 * 4096, ws.partial, ws.flags, epoch};
   return g.token_tile == 32 ? launch_gemm<1, 32>(g, a, num_sms, st) : launch_gemm<1, 64>(g, a, num_sms, st);
 }
 
 cudaError_t launch_gemm2(const GemmLaunch& g, const float* w2_scale, int e_local, const Workspace& ws, int num_sms,
-                         cudaStream_t st) {
+                         int epoch, cudaStream_t st) {
   GemmArgs a{ws.work, ws.meta, ws.c_scale, w2_scale, nullptr, nullptr, nullptr, ws.o_rows, ws.row_cap, e_local,
-             ws.status, ws.trace + 3 * 4096};
+             ws.status, ws.trace + 3 * 4096, ws.trace + 7 * 4096, ws.partial, ws.flags, epoch};
   return g.token_tile == 32 ? launch_gemm<2, 32>(g, a, num_sms, st) : launch_gemm<2, 64>(g, a, num_sms, st);
 }
 

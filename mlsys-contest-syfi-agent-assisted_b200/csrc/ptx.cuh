@@ -165,6 +165,30 @@ __device__ __forceinline__ void cp_async_wait_all() {
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
+// 4x4 transposes across a lane quad (lanes 4q..4q+3).  Before: lane r holds row r = (m[r][0..3]).
+// After: lane c holds column c = (m[0..3][c]).  Used to turn "one feature, four token rows" per
+// thread into "four adjacent features of one token row", so a store carries 4x the bytes.
+__device__ __forceinline__ uint32_t quad_transpose_bytes(uint32_t v, int lane) {
+  const uint32_t o1 = __shfl_xor_sync(0xffffffffu, v, 1);
+  v = (lane & 1) ? __byte_perm(v, o1, 0x3715) : __byte_perm(v, o1, 0x6240);
+  const uint32_t o2 = __shfl_xor_sync(0xffffffffu, v, 2);
+  return (lane & 2) ? __byte_perm(v, o2, 0x3276) : __byte_perm(v, o2, 0x5410);
+}
+__device__ __forceinline__ void quad_transpose_f32(float& a0, float& a1, float& a2, float& a3, int lane) {
+  {
+    const bool odd = lane & 1;
+    const float rx = __shfl_xor_sync(0xffffffffu, odd ? a0 : a1, 1);
+    const float ry = __shfl_xor_sync(0xffffffffu, odd ? a2 : a3, 1);
+    if (odd) { a0 = rx; a2 = ry; } else { a1 = rx; a3 = ry; }
+  }
+  {
+    const bool hi = lane & 2;
+    const float rx = __shfl_xor_sync(0xffffffffu, hi ? a0 : a2, 2);
+    const float ry = __shfl_xor_sync(0xffffffffu, hi ? a1 : a3, 2);
+    if (hi) { a0 = rx; a1 = ry; } else { a2 = rx; a3 = ry; }
+  }
+}
+
 // two floats -> two e4m3 bytes (lo -> bits 0..7, hi -> bits 8..15), round-nearest, saturating
 __device__ __forceinline__ uint16_t cvt_e4m3x2(float lo, float hi) {
   uint16_t r;
