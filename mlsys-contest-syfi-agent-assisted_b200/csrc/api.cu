@@ -190,9 +190,13 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
   if ((rc = make_map(&g1.tm_w, w13, (uint64_t)e_local * 2 * kInter, kHidden, 128))) return rc;
   if ((rc = make_map(&g1.tm_b0, ws.a_perm, ws.row_cap, kHidden, token_tile))) return rc;
   g1.tm_b1 = g1.tm_b0;
+  if ((rc = make_map(&g1.tm_b0s, ws.a_perm, ws.row_cap, kHidden, 16))) return rc;
+  g1.tm_b1s = g1.tm_b0s;
   if ((rc = make_map(&g2.tm_w, w2, (uint64_t)e_local * kHidden, kInter, 128))) return rc;
   if ((rc = make_map(&g2.tm_b0, ws.c_hi, ws.row_cap, kInter, token_tile))) return rc;
   if ((rc = make_map(&g2.tm_b1, ws.c_lo, ws.row_cap, kInter, token_tile))) return rc;
+  if ((rc = make_map(&g2.tm_b0s, ws.c_hi, ws.row_cap, kInter, 16))) return rc;
+  if ((rc = make_map(&g2.tm_b1s, ws.c_lo, ws.row_cap, kInter, 16))) return rc;
 
   const int grid = ctx->num_sms < kMaxGrid ? ctx->num_sms : kMaxGrid;
   if (ctx->epoch > (1 << 30)) ctx->epoch = 0;   // flags hold older epochs only; any fresh value works

@@ -10,6 +10,7 @@
 #include <cuda_bf16.h>
 
 #include "moe_internal.h"
+#include "ptx.cuh"
 
 namespace syfi {
 
@@ -23,6 +24,8 @@ __global__ void __launch_bounds__(kCombineThreads)
 combine_kernel(int T, const int* __restrict__ route_row, const float* __restrict__ topk_w,
                const float* __restrict__ o_rows, void* __restrict__ out, int out_is_f32, int row_cap) {
   const int t = blockIdx.x;
+  pdl_wait();
+  pdl_trigger();
   if (t >= T) return;
   const int tid = threadIdx.x;
   float4 acc[kVecPerThread];
@@ -64,9 +67,8 @@ combine_kernel(int T, const int* __restrict__ route_row, const float* __restrict
 }  // namespace
 
 cudaError_t launch_combine(int T, const Workspace& ws, void* out, int out_is_f32, cudaStream_t st) {
-  combine_kernel<<<T, kCombineThreads, 0, st>>>(T, ws.route_row, ws.topk_w, ws.o_rows, out, out_is_f32,
-                                                ws.row_cap);
-  return cudaGetLastError();
+  return launch_dependent(combine_kernel, dim3(T), dim3(kCombineThreads), 0, st, T, ws.route_row, ws.topk_w,
+                          ws.o_rows, out, out_is_f32, ws.row_cap);
 }
 
 }  // namespace syfi

@@ -158,7 +158,8 @@ __device__ __forceinline__ void st_release(int* p, int v) {
 template <int MODE, int NT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_b0,
-                    const __grid_constant__ CUtensorMap tm_b1, const GemmArgs p) {
+                    const __grid_constant__ CUtensorMap tm_b1, const __grid_constant__ CUtensorMap tm_b0s,
+                    const __grid_constant__ CUtensorMap tm_b1s, const GemmArgs p) {
   using C = Cfg<MODE, NT>;
   constexpr int G = C::kGroups;           // smem ring entries, each kKps K blocks
   constexpr int KPS = C::kKps;
@@ -205,11 +206,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     tma_prefetch_desc(&tm_w);
     tma_prefetch_desc(&tm_b0);
     if (MODE == 2) tma_prefetch_desc(&tm_b1);
+    tma_prefetch_desc(&tm_b0s);
+    if (MODE == 2) tma_prefetch_desc(&tm_b1s);
   }
   if (warp == 1) {
     tmem_alloc(s_tmem, kTmemCols);
     tmem_relinquish();
   }
+  // everything above touched only this CTA's own resources; from here on the kernel reads what the
+  // kernels before it in the stream produced
+  pdl_wait();
+  pdl_trigger();
   if (threadIdx.x >= 64 && threadIdx.x < 64 + kMaxLocalExperts) {
     const int e = threadIdx.x - 64;
     s_work[e] = (e < p.e_local) ? p.work[e] : ExpertWork{0, 0, 0, 0};
@@ -235,10 +242,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         u += s_last - s_first;
         const Item im = decode_item<FT, NT>(s_work, p.e_local, w);
         const int wrow = im.expert * C::kRowsPerExpert + im.ft * 128;
+        // Tiles of at most 16 rows use the 16-row box: the token-side tiles come from L2 through the
+        // same SM port as the weights, so every byte not fetched is bandwidth for the weight stream.
+        const bool small = im.n <= 16;
+        const CUtensorMap* mb0 = small ? &tm_b0s : &tm_b0;
+        const CUtensorMap* mb1 = small ? &tm_b1s : &tm_b1;
+        const uint32_t b_bytes = small ? 16 * 128 : kBTile;
+        const uint32_t group_tx = KPS * (MODE == 1 ? 2 * kATile + b_bytes : kATile + 2 * b_bytes);
         for (int step = s_first; step < s_last; ++step) {
           if (!mbar_wait_bounded(&empty[g], ph ^ 1u, s_abort, kStatusWaitTimeoutProducer)) { alive = false; break; }
           TRACE(0, step);
-          mbar_arrive_expect_tx(&full[g], C::kGroupBytes);
+          mbar_arrive_expect_tx(&full[g], group_tx);
 #pragma unroll
           for (int k = 0; k < KPS; ++k) {
             uint8_t* st = smem + g * C::kGroupBytes + k * C::kStageBytes;
@@ -246,11 +260,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             if (MODE == 1) {
               tma_load_2d(st, &tm_w, &full[g], x, wrow, pol_w);
               tma_load_2d(st + kATile, &tm_w, &full[g], x, wrow + kInter, pol_w);
-              tma_load_2d(st + 2 * kATile, &tm_b0, &full[g], x, im.row_start, pol_b);
+              tma_load_2d(st + 2 * kATile, mb0, &full[g], x, im.row_start, pol_b);
             } else {
               tma_load_2d(st, &tm_w, &full[g], x, wrow, pol_w);
-              tma_load_2d(st + kATile, &tm_b0, &full[g], x, im.row_start, pol_b);
-              tma_load_2d(st + kATile + kBTile, &tm_b1, &full[g], x, im.row_start, pol_b);
+              tma_load_2d(st + kATile, mb0, &full[g], x, im.row_start, pol_b);
+              tma_load_2d(st + kATile + kBTile, mb1, &full[g], x, im.row_start, pol_b);
             }
           }
           ++it;
@@ -570,8 +584,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
 template <int MODE, int NT>
 cudaError_t launch_gemm(const GemmLaunch& g, const GemmArgs& a, int num_sms, cudaStream_t st) {
-  grouped_gemm_kernel<MODE, NT><<<num_sms, kGemmThreads, Cfg<MODE, NT>::kSmemBytes, st>>>(g.tm_w, g.tm_b0, g.tm_b1, a);
-  return cudaGetLastError();
+  return launch_dependent(grouped_gemm_kernel<MODE, NT>, dim3(num_sms), dim3(kGemmThreads),
+                          static_cast<size_t>(Cfg<MODE, NT>::kSmemBytes), st, g.tm_w, g.tm_b0, g.tm_b1, g.tm_b0s,
+                          g.tm_b1s, a);
 }
 
 template <int MODE, int NT>

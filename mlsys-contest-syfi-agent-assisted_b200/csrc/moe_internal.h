@@ -82,8 +82,30 @@ struct GemmLaunch {
   CUtensorMap tm_w;    // weights, 2-D [E * rows_per_expert, K], box 128 x 128
   CUtensorMap tm_b0;   // token-side operand, box token_tile x 128 (GEMM1: a_perm; GEMM2: c_hi)
   CUtensorMap tm_b1;   // GEMM2: c_lo (unused by GEMM1)
+  CUtensorMap tm_b0s;  // same tensors with a 16-row box: tiles of <= 16 rows pull half the bytes
+  CUtensorMap tm_b1s;
   int token_tile;      // 32 or 64: token rows per work item, must match the row-list kernel's
 };
+
+// Programmatic dependent launch: the kernel may be scheduled while its predecessor in the stream is
+// still running (its CTAs take whatever SM resources are free and run their prologue); it must
+// execute griddepcontrol.wait (pdl_wait() in ptx.cuh) before it touches anything the predecessor
+// wrote.  Hides the launch latency and the prologue of every kernel after the first.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                    Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 // launchers (each returns the cudaGetLastError() of its launches)
 cudaError_t launch_router(const float* logits, const void* bias_bf16, int T, int e_local, int expert_offset,

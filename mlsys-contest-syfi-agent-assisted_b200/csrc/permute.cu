@@ -11,6 +11,7 @@
 // that with ballots.  Every expert's row range is padded to a multiple of 16 rows
 // (the tcgen05 N granularity), padding rows carry token -1 and zero data.
 #include "moe_internal.h"
+#include "ptx.cuh"
 
 namespace syfi {
 
@@ -26,6 +27,8 @@ build_rows_kernel(int T, int e_local, int expert_offset, const uint32_t* __restr
   __shared__ int s_warp[kBuildThreads / 32];
   const int e = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_wait();
+  pdl_trigger();
 
   int row_off = 0, tile_off = 0, rows_total = 0, tiles_total = 0, routed = 0, active = 0, cnt = 0;
   for (int i = 0; i < e_local; ++i) {
@@ -87,6 +90,8 @@ __global__ void __launch_bounds__(kGatherThreads)
 gather_rows_kernel(const uint8_t* __restrict__ hidden, const float* __restrict__ hidden_scale, int T,
                    const int* __restrict__ row_token, const int* __restrict__ meta, uint8_t* __restrict__ a_perm,
                    float* __restrict__ a_scale, int row_cap) {
+  pdl_wait();
+  pdl_trigger();
   const int rows_total = meta[1];
   const int tid = threadIdx.x;
   for (int r = blockIdx.x; r < rows_total; r += gridDim.x) {
@@ -111,19 +116,17 @@ gather_rows_kernel(const uint8_t* __restrict__ hidden, const float* __restrict__
 
 cudaError_t launch_build_rows(int T, int e_local, int expert_offset, int token_tile, const Workspace& ws,
                               cudaStream_t st) {
-  build_rows_kernel<<<e_local, kBuildThreads, 0, st>>>(T, e_local, expert_offset, ws.local_mask, ws.counts,
-                                                       ws.topk_idx, ws.row_token, ws.route_row, ws.work, ws.meta,
-                                                       ws.row_cap, token_tile, ws.status);
-  return cudaGetLastError();
+  return launch_dependent(build_rows_kernel, dim3(e_local), dim3(kBuildThreads), 0, st, T, e_local, expert_offset,
+                          ws.local_mask, ws.counts, ws.topk_idx, ws.row_token, ws.route_row, ws.work, ws.meta,
+                          ws.row_cap, token_tile, ws.status);
 }
 
 cudaError_t launch_gather(const uint8_t* hidden, const float* hidden_scale, int T, const Workspace& ws,
                           cudaStream_t st) {
   const int max_rows = 8 * T + kRowPad * kMaxLocalExperts;
   const int grid = max_rows < 148 * 8 ? max_rows : 148 * 8;
-  gather_rows_kernel<<<grid, kGatherThreads, 0, st>>>(hidden, hidden_scale, T, ws.row_token, ws.meta, ws.a_perm,
-                                                      ws.a_scale, ws.row_cap);
-  return cudaGetLastError();
+  return launch_dependent(gather_rows_kernel, dim3(grid), dim3(kGatherThreads), 0, st, hidden, hidden_scale, T,
+                          ws.row_token, ws.meta, ws.a_perm, ws.a_scale, ws.row_cap);
 }
 
 }  // namespace syfi

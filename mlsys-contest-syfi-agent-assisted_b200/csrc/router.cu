@@ -18,6 +18,7 @@
 
 #include "../../include/syfi_moe.h"
 #include "moe_internal.h"
+#include "ptx.cuh"
 
 namespace syfi {
 
@@ -31,6 +32,7 @@ route_kernel(const float* __restrict__ logits, const __nv_bfloat16* __restrict__
              uint32_t* __restrict__ local_mask, int* __restrict__ route_row, int* __restrict__ counts) {
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  pdl_trigger();
   if (t >= T) return;
   const unsigned full = 0xffffffffu;
 
