@@ -44,8 +44,6 @@ namespace syfi {
 
 namespace {
 
-constexpr int kGemmThreads = 192;
-constexpr int kEpiThreads = 128;
 constexpr int kATile = 128 * 128;         // weight tile: 128 rows x 128 bytes of K
 constexpr int kTmemCols = 512;
 
@@ -64,6 +62,8 @@ template <int MODE, int NT> struct Cfg {
   static constexpr int kSlots = kTmemCols / (2 * NT);                           // accumulator-pair slots
   static constexpr int kPairs = kSlots / kKps;                                  // slot groups signalled together
   static constexpr int kScaleBufs = MODE == 2 ? 2 : 1;   // mode 2 prefetches the next item's scales
+  static constexpr int kColSplit = NT / 32;               // epilogue warps per TMEM lane quarter
+  static constexpr int kThreads = 64 + 128 * kColSplit;   // producer warp + MMA warp + epilogue warps
   static constexpr int kSmemBytes = 1024 /* alignment slack */ + kGroups * kGroupBytes +
                                     4 * (kScaleBufs * (kKBlocks * NT + 128) + 4 * NT + 2 * NT) +
                                     8 * (2 * kGroups + 2 * kPairs) +
@@ -89,6 +89,7 @@ struct GemmArgs {
   float* partial;           // [grid][2 * NT * 128] split-item partial sums, one slot per CTA
   int* flags;               // [grid] flags[c] == epoch once CTA c published its partial
   int epoch;                // distinct for every launch that shares partial/flags
+  int round_robin;          // schedule: 0 = contiguous unit ranges (items may split), 1 = whole items round-robin
 };
 
 // Optional timeline trace of CTA 0 (compile with -DSYFI_TRACE): role r appends (tag, clock) pairs.
@@ -156,7 +157,7 @@ __device__ __forceinline__ void st_release(int* p, int v) {
 }
 
 template <int MODE, int NT>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__((Cfg<MODE, NT>::kThreads), 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_b0,
                     const __grid_constant__ CUtensorMap tm_b1, const __grid_constant__ CUtensorMap tm_b0s,
                     const __grid_constant__ CUtensorMap tm_b1s, const GemmArgs p) {
@@ -200,7 +201,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < G; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
-    for (int i = 0; i < PAIRS; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 4); }
+    for (int i = 0; i < PAIRS; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 4 * C::kColSplit); }
     *s_abort = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tm_w);
@@ -228,17 +229,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   const int total = p.meta[0] * FT;                 // work items
   const int units = total * STEPS;
   const UnitSplit split{units / static_cast<int>(gridDim.x), units % static_cast<int>(gridDim.x)};
-  const int u_begin = split.start(blockIdx.x), u_end = split.start(blockIdx.x + 1);
+  // Two schedules.  Few items (decode): contiguous unit ranges, items split across CTAs.  Many items
+  // (prefill): whole items dealt round-robin, so the CTAs running side by side work on the token
+  // tiles of the SAME weight tile and all but one of them find it in L2.
+  const bool rr = p.round_robin != 0;
+  const int my_items = static_cast<int>(blockIdx.x) < total ? (total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const int u_begin = rr ? 0 : split.start(blockIdx.x);
+  const int u_end = rr ? my_items * STEPS : split.start(blockIdx.x + 1);
+  auto item_at = [&](int u) { return rr ? static_cast<int>(blockIdx.x + (u / STEPS) * gridDim.x) : u / STEPS; };
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (one thread)
     if (lane == 0) {
-      const uint64_t pol_w = l2_policy_evict_first();
+      const uint64_t pol_w = rr ? l2_policy_evict_last() : l2_policy_evict_first();
       const uint64_t pol_b = l2_policy_evict_last();
       uint32_t it = 0, g = 0, ph = 0;      // step counter, ring entry, its phase
       bool alive = true;
       for (int u = u_begin; u < u_end && alive;) {
-        const int w = u / STEPS, s_first = u % STEPS, s_last = min(STEPS, s_first + (u_end - u));
+        const int w = item_at(u), s_first = u % STEPS, s_last = min(STEPS, s_first + (u_end - u));
         u += s_last - s_first;
         const Item im = decode_item<FT, NT>(s_work, p.e_local, w);
         const int wrow = im.expert * C::kRowsPerExpert + im.ft * 128;
@@ -283,7 +291,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       uint32_t g = 0, ph = 0, pr = 0, pph = 0;   // smem ring entry / phase, TMEM ring entry / phase
       bool alive = true;
       for (int u = u_begin; u < u_end && alive;) {
-        const int w = u / STEPS, s_first = u % STEPS, s_last = min(STEPS, s_first + (u_end - u));
+        const int w = item_at(u), s_first = u % STEPS, s_last = min(STEPS, s_first + (u_end - u));
         u += s_last - s_first;
         const Item im = decode_item<FT, NT>(s_work, p.e_local, w);
         // Mode 2 issues ONE MMA of N = 2 NT per 32 bytes of K over the adjacent hi and lo tiles
@@ -326,17 +334,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     __syncwarp();
   } else {
     // ------------------------------------------------ promotion + epilogue warps
+    // CS warps share each TMEM lane quarter and split the tile's columns between them, so a thread
+    // owns one feature and CN = NT / CS token columns.
+    constexpr int CS = C::kColSplit;
+    constexpr int CN = NT / CS;
+    constexpr int kEpi = 128 * CS;          // epilogue threads
+    static_assert(CN == 32, "the drain below moves 32 columns per thread and step");
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
+    const int c0 = ((warp - 2) >> 2) * CN;  // first column of this thread's share
     const int feat = q * 32 + lane;         // feature (row of the weight tile) of this thread
-    const int et = threadIdx.x - 64;        // 0..127 among the epilogue threads
+    const int et = threadIdx.x - 64;        // 0..kEpi-1 among the epilogue threads
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     uint32_t pr = 0, pph = 0;               // TMEM ring entry and its phase
     bool ok = true;
     int sbuf = 0;
     int cached_row_start = -1;              // token tile whose activation scales sit in shared memory (mode 1)
     if (MODE == 2 && u_begin < u_end) {
-      const Item nx = decode_item<FT, NT>(s_work, p.e_local, u_begin / STEPS);
-      for (int i = et; i < KB * NT; i += kEpiThreads) {
+      const Item nx = decode_item<FT, NT>(s_work, p.e_local, item_at(u_begin));
+      for (int i = et; i < KB * NT; i += kEpi) {
         const int kb = i / NT, j = i % NT;
         if (j < nx.n) cp_async_f32(s_scales + i, p.act_scale + static_cast<size_t>(kb) * p.row_cap + nx.row_start + j);
       }
@@ -345,9 +360,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
                      p.w_scale + (static_cast<size_t>(nx.expert) * kHBlocks + nx.ft) * kIBlocks + et);
     }
     // After a failed wait a warp keeps walking the work list and still joins every named
-    // barrier below (doing no other work), so the four warps can never strand each other.
+    // barrier below (doing no other work), so the epilogue warps can never strand each other.
     for (int u = u_begin; u < u_end;) {
-      const int w = u / STEPS, s_first = u % STEPS, s_last = min(STEPS, s_first + (u_end - u));
+      const int w = item_at(u), s_first = u % STEPS, s_last = min(STEPS, s_first + (u_end - u));
       u += s_last - s_first;
       const Item im = decode_item<FT, NT>(s_work, p.e_local, w);
       const int ft = im.ft;
@@ -358,21 +373,28 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       if (MODE == 1) {
         s_act = s_scales;
         s_ws = s_scales + KB * NT;
-        named_bar_sync(1, kEpiThreads);     // previous item's readers of the staging arrays are done
+        named_bar_sync(1, kEpi);            // previous item's readers of the staging arrays are done
         // the activation scales depend on the token tile only: consecutive items of a CTA mostly
         // share it (same expert, next feature tile), so they are reloaded only when it changes
         if (im.row_start != cached_row_start) {
-          for (int i = et; i < KB * NT && ok; i += kEpiThreads) {
+          constexpr int kIters = KB * NT / kEpi;
+          static_assert(kIters * kEpi == KB * NT, "scale staging must divide evenly");
+          float tmp[kIters];
+#pragma unroll
+          for (int r = 0; r < kIters; ++r) {   // all loads in flight before the first store
+            const int i = et + r * kEpi;
             const int kb = i / NT, j = i % NT;
-            s_act[i] = (j < n) ? __ldg(p.act_scale + static_cast<size_t>(kb) * p.row_cap + im.row_start + j) : 0.0f;
+            tmp[r] = (j < n) ? __ldg(p.act_scale + static_cast<size_t>(kb) * p.row_cap + im.row_start + j) : 0.0f;
           }
+#pragma unroll
+          for (int r = 0; r < kIters; ++r) s_act[et + r * kEpi] = tmp[r];
           cached_row_start = ok ? im.row_start : -1;
         }
         if (et < KB && ok) {
           s_ws[et] = __ldg(p.w_scale + (static_cast<size_t>(im.expert) * 32 + ft) * kHBlocks + et);
           s_ws[64 + et] = __ldg(p.w_scale + (static_cast<size_t>(im.expert) * 32 + 16 + ft) * kHBlocks + et);
         }
-        named_bar_sync(1, kEpiThreads);
+        named_bar_sync(1, kEpi);
       } else {
         // Scales of this item were requested with cp.async while the previous item ran (the very
         // first item's just before the loop); one barrier publishes them and retires the buffer
@@ -381,11 +403,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         s_act = s_scales + sbuf * kScaleStride;
         s_ws = s_act + KB * NT;
         cp_async_wait_all();
-        named_bar_sync(1, kEpiThreads);
+        named_bar_sync(1, kEpi);
         if (u < u_end && ok) {                // u already points at the next segment
-          const Item nx = decode_item<FT, NT>(s_work, p.e_local, u / STEPS);
+          const Item nx = decode_item<FT, NT>(s_work, p.e_local, item_at(u));
           float* d_act = s_scales + (sbuf ^ 1) * kScaleStride;
-          for (int i = et; i < KB * NT; i += kEpiThreads) {
+          for (int i = et; i < KB * NT; i += kEpi) {
             const int kb = i / NT, j = i % NT;
             if (j < nx.n) cp_async_f32(d_act + i, p.act_scale + static_cast<size_t>(kb) * p.row_cap + nx.row_start + j);
           }
@@ -397,13 +419,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       }
       if (et == 0) TRACE(2, 1001);
 
-      float acc0[NT];                        // mode 1: up,   mode 2: output
-      float acc1[MODE == 1 ? NT : 1];        // mode 1: gate
+      float acc0[CN];                        // mode 1: up,   mode 2: output
+      float acc1[MODE == 1 ? CN : 1];        // mode 1: gate
 #pragma unroll
-      for (int j = 0; j < NT; ++j) acc0[j] = 0.0f;
+      for (int j = 0; j < CN; ++j) acc0[j] = 0.0f;
       if (MODE == 1) {
 #pragma unroll
-        for (int j = 0; j < NT; ++j) acc1[j] = 0.0f;
+        for (int j = 0; j < CN; ++j) acc1[j] = 0.0f;
       }
 
       for (int step = s_first; step < s_last && ok; ++step) {
@@ -413,35 +435,32 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 #pragma unroll
         for (int k = 0; k < KPS; ++k) {
           const int kb = step * KPS + k;
-          const uint32_t t0 = lane_addr + (pr * KPS + k) * (2 * NT);
+          const uint32_t t0 = lane_addr + (pr * KPS + k) * (2 * NT) + c0;
           const float ws0 = s_ws[kb];
           const float ws1 = (MODE == 1) ? s_ws[64 + kb] : 0.0f;
-          const float* sa = s_act + kb * NT;
+          const float* sa = s_act + kb * NT + c0;
+          if (c0 < n) {                       // this thread's 32 columns: four loads in flight, one wait
+            uint32_t v0[2][16], v1[2][16];
+            tmem_ld16(t0, v0[0]);
+            tmem_ld16(t0 + NT, v1[0]);
+            if (c0 + 16 < n) {
+              tmem_ld16(t0 + 16, v0[1]);
+              tmem_ld16(t0 + NT + 16, v1[1]);
+            }
+            tmem_ld_wait();
 #pragma unroll
-          for (int h = 0; h < NT / 32; ++h) {   // 32 columns at a time: four loads in flight, one wait
-            if (h * 32 < n) {
-              uint32_t v0[2][16], v1[2][16];
-              tmem_ld16(t0 + h * 32, v0[0]);
-              tmem_ld16(t0 + NT + h * 32, v1[0]);
-              if (h * 32 + 16 < n) {
-                tmem_ld16(t0 + h * 32 + 16, v0[1]);
-                tmem_ld16(t0 + NT + h * 32 + 16, v1[1]);
-              }
-              tmem_ld_wait();
+            for (int c = 0; c < 2; ++c) {
+              if (c0 + c * 16 < n) {
 #pragma unroll
-              for (int c = 0; c < 2; ++c) {
-                if (h * 32 + c * 16 < n) {
-#pragma unroll
-                  for (int j = 0; j < 16; ++j) {
-                    const int col = h * 32 + c * 16 + j;
-                    const float a = sa[col];
-                    if (MODE == 1) {
-                      acc0[col] = fmaf(__uint_as_float(v0[c][j]), a * ws0, acc0[col]);
-                      acc1[col] = fmaf(__uint_as_float(v1[c][j]), a * ws1, acc1[col]);
-                    } else {
-                      const float v = fmaf(__uint_as_float(v1[c][j]), 1.0f / kLoRatio, __uint_as_float(v0[c][j]));
-                      acc0[col] = fmaf(v, a * ws0, acc0[col]);
-                    }
+                for (int j = 0; j < 16; ++j) {
+                  const int col = c * 16 + j;
+                  const float a = sa[col];
+                  if (MODE == 1) {
+                    acc0[col] = fmaf(__uint_as_float(v0[c][j]), a * ws0, acc0[col]);
+                    acc1[col] = fmaf(__uint_as_float(v1[c][j]), a * ws1, acc1[col]);
+                  } else {
+                    const float v = fmaf(__uint_as_float(v1[c][j]), 1.0f / kLoRatio, __uint_as_float(v0[c][j]));
+                    acc0[col] = fmaf(v, a * ws0, acc0[col]);
                   }
                 }
               }
@@ -456,17 +475,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       if (et == 0) TRACE(2, 1002);
       if (s_first > 0) {
         // contribution: publish the partial sums of this segment, then signal the owner
-        // slot layout [accumulator][feature][column]: each thread owns NT contiguous floats
-        float4* slot = reinterpret_cast<float4*>(p.partial + static_cast<size_t>(blockIdx.x) * (2 * NT * 128) + feat * NT);
+        // slot layout [accumulator][feature][column]: each thread owns CN contiguous floats
+        float4* slot = reinterpret_cast<float4*>(p.partial + static_cast<size_t>(blockIdx.x) * (2 * NT * 128) + feat * NT + c0);
 #pragma unroll
-        for (int j = 0; j < NT; j += 4) {
-          if (j < n) {
+        for (int j = 0; j < CN; j += 4) {
+          if (c0 + j < n) {
             __stcg(slot + j / 4, make_float4(acc0[j], acc0[j + 1], acc0[j + 2], acc0[j + 3]));
             if (MODE == 1) __stcg(slot + (NT * 128 + j) / 4, make_float4(acc1[j], acc1[j + 1], acc1[j + 2], acc1[j + 3]));
           }
         }
         __threadfence();
-        named_bar_sync(3, kEpiThreads);
+        named_bar_sync(3, kEpi);
         if (et == 0 && ok) st_release(p.flags + blockIdx.x, p.epoch);
         continue;                             // no epilogue: the owner runs it
       }
@@ -482,12 +501,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
               __nanosleep(64);
             }
           }
-          named_bar_sync(3, kEpiThreads);
+          named_bar_sync(3, kEpi);
           if (*s_abort != 0) ok = false;
-          const float4* slot = reinterpret_cast<const float4*>(p.partial + static_cast<size_t>(cc) * (2 * NT * 128) + feat * NT);
+          const float4* slot = reinterpret_cast<const float4*>(p.partial + static_cast<size_t>(cc) * (2 * NT * 128) + feat * NT + c0);
 #pragma unroll
-          for (int j = 0; j < NT; j += 4) {
-            if (j < n && ok) {
+          for (int j = 0; j < CN; j += 4) {
+            if (c0 + j < n && ok) {
               const float4 a = __ldcg(slot + j / 4);
               acc0[j] += a.x; acc0[j + 1] += a.y; acc0[j + 2] += a.z; acc0[j + 3] += a.w;
               if (MODE == 1) {
@@ -501,18 +520,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       const int n_out = ok ? n : 0;           // a failed item stores nothing
 
       if (MODE == 1) {
-        // SwiGLU, then the per-row amax over the 128 features of this tile
+        // SwiGLU, then the per-row amax over the 128 features of this tile.  The fast exp and
+        // divide are a few ulp off the exact ones, far below the 8-bit requantisation that follows.
 #pragma unroll
-        for (int j = 0; j < NT; ++j) {
-          if (j < n_out) {
+        for (int j = 0; j < CN; ++j) {
+          if (c0 + j < n_out) {
             const float gt = acc1[j];
-            const float cv = (gt / (1.0f + expf(-gt))) * acc0[j];
+            const float cv = gt * __fdividef(1.0f, 1.0f + __expf(-gt)) * acc0[j];
             acc0[j] = cv;
             const uint32_t m = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(cv)));
-            if (lane == 0) s_red[q * NT + j] = __uint_as_float(m);
+            if (lane == 0) s_red[q * NT + c0 + j] = __uint_as_float(m);
           }
         }
-        named_bar_sync(2, kEpiThreads);
+        named_bar_sync(2, kEpi);
         if (et < n_out) {
           const float amax = fmaxf(fmaxf(s_red[et], s_red[NT + et]), fmaxf(s_red[2 * NT + et], s_red[3 * NT + et]));
           const float sc = fmaxf(amax * (1.0f / 448.0f), 1e-12f);
@@ -520,44 +540,44 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           s_inv[et] = 1.0f / sc;
           p.c_scale[static_cast<size_t>(ft) * p.row_cap + im.row_start + et] = sc;
         }
-        named_bar_sync(2, kEpiThreads);
+        named_bar_sync(2, kEpi);
         // Quantise four token rows at a time into packed bytes, transpose across the lane quad so a
         // lane holds four adjacent features of ONE row, and store 4 bytes per lane: n/4 store
         // instructions per tensor instead of n byte stores.
         const int qrow = lane & 3;              // which of the four rows this lane stores
         const size_t qoff = static_cast<size_t>(ft) * 128 + q * 32 + (lane >> 2) * 4;
 #pragma unroll
-        for (int j = 0; j < NT; j += 4) {
-          if (j < n_out) {
+        for (int j = 0; j < CN; j += 4) {
+          if (c0 + j < n_out) {
             uint32_t hp = 0, lp = 0;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
               const int c = j + 2 * h;
-              const float sc0 = s_cs[c], sc1 = s_cs[c + 1];
-              const float in0 = s_inv[c], in1 = s_inv[c + 1];
-              const float c0 = acc0[c], c1 = acc0[c + 1];
-              const uint16_t hh = cvt_e4m3x2(c0 * in0, c1 * in1);
+              const float sc0 = s_cs[c0 + c], sc1 = s_cs[c0 + c + 1];
+              const float in0 = s_inv[c0 + c], in1 = s_inv[c0 + c + 1];
+              const float v0 = acc0[c], v1 = acc0[c + 1];
+              const uint16_t hh = cvt_e4m3x2(v0 * in0, v1 * in1);
               const float2 hb = e4m3x2_to_float2(hh);
-              const float r0 = fmaf(-hb.x, sc0, c0), r1 = fmaf(-hb.y, sc1, c1);
+              const float r0 = fmaf(-hb.x, sc0, v0), r1 = fmaf(-hb.y, sc1, v1);
               const uint16_t ll = cvt_e4m3x2(r0 * in0 * kLoRatio, r1 * in1 * kLoRatio);
               hp |= static_cast<uint32_t>(hh) << (16 * h);
               lp |= static_cast<uint32_t>(ll) << (16 * h);
             }
             hp = quad_transpose_bytes(hp, lane);
             lp = quad_transpose_bytes(lp, lane);
-            const size_t off = static_cast<size_t>(im.row_start + j + qrow) * kInter + qoff;
+            const size_t off = static_cast<size_t>(im.row_start + c0 + j + qrow) * kInter + qoff;
             *reinterpret_cast<uint32_t*>(p.c_hi + off) = hp;
             *reinterpret_cast<uint32_t*>(p.c_lo + off) = lp;
           }
         }
       } else {
         const int qrow = lane & 3;
-        float* o = p.o_rows + static_cast<size_t>(im.row_start + qrow) * kHidden + ft * 128 + q * 32 + (lane >> 2) * 4;
+        float* o = p.o_rows + static_cast<size_t>(im.row_start + c0 + qrow) * kHidden + ft * 128 + q * 32 + (lane >> 2) * 4;
 #pragma unroll
-        for (int j = 0; j < NT; j += 4) {
-          if (j < n_out) {
+        for (int j = 0; j < CN; j += 4) {
+          if (c0 + j < n_out) {
             float a0 = acc0[j], a1 = acc0[j + 1], a2 = acc0[j + 2], a3 = acc0[j + 3];
-            quad_transpose_f32(a0, a1, a2, a3, lane);   // now: row j + qrow, four adjacent features
+            quad_transpose_f32(a0, a1, a2, a3, lane);   // now: row c0 + j + qrow, four adjacent features
             *reinterpret_cast<float4*>(o + static_cast<size_t>(j) * kHidden) = make_float4(a0, a1, a2, a3);
           }
         }
@@ -584,7 +604,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
 template <int MODE, int NT>
 cudaError_t launch_gemm(const GemmLaunch& g, const GemmArgs& a, int num_sms, cudaStream_t st) {
-  return launch_dependent(grouped_gemm_kernel<MODE, NT>, dim3(num_sms), dim3(kGemmThreads),
+  return launch_dependent(grouped_gemm_kernel<MODE, NT>, dim3(num_sms), dim3(Cfg<MODE, NT>::kThreads),
                           static_cast<size_t>(Cfg<MODE, NT>::kSmemBytes), st, g.tm_w, g.tm_b0, g.tm_b1, g.tm_b0s,
                           g.tm_b1s, a);
 }
@@ -608,14 +628,14 @@ cudaError_t gemm_set_attributes() {
 cudaError_t launch_gemm1(const GemmLaunch& g, const float* w13_scale, int e_local, const Workspace& ws, int num_sms,
                          int epoch, cudaStream_t st) {
   GemmArgs a{ws.work, ws.meta, ws.a_scale, w13_scale, ws.c_hi, ws.c_lo, ws.c_scale, nullptr, ws.row_cap, e_local,
-             ws.status, ws.trace, ws.trace + 6 * 4096, ws.partial, ws.flags, epoch};
+             ws.status, ws.trace, ws.trace + 6 * 4096, ws.partial, ws.flags, epoch, g.token_tile >= 64 ? 1 : 0};
   return g.token_tile == 32 ? launch_gemm<1, 32>(g, a, num_sms, st) : launch_gemm<1, 64>(g, a, num_sms, st);
 }
 
 cudaError_t launch_gemm2(const GemmLaunch& g, const float* w2_scale, int e_local, const Workspace& ws, int num_sms,
                          int epoch, cudaStream_t st) {
   GemmArgs a{ws.work, ws.meta, ws.c_scale, w2_scale, nullptr, nullptr, nullptr, ws.o_rows, ws.row_cap, e_local,
-             ws.status, ws.trace + 3 * 4096, ws.trace + 7 * 4096, ws.partial, ws.flags, epoch};
+             ws.status, ws.trace + 3 * 4096, ws.trace + 7 * 4096, ws.partial, ws.flags, epoch, g.token_tile >= 64 ? 1 : 0};
   return g.token_tile == 32 ? launch_gemm<2, 32>(g, a, num_sms, st) : launch_gemm<2, 64>(g, a, num_sms, st);
 }
 
