@@ -421,6 +421,8 @@ int syfi_moe_check(syfi_moe_ctx* ctx, int32_t* stats4, void* stream) {
     for (int i = 0; i < 4; ++i) stats4[i] = meta[i];
   if (status[0] != kStatusOk) {
     cudaMemsetAsync(ctx->ws.status, 0, sizeof(status), st);
+    cudaMemsetAsync(ctx->ws.flags, 0, kMaxGrid * sizeof(int), st);   // a failed launch may leave hand-off flags set
+    cudaMemsetAsync(ctx->ws.counts, 0, kMaxLocalExperts * sizeof(int), st);
     return fail(SYFI_MOE_ERR_DEVICE, "a kernel reported status %d (101/102/103: bounded wait expired in the TMA / MMA / "
                 "epilogue role of a grouped GEMM; 104: row or tile table overflow)", status[0]);
   }

@@ -87,8 +87,8 @@ struct GemmArgs {
   long long* trace;         // [3][4096] timeline of CTA 0 when built with SYFI_TRACE, else unused
   long long* trace_cta;     // [grid][5] per-CTA start/end (globaltimer, clock64) and SM id, SYFI_TRACE only
   float* partial;           // [grid][2 * NT * 128] split-item partial sums, one slot per CTA
-  int* flags;               // [grid] flags[c] == epoch once CTA c published its partial
-  int epoch;                // distinct for every launch that shares partial/flags
+  int* flags;               // [grid] flags[c] == 1 once CTA c published its partial; the owner clears it
+  int epoch;                // unused (kept so the argument block keeps its layout)
   int round_robin;          // schedule: 0 = contiguous unit ranges (items may split), 1 = whole items round-robin
 };
 
@@ -486,7 +486,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         }
         __threadfence();
         named_bar_sync(3, kEpi);
-        if (et == 0 && ok) st_release(p.flags + blockIdx.x, p.epoch);
+        if (et == 0 && ok) st_release(p.flags + blockIdx.x, 1);
         continue;                             // no epilogue: the owner runs it
       }
       if (s_last < STEPS) {
@@ -495,11 +495,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         for (int cc = blockIdx.x + 1; cc <= c_last; ++cc) {
           if (et == 0 && ok) {
             const long long t0 = clock64();
-            while (ld_acquire(p.flags + cc) != p.epoch) {
+            while (ld_acquire(p.flags + cc) != 1) {
               if (*s_abort != 0) break;
               if (clock64() - t0 > (1ll << 32)) { *s_abort = kStatusWaitTimeoutEpilogue; break; }
               __nanosleep(64);
             }
+            // every slot has exactly one reader (the owner of that item): clearing the flag here leaves
+            // the array all-zero for the next launch, so no per-launch value has to be passed in and a
+            // captured CUDA graph can replay the launch unchanged
+            if (*s_abort == 0) p.flags[cc] = 0;
           }
           named_bar_sync(3, kEpi);
           if (*s_abort != 0) ok = false;

@@ -21,6 +21,30 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
+class _coalesced:
+    """Batches the collectives issued inside the block into one NCCL group; a plain pass-through
+    on backends without coalescing (gloo)."""
+
+    def __init__(self, group, device):
+        self.cm = None
+        if dist.get_backend(group) == "nccl":
+            try:
+                from torch.distributed.distributed_c10d import _coalescing_manager
+                self.cm = _coalescing_manager(group=group, device=device, async_ops=False)
+            except Exception:
+                self.cm = None
+
+    def __enter__(self):
+        if self.cm is not None:
+            self.cm.__enter__()
+        return self
+
+    def __exit__(self, *exc):
+        if self.cm is not None:
+            return self.cm.__exit__(*exc)
+        return False
+
+
 def _reduce_scatter_rows(out, inp, group):
     """Sum ``inp`` [W*R, H] over ranks and leave this rank's R rows in ``out``.  NCCL does it in one
     collective; backends without reduce-scatter (gloo, used by the CPU tests) all-reduce and slice."""
@@ -111,9 +135,11 @@ class ExpertParallelMoe:
         g_logits = self._buffer("g_logits", (W * T, logits.shape[1]), logits.dtype, dev)
         g_hs = self._buffer("g_hs", (W * T, hs.shape[1]), torch.uint8, dev)
         g_sc = self._buffer("g_sc", (W * hs_scale.shape[0], T), hs_scale.dtype, dev)
-        dist.all_gather_into_tensor(g_logits, logits.contiguous(), group=self.group)
-        dist.all_gather_into_tensor(g_hs, hs.view(torch.uint8).contiguous(), group=self.group)
-        dist.all_gather_into_tensor(g_sc, hs_scale.contiguous(), group=self.group)
+        # one NCCL group launch for the three gathers (each costs a launch latency on its own)
+        with _coalesced(self.group, dev):
+            dist.all_gather_into_tensor(g_logits, logits.contiguous(), group=self.group)
+            dist.all_gather_into_tensor(g_hs, hs.view(torch.uint8).contiguous(), group=self.group)
+            dist.all_gather_into_tensor(g_sc, hs_scale.contiguous(), group=self.group)
         # scales are stored [K/128, tokens]: put the gathered ranks side by side along the token axis
         sc = g_sc.view(W, hs_scale.shape[0], T).permute(1, 0, 2).reshape(hs_scale.shape[0], W * T).contiguous()
         part = self.partial(g_logits, bias, g_hs.view(hs.dtype), sc)
