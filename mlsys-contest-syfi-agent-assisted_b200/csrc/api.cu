@@ -21,7 +21,6 @@ struct syfi_moe_ctx {
   Workspace ws;
   int num_sms = 0;
   int launches = 0;
-  int epoch = 0;          // bumped for every GEMM launch: tags the split-item hand-off flags
   // staging buffers of syfi_moe_forward_host
   void* stage = nullptr;
   size_t stage_bytes = 0;
@@ -98,7 +97,7 @@ int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uin
 
 void free_workspace(Workspace& ws) {
   void* ptrs[] = {ws.topk_idx, ws.topk_w, ws.local_mask, ws.counts, ws.meta, ws.status, ws.trace, ws.row_token, ws.route_row,
-                  ws.work, ws.a_perm, ws.a_scale, ws.c_hi, ws.c_lo, ws.c_scale, ws.o_rows, ws.partial, ws.flags};
+                  ws.work, ws.a_perm, ws.a_scale, ws.c_hi, ws.c_lo, ws.c_scale, ws.o_rows};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   const int dev = ws.device;
@@ -137,9 +136,6 @@ int alloc_workspace(Workspace& ws, int64_t max_tokens) {
   CU_TRY(dev_alloc(&ws.c_lo, row_cap * kInter, &total));
   CU_TRY(dev_alloc(&ws.c_scale, row_cap * kIBlocks, &total));
   CU_TRY(dev_alloc(&ws.o_rows, row_cap * kHidden, &total));
-  CU_TRY(dev_alloc(&ws.partial, (size_t)kMaxGrid * 2 * kMaxTokenTile * 128, &total));
-  CU_TRY(dev_alloc(&ws.flags, kMaxGrid, &total));
-  CU_TRY(cudaMemset(ws.flags, 0, kMaxGrid * sizeof(int)));
   CU_TRY(cudaMemset(ws.status, 0, 4 * sizeof(int)));
   CU_TRY(cudaMemset(ws.meta, 0, kMetaInts * sizeof(int)));
   ws.max_tokens = (int)T;
@@ -199,7 +195,6 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
   if ((rc = make_map(&g2.tm_b1s, ws.c_lo, ws.row_cap, kInter, 16))) return rc;
 
   const int grid = ctx->num_sms < kMaxGrid ? ctx->num_sms : kMaxGrid;
-  if (ctx->epoch > (1 << 30)) ctx->epoch = 0;   // flags hold older epochs only; any fresh value works
   ctx->launches = 0;
   const bool timed = ctx->timing && ctx->ev[0] != nullptr;
   ctx->timing_valid = false;
@@ -214,10 +209,10 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
   CU_TRY(launch_gather(static_cast<const uint8_t*>(hs), static_cast<const float*>(hs_scale), T, ws, st));
   ctx->launches += 1;
   STAGE_MARK(3);
-  CU_TRY(launch_gemm1(g1, static_cast<const float*>(w13_scale), e_local, ws, grid, ++ctx->epoch, st));
+  CU_TRY(launch_gemm1(g1, static_cast<const float*>(w13_scale), e_local, ws, grid, st));
   ctx->launches += 1;
   STAGE_MARK(4);
-  CU_TRY(launch_gemm2(g2, static_cast<const float*>(w2_scale), e_local, ws, grid, ++ctx->epoch, st));
+  CU_TRY(launch_gemm2(g2, static_cast<const float*>(w2_scale), e_local, ws, grid, st));
   ctx->launches += 1;
   STAGE_MARK(5);
   CU_TRY(launch_combine(T, ws, out, out_is_f32, st));
@@ -421,7 +416,6 @@ int syfi_moe_check(syfi_moe_ctx* ctx, int32_t* stats4, void* stream) {
     for (int i = 0; i < 4; ++i) stats4[i] = meta[i];
   if (status[0] != kStatusOk) {
     cudaMemsetAsync(ctx->ws.status, 0, sizeof(status), st);
-    cudaMemsetAsync(ctx->ws.flags, 0, kMaxGrid * sizeof(int), st);   // a failed launch may leave hand-off flags set
     cudaMemsetAsync(ctx->ws.counts, 0, kMaxLocalExperts * sizeof(int), st);
     return fail(SYFI_MOE_ERR_DEVICE, "a kernel reported status %d (101/102/103: bounded wait expired in the TMA / MMA / "
                 "epilogue role of a grouped GEMM; 104: row or tile table overflow)", status[0]);

@@ -86,10 +86,6 @@ struct GemmArgs {
   int* status;
   long long* trace;         // [3][4096] timeline of CTA 0 when built with SYFI_TRACE, else unused
   long long* trace_cta;     // [grid][5] per-CTA start/end (globaltimer, clock64) and SM id, SYFI_TRACE only
-  float* partial;           // [grid][2 * NT * 128] split-item partial sums, one slot per CTA
-  int* flags;               // [grid] flags[c] == 1 once CTA c published its partial; the owner clears it
-  int epoch;                // unused (kept so the argument block keeps its layout)
-  int round_robin;          // schedule: 0 = contiguous unit ranges (items may split), 1 = whole items round-robin
 };
 
 // Optional timeline trace of CTA 0 (compile with -DSYFI_TRACE): role r appends (tag, clock) pairs.
@@ -130,31 +126,12 @@ __device__ __forceinline__ Item decode_item(const ExpertWork* s_work, int e_loca
   return it;
 }
 
-// Work is cut at K-step granularity ("stream-K"): the launch's items x steps units are dealt to the
-// CTAs in contiguous, equal ranges, so every SM streams weights until the very end even when the
-// item count does not divide by the grid.  A CTA's range is a sequence of segments (item, first
-// step, last step); a segment that does not start at step 0 is a CONTRIBUTION: its partial sums go
-// to the CTA's slot in global memory.  The CTA whose range holds an item's step 0 OWNS the item: if
-// its segment stops early it adds the contributions of the following CTAs before the epilogue.  An
-// owner meets a split item only at the END of its range while contributors handle it FIRST, so the
-// owner practically never waits; the wait is bounded all the same.
-struct UnitSplit {
-  int base, rem;            // CTA c owns base + (c < rem) units
-  __device__ __forceinline__ int start(int c) const { return c * base + min(c, rem); }
-  __device__ __forceinline__ int cta_of(int u) const {
-    const int big = rem * (base + 1);
-    return u < big ? u / (base + 1) : rem + (base > 0 ? (u - big) / base : 0);
-  }
-};
-
-__device__ __forceinline__ int ld_acquire(const int* p) {
-  int v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void st_release(int* p, int v) {
-  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
+// Schedule: whole work items are dealt round-robin over the persistent grid (CTA b takes items b,
+// b + grid, ...).  With the item numbering above, the CTAs running side by side work on the token
+// tiles of the SAME weight tile, so all but one of them find it in L2.  Splitting items across CTAs
+// at K-step granularity (stream-K, static or with a dynamically claimed tail) was measured and
+// bought nothing at any batch size: the kernels are bound by aggregate HBM bandwidth, not by the
+// last wave, and the hand-off of partial sums costs what the better balance gains.
 
 template <int MODE, int NT>
 __global__ void __launch_bounds__((Cfg<MODE, NT>::kThreads), 1)
@@ -227,21 +204,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = *s_tmem;
   const int total = p.meta[0] * FT;                 // work items
-  const int units = total * STEPS;
-  const UnitSplit split{units / static_cast<int>(gridDim.x), units % static_cast<int>(gridDim.x)};
-  // Two schedules.  Few items (decode): contiguous unit ranges, items split across CTAs.  Many items
-  // (prefill): whole items dealt round-robin, so the CTAs running side by side work on the token
-  // tiles of the SAME weight tile and all but one of them find it in L2.
-  const bool rr = p.round_robin != 0;
   const int my_items = static_cast<int>(blockIdx.x) < total ? (total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
-  const int u_begin = rr ? 0 : split.start(blockIdx.x);
-  const int u_end = rr ? my_items * STEPS : split.start(blockIdx.x + 1);
-  auto item_at = [&](int u) { return rr ? static_cast<int>(blockIdx.x + (u / STEPS) * gridDim.x) : u / STEPS; };
+  const int u_begin = 0, u_end = my_items * STEPS;    // this CTA's steps, item after item
+  auto item_at = [&](int u) { return static_cast<int>(blockIdx.x + (u / STEPS) * gridDim.x); };
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (one thread)
     if (lane == 0) {
-      const uint64_t pol_w = rr ? l2_policy_evict_last() : l2_policy_evict_first();
+      // a weight tile is re-read by the other token tiles of its expert (from L2) only when the
+      // expert has several tiles; with a single tile per expert it is streamed exactly once
+      const uint64_t pol_w = p.meta[0] > p.meta[3] ? l2_policy_evict_last() : l2_policy_evict_first();
       const uint64_t pol_b = l2_policy_evict_last();
       uint32_t it = 0, g = 0, ph = 0;      // step counter, ring entry, its phase
       bool alive = true;
@@ -342,7 +314,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     static_assert(CN == 32, "the drain below moves 32 columns per thread and step");
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     const int c0 = ((warp - 2) >> 2) * CN;  // first column of this thread's share
-    const int feat = q * 32 + lane;         // feature (row of the weight tile) of this thread
     const int et = threadIdx.x - 64;        // 0..kEpi-1 among the epilogue threads
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
     uint32_t pr = 0, pph = 0;               // TMEM ring entry and its phase
@@ -473,54 +444,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         if (++pr == PAIRS) { pr = 0; pph ^= 1u; }
       }
       if (et == 0) TRACE(2, 1002);
-      if (s_first > 0) {
-        // contribution: publish the partial sums of this segment, then signal the owner
-        // slot layout [accumulator][feature][column]: each thread owns CN contiguous floats
-        float4* slot = reinterpret_cast<float4*>(p.partial + static_cast<size_t>(blockIdx.x) * (2 * NT * 128) + feat * NT + c0);
-#pragma unroll
-        for (int j = 0; j < CN; j += 4) {
-          if (c0 + j < n) {
-            __stcg(slot + j / 4, make_float4(acc0[j], acc0[j + 1], acc0[j + 2], acc0[j + 3]));
-            if (MODE == 1) __stcg(slot + (NT * 128 + j) / 4, make_float4(acc1[j], acc1[j + 1], acc1[j + 2], acc1[j + 3]));
-          }
-        }
-        __threadfence();
-        named_bar_sync(3, kEpi);
-        if (et == 0 && ok) st_release(p.flags + blockIdx.x, 1);
-        continue;                             // no epilogue: the owner runs it
-      }
-      if (s_last < STEPS) {
-        // owner of a split item: add what the following CTAs computed for steps s_last .. STEPS-1
-        const int c_last = split.cta_of((w + 1) * STEPS - 1);
-        for (int cc = blockIdx.x + 1; cc <= c_last; ++cc) {
-          if (et == 0 && ok) {
-            const long long t0 = clock64();
-            while (ld_acquire(p.flags + cc) != 1) {
-              if (*s_abort != 0) break;
-              if (clock64() - t0 > (1ll << 32)) { *s_abort = kStatusWaitTimeoutEpilogue; break; }
-              __nanosleep(64);
-            }
-            // every slot has exactly one reader (the owner of that item): clearing the flag here leaves
-            // the array all-zero for the next launch, so no per-launch value has to be passed in and a
-            // captured CUDA graph can replay the launch unchanged
-            if (*s_abort == 0) p.flags[cc] = 0;
-          }
-          named_bar_sync(3, kEpi);
-          if (*s_abort != 0) ok = false;
-          const float4* slot = reinterpret_cast<const float4*>(p.partial + static_cast<size_t>(cc) * (2 * NT * 128) + feat * NT + c0);
-#pragma unroll
-          for (int j = 0; j < CN; j += 4) {
-            if (c0 + j < n && ok) {
-              const float4 a = __ldcg(slot + j / 4);
-              acc0[j] += a.x; acc0[j + 1] += a.y; acc0[j + 2] += a.z; acc0[j + 3] += a.w;
-              if (MODE == 1) {
-                const float4 b = __ldcg(slot + (NT * 128 + j) / 4);
-                acc1[j] += b.x; acc1[j + 1] += b.y; acc1[j + 2] += b.z; acc1[j + 3] += b.w;
-              }
-            }
-          }
-        }
-      }
       const int n_out = ok ? n : 0;           // a failed item stores nothing
 
       if (MODE == 1) {
@@ -630,16 +553,16 @@ cudaError_t gemm_set_attributes() {
 }
 
 cudaError_t launch_gemm1(const GemmLaunch& g, const float* w13_scale, int e_local, const Workspace& ws, int num_sms,
-                         int epoch, cudaStream_t st) {
+                         cudaStream_t st) {
   GemmArgs a{ws.work, ws.meta, ws.a_scale, w13_scale, ws.c_hi, ws.c_lo, ws.c_scale, nullptr, ws.row_cap, e_local,
-             ws.status, ws.trace, ws.trace + 6 * 4096, ws.partial, ws.flags, epoch, g.token_tile >= 64 ? 1 : 0};
+             ws.status, ws.trace, ws.trace + 6 * 4096};
   return g.token_tile == 32 ? launch_gemm<1, 32>(g, a, num_sms, st) : launch_gemm<1, 64>(g, a, num_sms, st);
 }
 
 cudaError_t launch_gemm2(const GemmLaunch& g, const float* w2_scale, int e_local, const Workspace& ws, int num_sms,
-                         int epoch, cudaStream_t st) {
+                         cudaStream_t st) {
   GemmArgs a{ws.work, ws.meta, ws.c_scale, w2_scale, nullptr, nullptr, nullptr, ws.o_rows, ws.row_cap, e_local,
-             ws.status, ws.trace + 3 * 4096, ws.trace + 7 * 4096, ws.partial, ws.flags, epoch, g.token_tile >= 64 ? 1 : 0};
+             ws.status, ws.trace + 3 * 4096, ws.trace + 7 * 4096};
   return g.token_tile == 32 ? launch_gemm<2, 32>(g, a, num_sms, st) : launch_gemm<2, 64>(g, a, num_sms, st);
 }
 

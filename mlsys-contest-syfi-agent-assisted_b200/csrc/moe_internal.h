@@ -72,9 +72,6 @@ struct Workspace {
   uint8_t* c_lo = nullptr;        // [row_cap, 2048] e4m3 residual term (scale = c_scale / 28)
   float* c_scale = nullptr;       // [16, row_cap]
   float* o_rows = nullptr;        // [row_cap, 7168] f32 per-route expert outputs
-  // split-item hand-off of the GEMM kernels (one slot per CTA of the persistent grid)
-  float* partial = nullptr;       // [kMaxGrid][2 * kMaxTokenTile * 128]
-  int* flags = nullptr;           // [kMaxGrid] launch epoch of the slot's current content
   size_t bytes = 0;
 };
 
@@ -115,9 +112,9 @@ cudaError_t launch_build_rows(int T, int e_local, int expert_offset, int token_t
 cudaError_t launch_gather(const uint8_t* hidden, const float* hidden_scale, int T, const Workspace& ws,
                           cudaStream_t st);
 cudaError_t launch_gemm1(const GemmLaunch& g, const float* w13_scale, int e_local, const Workspace& ws, int num_sms,
-                         int epoch, cudaStream_t st);
+                         cudaStream_t st);
 cudaError_t launch_gemm2(const GemmLaunch& g, const float* w2_scale, int e_local, const Workspace& ws, int num_sms,
-                         int epoch, cudaStream_t st);
+                         cudaStream_t st);
 cudaError_t launch_combine(int T, const Workspace& ws, void* out, int out_is_f32, cudaStream_t st);
 cudaError_t gemm_set_attributes();
 

@@ -154,6 +154,23 @@ def test_deterministic_and_workspace_reuse(pkg):
     assert torch.equal(a.view(torch.int16), b.view(torch.int16))
 
 
+def test_cuda_graph_replay(pkg):
+    """The call enqueues only stream work (no host synchronisation, no per-call device state passed by
+    value), so it can be captured once and replayed; replays reproduce the eager result bit for bit."""
+    inp = pkg.make_inputs(num_tokens=48, seed=17, e_local=16, device=DEV)
+    eager, _ = _run(pkg, inp)
+    out = torch.empty_like(eager)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        pkg.run_moe(*inp.args(), out)
+    for _ in range(3):
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(out.view(torch.int16), eager.view(torch.int16))
+    pkg.get_context(0).check()
+
+
 def test_scaling_factor_is_linear_exactly(pkg):
     """Doubling routed_scaling_factor doubles every f32 partial exactly (power-of-two scaling
     commutes with every rounding on the path), a size-independent property checked at T = 2048."""
