@@ -7,6 +7,7 @@
 // persistent GEMM kernels read their work count from device memory.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <new>
@@ -179,9 +180,14 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
   const int T = (int)T64;
   GemmLaunch g1, g2;
   int rc;
-  // Token tile (MMA N) of this call's GEMMs: 32 rows while the average expert sees few tokens
-  // (8 accumulator slots in flight hide the TMEM round trip), 64 rows otherwise.
-  const int token_tile = (T64 <= 256) ? 32 : 64;
+  // Token tile (MMA N) of this call's GEMMs, chosen from the batch size because the per-expert counts
+  // only exist on the device: 32 rows while the layer is bound by streaming weights (measured faster up
+  // to 1024 tokens: 8 accumulator slots in flight, two K blocks per barrier round), 64 rows beyond.
+  int token_tile = (T64 <= 1024) ? 32 : 64;
+  if (const char* ov = getenv("SYFI_MOE_TOKEN_TILE")) {   // tuning knob: force 32 or 64
+    const int v = atoi(ov);
+    if (v == 32 || v == 64) token_tile = v;
+  }
   g1.token_tile = g2.token_tile = token_tile;
   if ((rc = make_map(&g1.tm_w, w13, (uint64_t)e_local * 2 * kInter, kHidden, 128))) return rc;
   if ((rc = make_map(&g1.tm_b0, ws.a_perm, ws.row_cap, kHidden, token_tile))) return rc;

@@ -81,7 +81,7 @@ def test_row_lists(T, E, off, pkg):
     # per-expert work table: row ranges tile the padded row space, token tiles are counted consistently
     work, _ = ctx.debug_read("expert_work", torch.int32)
     work = work.view(32, 4)[:E]
-    tile = 32 if T <= 256 else 64
+    tile = 32 if T <= 1024 else 64
     bounds = torch.cumsum(torch.cat([torch.zeros(1, dtype=torch.long), pad]), 0)
     tile_off = 0
     for e, (row_off, rows_pad, t_off, tiles) in enumerate(work.tolist()):
