@@ -25,6 +25,17 @@ struct syfi_moe_ctx {
   // staging buffers of syfi_moe_forward_host
   void* stage = nullptr;
   size_t stage_bytes = 0;
+  // tensor maps of the last call: they only depend on the operand addresses, the expert count and
+  // the token tile, which rarely change between calls (re-encoding costs a few microseconds of host time)
+  GemmLaunch g1, g2;
+  const void* map_w13 = nullptr;
+  const void* map_w2 = nullptr;
+  const void* map_ws = nullptr;      // workspace generation the maps were built for (a_perm pointer)
+  int map_e_local = 0, map_token_tile = 0;
+  // second stream of syfi_moe_forward_host: the hidden states travel while the router runs
+  cudaStream_t copy_stream = nullptr;
+  cudaEvent_t ev_copy_begin = nullptr, ev_copy_done = nullptr;
+  cudaEvent_t wait_before_gather = nullptr;   // set by forward_host for one call
   // optional per-kernel timing
   bool timing = false;
   bool timing_valid = false;
@@ -170,6 +181,7 @@ int ensure_capacity(syfi_moe_ctx* ctx, int64_t T) {
   if (T <= ctx->ws.max_tokens) return SYFI_MOE_OK;
   // growing frees buffers that earlier calls may still be using
   CU_TRY(cudaDeviceSynchronize());
+  ctx->map_w13 = nullptr;   // cached tensor maps point into the old workspace
   return alloc_workspace(ctx->ws, T);
 }
 
@@ -178,7 +190,8 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
               int32_t e_local, int64_t offset, double scaling, void* out, int out_is_f32, cudaStream_t st) {
   Workspace& ws = ctx->ws;
   const int T = (int)T64;
-  GemmLaunch g1, g2;
+  GemmLaunch& g1 = ctx->g1;
+  GemmLaunch& g2 = ctx->g2;
   int rc;
   // Token tile (MMA N) of this call's GEMMs, chosen from the batch size because the per-expert counts
   // only exist on the device: 32 rows while the layer is bound by streaming weights (measured faster up
@@ -188,6 +201,10 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
     const int v = atoi(ov);
     if (v == 32 || v == 64) token_tile = v;
   }
+  const bool maps_valid = ctx->map_w13 == w13 && ctx->map_w2 == w2 && ctx->map_ws == ws.a_perm &&
+                          ctx->map_e_local == e_local && ctx->map_token_tile == token_tile;
+  if (!maps_valid) {
+  ctx->map_w13 = nullptr;
   g1.token_tile = g2.token_tile = token_tile;
   if ((rc = make_map(&g1.tm_w, w13, (uint64_t)e_local * 2 * kInter, kHidden, 128))) return rc;
   if ((rc = make_map(&g1.tm_b0, ws.a_perm, ws.row_cap, kHidden, token_tile))) return rc;
@@ -199,6 +216,12 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
   if ((rc = make_map(&g2.tm_b1, ws.c_lo, ws.row_cap, kInter, token_tile))) return rc;
   if ((rc = make_map(&g2.tm_b0s, ws.c_hi, ws.row_cap, kInter, 16))) return rc;
   if ((rc = make_map(&g2.tm_b1s, ws.c_lo, ws.row_cap, kInter, 16))) return rc;
+  ctx->map_w13 = w13;
+  ctx->map_w2 = w2;
+  ctx->map_ws = ws.a_perm;
+  ctx->map_e_local = e_local;
+  ctx->map_token_tile = token_tile;
+  }
 
   const int grid = ctx->num_sms < kMaxGrid ? ctx->num_sms : kMaxGrid;
   ctx->launches = 0;
@@ -212,6 +235,10 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
   CU_TRY(launch_build_rows(T, e_local, (int)offset, token_tile, ws, st));
   ctx->launches += 1;
   STAGE_MARK(2);
+  if (ctx->wait_before_gather) {    // hidden states still on their way from the host (forward_host)
+    CU_TRY(cudaStreamWaitEvent(st, ctx->wait_before_gather, 0));
+    ctx->wait_before_gather = nullptr;
+  }
   CU_TRY(launch_gather(static_cast<const uint8_t*>(hs), static_cast<const float*>(hs_scale), T, ws, st));
   ctx->launches += 1;
   STAGE_MARK(3);
@@ -296,6 +323,9 @@ int syfi_moe_destroy(syfi_moe_ctx* ctx) {
     if (ctx->stage) cudaFree(ctx->stage);
     for (cudaEvent_t e : ctx->ev)
       if (e) cudaEventDestroy(e);
+    if (ctx->ev_copy_begin) cudaEventDestroy(ctx->ev_copy_begin);
+    if (ctx->ev_copy_done) cudaEventDestroy(ctx->ev_copy_done);
+    if (ctx->copy_stream) cudaStreamDestroy(ctx->copy_stream);
   }
   delete ctx;
   return SYFI_MOE_OK;
@@ -359,14 +389,29 @@ int syfi_moe_forward_host(syfi_moe_ctx* ctx, const void* routing_logits_host, co
   }
   DeviceGuard guard(ctx->ws.device);
   char* base = static_cast<char*>(ctx->stage);
+  if (!ctx->copy_stream) {
+    CU_TRY(cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
+    CU_TRY(cudaEventCreateWithFlags(&ctx->ev_copy_begin, cudaEventDisableTiming));
+    CU_TRY(cudaEventCreateWithFlags(&ctx->ev_copy_done, cudaEventDisableTiming));
+  }
+  // router inputs on the caller's stream; hidden states and their scales on a second stream, ordered
+  // after whatever the caller's stream did before, and awaited just before the gather kernel
+  CU_TRY(cudaEventRecord(ctx->ev_copy_begin, st));
+  CU_TRY(cudaStreamWaitEvent(ctx->copy_stream, ctx->ev_copy_begin, 0));
   CU_TRY(cudaMemcpyAsync(base + o_logits, routing_logits_host, b_logits, cudaMemcpyHostToDevice, st));
   CU_TRY(cudaMemcpyAsync(base + o_bias, routing_bias_host, b_bias, cudaMemcpyHostToDevice, st));
-  CU_TRY(cudaMemcpyAsync(base + o_hs, hidden_states_host, b_hs, cudaMemcpyHostToDevice, st));
-  CU_TRY(cudaMemcpyAsync(base + o_hss, hidden_states_scale_host, b_hss, cudaMemcpyHostToDevice, st));
+  CU_TRY(cudaMemcpyAsync(base + o_hs, hidden_states_host, b_hs, cudaMemcpyHostToDevice, ctx->copy_stream));
+  CU_TRY(cudaMemcpyAsync(base + o_hss, hidden_states_scale_host, b_hss, cudaMemcpyHostToDevice, ctx->copy_stream));
+  CU_TRY(cudaEventRecord(ctx->ev_copy_done, ctx->copy_stream));
+  ctx->wait_before_gather = ctx->ev_copy_done;
   int rc = forward_common(ctx, base + o_logits, base + o_bias, base + o_hs, base + o_hss, gemm1_weights,
                           gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, T, num_local_experts,
                           local_expert_offset, routed_scaling_factor, base + o_out, 0, stream);
-  if (rc) return rc;
+  if (rc) {
+    ctx->wait_before_gather = nullptr;
+    cudaStreamWaitEvent(st, ctx->ev_copy_done, 0);   // keep the second stream ordered even on failure
+    return rc;
+  }
   CU_TRY(cudaMemcpyAsync(output_host, base + o_out, b_out, cudaMemcpyDeviceToHost, st));
   CU_TRY(cudaStreamSynchronize(st));
   return SYFI_MOE_OK;
