@@ -215,6 +215,7 @@ def main():
     ctx = pkg.get_context(local_rank, T * world)
     out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
 
+    peer_ok = False
     if world == 1:
         def step():
             pkg.run_moe(*inp.args(), out)
@@ -222,6 +223,14 @@ def main():
     else:
         ep = pkg.ExpertParallelMoe(inp.gemm1_weights, inp.gemm1_weights_scale, inp.gemm2_weights,
                                    inp.gemm2_weights_scale, inp.local_expert_offset, inp.routed_scaling_factor)
+        # token all-gather and reduce-scatter through the library's own peer-memory kernels when the
+        # ranks can map each other's memory, NCCL collectives otherwise
+        peer_ok = ep.enable_peer_exchange(T, dev)
+        flag = torch.tensor([1 if peer_ok else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            ep._peer = None
+            peer_ok = False
 
         def step():
             ep.forward_sharded(inp.routing_logits, inp.routing_bias, inp.hidden_states, inp.hidden_states_scale, out)
@@ -318,7 +327,8 @@ def main():
             "data": "synthetic",
             "config": {"workload": (f"decode batch T={T} per rank, 32 local experts per rank of 256 global, seed = rank"
                                     + ("" if world == 1 else f"; expert parallel over {world} ranks: all-gather tokens, "
-                                       "reduce-scatter f32 partials")),
+                                       "reduce-scatter f32 partials ("
+                                       + ("own kernels over peer memory" if peer_ok else "NCCL") + ")")),
                        "tokens_per_rank": T, "local_experts": 32, "routes": rows, "active_experts": active,
                        "l2": f"inputs larger than L2: {active * 44050944 / 1e6:.0f} MB of active-expert weights per step",
                        "layer_algorithmic_bytes": layer_bytes, "layer_flops": flops,

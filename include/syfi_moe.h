@@ -94,6 +94,36 @@ int syfi_moe_route(syfi_moe_ctx* ctx, const void* routing_logits, const void* ro
                    int32_t num_local_experts, int64_t local_expert_offset, double routed_scaling_factor,
                    int32_t* topk_idx, float* topk_weights, void* stream);
 
+/* Expert parallelism over peer memory: one step of the serving layout (every rank brings its own
+ * tokens_per_rank tokens and owns num_local_experts experts starting at local_expert_offset), with the
+ * token all-gather and the reduce-scatter of the partial outputs done by this library's own kernels
+ * through plain loads and stores on NVLink-mapped peer memory instead of NCCL (the reference has no
+ * multi-GPU path at all; its only hook is local_expert_offset, moe.cu:182-185, 250-256).
+ *   region[r]   rank r's symmetric region as mapped into THIS process (region[rank] is the local one);
+ *               every rank allocates syfi_moe_ep_region_bytes(world_size, tokens_per_rank) bytes,
+ *               zero-fills them and exchanges the mappings before the first step (the Python mirror
+ *               uses torch's symmetric memory for that).
+ *   step        1, 2, 3, ... — the same on every rank, increased by one per call; it tags the flags the
+ *               ranks raise for each other and selects one of two buffer sets, so consecutive steps need
+ *               no barrier.
+ * Inputs are this rank's OWN token-side tensors (device pointers, shapes as in syfi_moe_forward with
+ * T = tokens_per_rank) and its expert weights; output is bf16 [tokens_per_rank, 7168]: this rank's tokens
+ * summed over all ranks' experts, rounded once.  Waits on other ranks are bounded (about a second);
+ * syfi_moe_check then reports status 105. */
+#define SYFI_MOE_EP_MAX_RANKS 8
+typedef struct syfi_moe_ep_desc {
+  int32_t world_size;
+  int32_t rank;
+  int64_t tokens_per_rank;
+  void* region[SYFI_MOE_EP_MAX_RANKS];
+} syfi_moe_ep_desc;
+int64_t syfi_moe_ep_region_bytes(int32_t world_size, int64_t tokens_per_rank);
+int syfi_moe_ep_forward(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep, int64_t step, const void* routing_logits,
+                        const void* routing_bias, const void* hidden_states, const void* hidden_states_scale,
+                        const void* gemm1_weights, const void* gemm1_weights_scale, const void* gemm2_weights,
+                        const void* gemm2_weights_scale, int32_t num_local_experts, int64_t local_expert_offset,
+                        double routed_scaling_factor, void* output, void* stream);
+
 /* Router for callers that cannot allocate device memory (no counterpart in the reference, which
  * allocates its workspace with cudaMalloc on first use, moe.cu:2863-2926).  Same result as
  * syfi_moe_route, but it needs no context and calls no cudaMalloc / cudaFree or any other allocating

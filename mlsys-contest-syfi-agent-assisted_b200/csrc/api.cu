@@ -36,6 +36,9 @@ struct syfi_moe_ctx {
   cudaStream_t copy_stream = nullptr;
   cudaEvent_t ev_copy_begin = nullptr, ev_copy_done = nullptr;
   cudaEvent_t wait_before_gather = nullptr;   // set by forward_host for one call
+  // gathered token-side tensors of the peer-memory expert-parallel path
+  void* ep_gather = nullptr;
+  size_t ep_gather_bytes = 0;
   // optional per-kernel timing
   bool timing = false;
   bool timing_valid = false;
@@ -109,7 +112,7 @@ int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uin
 
 void free_workspace(Workspace& ws) {
   void* ptrs[] = {ws.topk_idx, ws.topk_w, ws.local_mask, ws.counts, ws.meta, ws.status, ws.trace, ws.row_token, ws.route_row,
-                  ws.work, ws.a_perm, ws.a_scale, ws.c_hi, ws.c_lo, ws.c_scale, ws.o_rows};
+                  ws.work, ws.a_perm, ws.a_scale, ws.c_hi, ws.c_lo, ws.c_scale, ws.o_rows, ws.ep_ticket};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   const int dev = ws.device;
@@ -148,6 +151,8 @@ int alloc_workspace(Workspace& ws, int64_t max_tokens) {
   CU_TRY(dev_alloc(&ws.c_lo, row_cap * kInter, &total));
   CU_TRY(dev_alloc(&ws.c_scale, row_cap * kIBlocks, &total));
   CU_TRY(dev_alloc(&ws.o_rows, row_cap * kHidden, &total));
+  CU_TRY(dev_alloc(&ws.ep_ticket, 4, &total));
+  CU_TRY(cudaMemset(ws.ep_ticket, 0, 4 * sizeof(int)));
   CU_TRY(cudaMemset(ws.status, 0, 4 * sizeof(int)));
   CU_TRY(cudaMemset(ws.meta, 0, kMetaInts * sizeof(int)));
   ws.max_tokens = (int)T;
@@ -248,8 +253,10 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
   CU_TRY(launch_gemm2(g2, static_cast<const float*>(w2_scale), e_local, ws, grid, st));
   ctx->launches += 1;
   STAGE_MARK(5);
-  CU_TRY(launch_combine(T, ws, out, out_is_f32, st));
-  ctx->launches += 1;
+  if (out != nullptr) {   // the expert-parallel path combines straight into the owners' memory instead
+    CU_TRY(launch_combine(T, ws, out, out_is_f32, st));
+    ctx->launches += 1;
+  }
   STAGE_MARK(6);
 #undef STAGE_MARK
   ctx->timing_valid = timed;
@@ -321,6 +328,7 @@ int syfi_moe_destroy(syfi_moe_ctx* ctx) {
     cudaDeviceSynchronize();
     free_workspace(ctx->ws);
     if (ctx->stage) cudaFree(ctx->stage);
+    if (ctx->ep_gather) cudaFree(ctx->ep_gather);
     for (cudaEvent_t e : ctx->ev)
       if (e) cudaEventDestroy(e);
     if (ctx->ev_copy_begin) cudaEventDestroy(ctx->ev_copy_begin);
@@ -417,6 +425,59 @@ int syfi_moe_forward_host(syfi_moe_ctx* ctx, const void* routing_logits_host, co
   return SYFI_MOE_OK;
 }
 
+int64_t syfi_moe_ep_region_bytes(int32_t world_size, int64_t tokens_per_rank) {
+  if (world_size < 1 || world_size > SYFI_MOE_EP_MAX_RANKS || tokens_per_rank < 1 || tokens_per_rank > (1 << 20)) return 0;
+  return (int64_t)ep_region_bytes(world_size, tokens_per_rank);
+}
+
+int syfi_moe_ep_forward(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep, int64_t step, const void* routing_logits,
+                        const void* routing_bias, const void* hidden_states, const void* hidden_states_scale,
+                        const void* gemm1_weights, const void* gemm1_weights_scale, const void* gemm2_weights,
+                        const void* gemm2_weights_scale, int32_t num_local_experts, int64_t local_expert_offset,
+                        double routed_scaling_factor, void* output, void* stream) {
+  if (!ep) return fail(SYFI_MOE_ERR_INVALID, "ep descriptor is null");
+  const int W = ep->world_size;
+  const int64_t T = ep->tokens_per_rank;
+  if (W < 1 || W > SYFI_MOE_EP_MAX_RANKS) return fail(SYFI_MOE_ERR_INVALID, "world_size %d outside [1, %d]", W, SYFI_MOE_EP_MAX_RANKS);
+  if (ep->rank < 0 || ep->rank >= W) return fail(SYFI_MOE_ERR_INVALID, "rank %d outside the world of %d", ep->rank, W);
+  if (T < 1 || T * W > (1 << 24)) return fail(SYFI_MOE_ERR_INVALID, "tokens_per_rank %lld out of range", (long long)T);
+  if (step < 1 || step > 0x7fffffff) return fail(SYFI_MOE_ERR_INVALID, "step must count up from 1");
+  for (int r = 0; r < W; ++r)
+    if (!ep->region[r] || !aligned16(ep->region[r])) return fail(SYFI_MOE_ERR_INVALID, "region[%d] is null or misaligned", r);
+  const void* ptrs[] = {routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                        gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, output};
+  int rc = validate(ctx, ptrs, 9, T * W, num_local_experts, local_expert_offset, routed_scaling_factor);
+  if (rc) return rc;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard guard(ctx->ws.device);
+  if (!guard.ok) return fail(SYFI_MOE_ERR_CUDA, "cannot select device %d", ctx->ws.device);
+  if ((rc = ensure_capacity(ctx, T * W))) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // local gathered tensors: logits [W*T, 256] f32 | hidden [W*T, 7168] e4m3 | scales [56, W*T] f32
+  auto up = [](size_t v) { return (v + 255) / 256 * 256; };
+  const size_t NT = (size_t)T * W;
+  const size_t o_hs = up(NT * kExpertsGlobal * 4), o_sc = o_hs + up(NT * kHidden), need = o_sc + up(NT * kHBlocks * 4);
+  if (need > ctx->ep_gather_bytes) {
+    CU_TRY(cudaDeviceSynchronize());
+    if (ctx->ep_gather) cudaFree(ctx->ep_gather);
+    ctx->ep_gather = nullptr;
+    ctx->ep_gather_bytes = 0;
+    CU_TRY(cudaMalloc(&ctx->ep_gather, need));
+    ctx->ep_gather_bytes = need;
+  }
+  char* g = static_cast<char*>(ctx->ep_gather);
+  const uint32_t seq = (uint32_t)step;
+  CU_TRY(launch_ep_publish_gather(*ep, seq, routing_logits, hidden_states, hidden_states_scale, g, g + o_hs, g + o_sc,
+                                  ctx->ws.ep_ticket, ctx->ws.status, st));
+  rc = run_layer(ctx, g, routing_bias, g + o_hs, g + o_sc, gemm1_weights, gemm1_weights_scale, gemm2_weights,
+                 gemm2_weights_scale, (int64_t)NT, num_local_experts, local_expert_offset, routed_scaling_factor,
+                 nullptr, 0, st);
+  if (rc) return rc;
+  CU_TRY(launch_ep_push_final(*ep, seq, ctx->ws, output, ctx->ws.ep_ticket, st));
+  ctx->launches += 4;
+  return SYFI_MOE_OK;
+}
+
 int syfi_moe_route(syfi_moe_ctx* ctx, const void* routing_logits, const void* routing_bias, int64_t num_tokens,
                    int32_t num_local_experts, int64_t local_expert_offset, double routed_scaling_factor,
                    int32_t* topk_idx, float* topk_weights, void* stream) {
@@ -469,7 +530,7 @@ int syfi_moe_check(syfi_moe_ctx* ctx, int32_t* stats4, void* stream) {
     cudaMemsetAsync(ctx->ws.status, 0, sizeof(status), st);
     cudaMemsetAsync(ctx->ws.counts, 0, kMaxLocalExperts * sizeof(int), st);
     return fail(SYFI_MOE_ERR_DEVICE, "a kernel reported status %d (101/102/103: bounded wait expired in the TMA / MMA / "
-                "epilogue role of a grouped GEMM; 104: row or tile table overflow)", status[0]);
+                "epilogue role of a grouped GEMM; 104: row or tile table overflow; 105: a peer rank's flag did not arrive)", status[0]);
   }
   return SYFI_MOE_OK;
 }

@@ -1,0 +1,267 @@
+// Expert-parallel exchange over peer memory (NVLink), fused with the layer's own kernels.
+//
+// The reference has no multi-GPU path (its only hook is local_expert_offset,
+// moe/solution/cuda/moe.cu:182-185, 250-256).  In the serving layout every rank brings its own T
+// tokens and owns 32 experts; a step is
+//     all-gather token-side tensors -> layer on W*T tokens (partial rows) -> reduce-scatter -> bf16.
+// Instead of two NCCL collectives plus glue kernels, four small kernels work directly on a
+// symmetric memory region every rank maps from every other rank (plain peer loads and stores, no
+// multicast of any kind):
+//   publish : copy this rank's logits / hidden states / scales into its region, then raise
+//             in_flag[me] = seq on every rank
+//   gather  : per source rank, wait for its flag, PULL its block into the local gathered tensors
+//             (the scales land directly in the [56, W*T] layout the layer wants)
+//   push    : the weighted combine of the layer, but the f32 row of a token goes straight into the
+//             receive slot [me][token] of the rank that owns the token; tokens with no local route
+//             send nothing (a one-word presence mark); then raise out_flag[me] = seq on every rank
+//   final   : wait for all out flags, add the present slots in rank order, round to bf16 once
+// Flags carry the caller's monotonically increasing step number, buffers are double buffered by its
+// parity, so no barrier is needed between steps: a rank can only be one step ahead of a peer because
+// its own next final depends on that peer's push.  Every flag wait is bounded; on expiry the kernel
+// records status 105 and returns.
+#include <cuda_bf16.h>
+
+#include "../../include/syfi_moe.h"
+#include "moe_internal.h"
+#include "ptx.cuh"
+
+namespace syfi {
+
+namespace {
+
+constexpr int kMaxRanks = SYFI_MOE_EP_MAX_RANKS;
+constexpr long long kFlagWaitCycles = 1ll << 31;     // about a second
+
+struct EpView {
+  uint8_t* base[kMaxRanks];   // every rank's region, as mapped into this process
+  int world, rank, T;
+  size_t in_off[2], recv_off[2], has_off[2], flag_off;
+};
+
+__host__ __device__ inline size_t align256(size_t v) { return (v + 255) / 256 * 256; }
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// true once *flag >= seq (step numbers only grow); false after the cycle budget
+__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t seq) {
+  const long long t0 = clock64();
+  while (static_cast<int>(ld_acquire_sys(flag) - seq) < 0) {
+    if (clock64() - t0 > kFlagWaitCycles) return false;
+    __nanosleep(100);
+  }
+  return true;
+}
+
+__device__ __forceinline__ uint32_t* in_flag(const EpView& v, int on_rank, int src) {
+  return reinterpret_cast<uint32_t*>(v.base[on_rank] + v.flag_off) + src;
+}
+__device__ __forceinline__ uint32_t* out_flag(const EpView& v, int on_rank, int src) {
+  return reinterpret_cast<uint32_t*>(v.base[on_rank] + v.flag_off) + kMaxRanks + src;
+}
+
+// ------------------------------------------------------------------------------ publish
+__global__ void __launch_bounds__(256)
+ep_publish_kernel(EpView v, uint32_t seq, const uint4* __restrict__ logits, const uint4* __restrict__ hs,
+                  const uint4* __restrict__ scale, int* __restrict__ ticket) {
+  const int T = v.T;
+  uint4* dst = reinterpret_cast<uint4*>(v.base[v.rank] + v.in_off[seq & 1]);
+  const size_t n_logits = static_cast<size_t>(T) * 64, n_hs = static_cast<size_t>(T) * 448, n_sc = static_cast<size_t>(T) * 14;
+  const size_t total = n_logits + n_hs + n_sc;
+  for (size_t i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    uint4 x;
+    if (i < n_logits) x = __ldg(logits + i);
+    else if (i < n_logits + n_hs) x = __ldg(hs + (i - n_logits));
+    else x = __ldg(scale + (i - n_logits - n_hs));
+    dst[i] = x;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (atomicAdd(ticket, 1) == static_cast<int>(gridDim.x) - 1) {   // last CTA: everything is written
+      *ticket = 0;
+      __threadfence_system();
+      for (int r = 0; r < v.world; ++r) st_release_sys(in_flag(v, r, v.rank), seq);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------- gather
+// grid = (chunks, world): blockIdx.y is the source rank
+__global__ void __launch_bounds__(256)
+ep_gather_kernel(EpView v, uint32_t seq, uint4* __restrict__ g_logits, uint4* __restrict__ g_hs,
+                 float* __restrict__ g_scale, int* __restrict__ status) {
+  __shared__ int s_ok;
+  const int src = blockIdx.y, T = v.T, W = v.world;
+  if (threadIdx.x == 0) {
+    s_ok = wait_flag(in_flag(v, v.rank, src), seq) ? 1 : 0;
+    if (!s_ok) atomicExch(status, kStatusPeerTimeout);
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const uint4* in = reinterpret_cast<const uint4*>(v.base[src] + v.in_off[seq & 1]);
+  const size_t n_logits = static_cast<size_t>(T) * 64, n_hs = static_cast<size_t>(T) * 448;
+  const size_t n_sc = static_cast<size_t>(T) * 56;   // floats
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n_logits; i += stride)
+    g_logits[static_cast<size_t>(src) * n_logits + i] = in[i];
+  for (size_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n_hs; i += stride)
+    g_hs[static_cast<size_t>(src) * n_hs + i] = in[n_logits + i];
+  const float* sc = reinterpret_cast<const float*>(in + n_logits + n_hs);   // [56][T] on the source
+  for (size_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n_sc; i += stride) {
+    const int kb = static_cast<int>(i / T), t = static_cast<int>(i % T);
+    g_scale[static_cast<size_t>(kb) * (static_cast<size_t>(W) * T) + static_cast<size_t>(src) * T + t] = sc[i];
+  }
+}
+
+// --------------------------------------------------------------------------------- push
+constexpr int kPushThreads = 256;
+constexpr int kVec = kHidden / (kPushThreads * 4);   // 7 float4 per thread
+
+__global__ void __launch_bounds__(kPushThreads)
+ep_combine_push_kernel(EpView v, uint32_t seq, const int* __restrict__ route_row, const float* __restrict__ topk_w,
+                       const float* __restrict__ o_rows, int row_cap, int* __restrict__ ticket) {
+  const int t = blockIdx.x;                      // gathered token index, 0 .. W*T-1
+  const int owner = t / v.T, tl = t % v.T;
+  const int tid = threadIdx.x;
+  int rows[kTopK];
+  float w[kTopK];
+  bool any = false;
+#pragma unroll
+  for (int k = 0; k < kTopK; ++k) {
+    rows[k] = route_row[t * kTopK + k];
+    w[k] = topk_w[t * kTopK + k];
+    if (rows[k] >= row_cap) rows[k] = -1;
+    any = any || rows[k] >= 0;
+  }
+  uint32_t* has = reinterpret_cast<uint32_t*>(v.base[owner] + v.has_off[seq & 1]) + v.rank * v.T + tl;
+  if (any) {
+    float4 acc[kVec];
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+    for (int k = 0; k < kTopK; ++k) {
+      if (rows[k] < 0) continue;
+      const float4* src = reinterpret_cast<const float4*>(o_rows + static_cast<size_t>(rows[k]) * kHidden);
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) {
+        const float4 x = __ldg(src + i * kPushThreads + tid);
+        acc[i].x = fmaf(w[k], x.x, acc[i].x);
+        acc[i].y = fmaf(w[k], x.y, acc[i].y);
+        acc[i].z = fmaf(w[k], x.z, acc[i].z);
+        acc[i].w = fmaf(w[k], x.w, acc[i].w);
+      }
+    }
+    float4* dst = reinterpret_cast<float4*>(v.base[owner] + v.recv_off[seq & 1]) +
+                  (static_cast<size_t>(v.rank) * v.T + tl) * (kHidden / 4);
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) dst[i * kPushThreads + tid] = acc[i];
+  }
+  if (tid == 0) *has = any ? 1u : 0u;
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) {
+    if (atomicAdd(ticket, 1) == static_cast<int>(gridDim.x) - 1) {
+      *ticket = 0;
+      __threadfence_system();
+      for (int r = 0; r < v.world; ++r) st_release_sys(out_flag(v, r, v.rank), seq);
+    }
+  }
+}
+
+// -------------------------------------------------------------------------------- final
+__global__ void __launch_bounds__(kPushThreads)
+ep_final_kernel(EpView v, uint32_t seq, __nv_bfloat16* __restrict__ out, int* __restrict__ status) {
+  __shared__ int s_ok;
+  const int tl = blockIdx.x, tid = threadIdx.x;
+  if (tid == 0) {
+    int ok = 1;
+    for (int q = 0; q < v.world && ok; ++q) ok = wait_flag(out_flag(v, v.rank, q), seq) ? 1 : 0;
+    if (!ok) atomicExch(status, kStatusPeerTimeout);
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const uint32_t* has = reinterpret_cast<const uint32_t*>(v.base[v.rank] + v.has_off[seq & 1]);
+  const float4* recv = reinterpret_cast<const float4*>(v.base[v.rank] + v.recv_off[seq & 1]);
+  float4 acc[kVec];
+#pragma unroll
+  for (int i = 0; i < kVec; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int q = 0; q < v.world; ++q) {
+    if (__ldcg(has + q * v.T + tl) == 0) continue;
+    const float4* src = recv + (static_cast<size_t>(q) * v.T + tl) * (kHidden / 4);
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) {
+      const float4 x = __ldcg(src + i * kPushThreads + tid);
+      acc[i].x += x.x; acc[i].y += x.y; acc[i].z += x.z; acc[i].w += x.w;
+    }
+  }
+  uint2* dst = reinterpret_cast<uint2*>(out + static_cast<size_t>(tl) * kHidden);
+#pragma unroll
+  for (int i = 0; i < kVec; ++i) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(acc[i].x, acc[i].y);
+    const __nv_bfloat162 hi = __floats2bfloat162_rn(acc[i].z, acc[i].w);
+    uint2 p;
+    p.x = *reinterpret_cast<const uint32_t*>(&lo);
+    p.y = *reinterpret_cast<const uint32_t*>(&hi);
+    dst[i * kPushThreads + tid] = p;
+  }
+}
+
+EpView make_view(const syfi_moe_ep_desc& d) {
+  EpView v;
+  for (int r = 0; r < kMaxRanks; ++r) v.base[r] = r < d.world_size ? static_cast<uint8_t*>(d.region[r]) : nullptr;
+  v.world = d.world_size;
+  v.rank = d.rank;
+  v.T = static_cast<int>(d.tokens_per_rank);
+  const size_t T = v.T, W = v.world;
+  size_t off = 0;
+  for (int b = 0; b < 2; ++b) { v.in_off[b] = off; off += align256(T * (kExpertsGlobal * 4 + kHidden + kHBlocks * 4)); }
+  for (int b = 0; b < 2; ++b) { v.recv_off[b] = off; off += align256(W * T * kHidden * 4); }
+  for (int b = 0; b < 2; ++b) { v.has_off[b] = off; off += align256(W * T * 4); }
+  v.flag_off = off;
+  return v;
+}
+
+}  // namespace
+
+size_t ep_region_bytes(int world, int64_t tokens_per_rank) {
+  syfi_moe_ep_desc d{};
+  d.world_size = world;
+  d.tokens_per_rank = tokens_per_rank;
+  return make_view(d).flag_off + align256(2 * kMaxRanks * sizeof(uint32_t));
+}
+
+cudaError_t launch_ep_publish_gather(const syfi_moe_ep_desc& d, uint32_t seq, const void* logits, const void* hs,
+                                     const void* hs_scale, void* g_logits, void* g_hs, void* g_scale, int* ticket,
+                                     int* status, cudaStream_t st) {
+  const EpView v = make_view(d);
+  ep_publish_kernel<<<64, 256, 0, st>>>(v, seq, static_cast<const uint4*>(logits), static_cast<const uint4*>(hs),
+                                        static_cast<const uint4*>(hs_scale), ticket);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  ep_gather_kernel<<<dim3(16, d.world_size), 256, 0, st>>>(v, seq, static_cast<uint4*>(g_logits),
+                                                           static_cast<uint4*>(g_hs), static_cast<float*>(g_scale),
+                                                           status);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_push_final(const syfi_moe_ep_desc& d, uint32_t seq, const Workspace& ws, void* out_bf16,
+                                 int* ticket, cudaStream_t st) {
+  const EpView v = make_view(d);
+  const int tokens = d.world_size * static_cast<int>(d.tokens_per_rank);
+  ep_combine_push_kernel<<<tokens, kPushThreads, 0, st>>>(v, seq, ws.route_row, ws.topk_w, ws.o_rows, ws.row_cap,
+                                                         ticket);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  ep_final_kernel<<<static_cast<int>(d.tokens_per_rank), kPushThreads, 0, st>>>(
+      v, seq, static_cast<__nv_bfloat16*>(out_bf16), ws.status);
+  return cudaGetLastError();
+}
+
+}  // namespace syfi

@@ -30,6 +30,7 @@ enum : int {
   kStatusWaitTimeoutMma = 102,
   kStatusWaitTimeoutEpilogue = 103,
   kStatusBadIndex = 104,
+  kStatusPeerTimeout = 105,   // a flag another rank should have raised did not arrive in time
 };
 
 // Device-side control block (one int array); the GEMM kernels read the tile count from it.
@@ -72,6 +73,7 @@ struct Workspace {
   uint8_t* c_lo = nullptr;        // [row_cap, 2048] e4m3 residual term (scale = c_scale / 28)
   float* c_scale = nullptr;       // [16, row_cap]
   float* o_rows = nullptr;        // [row_cap, 7168] f32 per-route expert outputs
+  int* ep_ticket = nullptr;       // last-CTA ticket of the expert-parallel exchange kernels (self-resetting)
   size_t bytes = 0;
 };
 
@@ -117,6 +119,17 @@ cudaError_t launch_gemm2(const GemmLaunch& g, const float* w2_scale, int e_local
                          cudaStream_t st);
 cudaError_t launch_combine(int T, const Workspace& ws, void* out, int out_is_f32, cudaStream_t st);
 cudaError_t gemm_set_attributes();
+
+// expert-parallel exchange over peer memory (ep_exchange.cu)
+}  // namespace syfi
+struct syfi_moe_ep_desc;
+namespace syfi {
+size_t ep_region_bytes(int world, int64_t tokens_per_rank);
+cudaError_t launch_ep_publish_gather(const syfi_moe_ep_desc& d, uint32_t seq, const void* logits, const void* hs,
+                                     const void* hs_scale, void* g_logits, void* g_hs, void* g_scale, int* ticket,
+                                     int* status, cudaStream_t st);
+cudaError_t launch_ep_push_final(const syfi_moe_ep_desc& d, uint32_t seq, const Workspace& ws, void* out_bf16,
+                                 int* ticket, cudaStream_t st);
 
 // Records `msg` as the calling thread's last error (what syfi_moe_last_error() returns) and returns `code`.
 int set_last_error(int code, const char* msg);

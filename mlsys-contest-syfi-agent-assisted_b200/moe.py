@@ -37,6 +37,8 @@ ABI = {
     "syfi_moe_forward_partial_f32": (ctypes.c_int, [_vp] + [_vp] * 8 + [_i64, _i32, _i64, _f64, _vp, _vp]),
     "syfi_moe_forward_host": (ctypes.c_int, [_vp] + [_vp] * 8 + [_i64, _i32, _i64, _f64, _vp, _vp]),
     "syfi_moe_route": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i32, _i64, _f64, _vp, _vp, _vp]),
+    "syfi_moe_ep_region_bytes": (_i64, [_i32, _i64]),
+    "syfi_moe_ep_forward": (ctypes.c_int, [_vp, _vp, _i64] + [_vp] * 8 + [_i32, _i64, _f64, _vp, _vp]),
     "syfi_moe_route_noalloc": (ctypes.c_int, [_vp, _vp, _i64, _i32, _i64, _f64, _vp, _vp, _vp]),
     "syfi_moe_last_routing": (ctypes.c_int, [_vp, _i64, _vp, _vp, _vp]),
     "syfi_moe_check": (ctypes.c_int, [_vp, ctypes.POINTER(_i32), _vp]),
@@ -52,6 +54,14 @@ ABI = {
 
 class MoeError(RuntimeError):
     pass
+
+
+EP_MAX_RANKS = 8
+
+
+class EpDesc(ctypes.Structure):
+    """Mirror of ``syfi_moe_ep_desc`` (include/syfi_moe.h)."""
+    _fields_ = [("world_size", _i32), ("rank", _i32), ("tokens_per_rank", _i64), ("region", _vp * EP_MAX_RANKS)]
 
 
 def library_path() -> str:
@@ -258,6 +268,34 @@ def run_moe_host(routing_logits, routing_bias, hidden_states, hidden_states_scal
         hidden_states_scale.data_ptr(), gemm1_weights.data_ptr(), gemm1_weights_scale.data_ptr(),
         gemm2_weights.data_ptr(), gemm2_weights_scale.data_ptr(), T, E, off, float(routed_scaling_factor),
         output.data_ptr(), _stream_ptr(stream, ctx.device)))
+    return output
+
+
+def ep_region_bytes(world_size: int, tokens_per_rank: int) -> int:
+    """Bytes every rank must allocate (symmetrically) for the peer-memory expert-parallel path."""
+    n = int(load_library().syfi_moe_ep_region_bytes(int(world_size), int(tokens_per_rank)))
+    if n <= 0:
+        raise ValueError("world_size must be in [1, 8] and tokens_per_rank positive")
+    return n
+
+
+def run_moe_ep(desc: EpDesc, step: int, routing_logits, routing_bias, hidden_states, hidden_states_scale,
+               gemm1_weights, gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
+               routed_scaling_factor, output, *, stream=None):
+    """One expert-parallel step through peer memory (see ``syfi_moe_ep_forward``): this rank's own
+    tokens in, their bf16 outputs summed over all ranks' experts out.  ``step`` counts 1, 2, 3, ...
+    identically on every rank."""
+    T, E, off, dev = _validate(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                               gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
+                               output, torch.bfloat16, None)
+    if T != desc.tokens_per_rank:
+        raise ValueError(f"descriptor is for {desc.tokens_per_rank} tokens per rank, got {T}")
+    ctx = get_context(dev.index, T * desc.world_size)
+    _check(ctx.lib.syfi_moe_ep_forward(
+        ctx.handle, ctypes.byref(desc), int(step), routing_logits.data_ptr(), routing_bias.data_ptr(),
+        hidden_states.data_ptr(), hidden_states_scale.data_ptr(), gemm1_weights.data_ptr(),
+        gemm1_weights_scale.data_ptr(), gemm2_weights.data_ptr(), gemm2_weights_scale.data_ptr(), E, off,
+        float(routed_scaling_factor), output.data_ptr(), _stream_ptr(stream, ctx.device)))
     return output
 
 

@@ -124,6 +124,34 @@ class ExpertParallelMoe:
         out_bf16.copy_(res)
         return out_bf16
 
+    def enable_peer_exchange(self, tokens_per_rank: int, device) -> bool:
+        """Set up the peer-memory path for ``forward_sharded``: a symmetric region on every rank, mapped
+        into every other rank (torch's symmetric memory does the allocation and the exchange of
+        mappings; the data path is this library's own kernels).  Returns False when symmetric memory is
+        not available (then ``forward_sharded`` keeps using NCCL)."""
+        from . import moe as _moe
+        if self.world < 2 or self.world > _moe.EP_MAX_RANKS:
+            return False
+        try:
+            import torch.distributed._symmetric_memory as symm
+            nbytes = _moe.ep_region_bytes(self.world, tokens_per_rank)
+            region = symm.empty(nbytes, dtype=torch.uint8, device=device)
+            handle = symm.rendezvous(region, self.group if self.group is not None else dist.group.WORLD)
+            region.zero_()
+            torch.cuda.synchronize(device)
+            handle.barrier()
+            torch.cuda.synchronize(device)
+            desc = _moe.EpDesc()
+            desc.world_size, desc.rank, desc.tokens_per_rank = self.world, self.rank, int(tokens_per_rank)
+            for r, ptr in enumerate(handle.buffer_ptrs):
+                desc.region[r] = ptr
+        except Exception as exc:  # no symmetric memory on this system / backend
+            self._peer_error = repr(exc)
+            return False
+        self._peer = (region, handle, desc)
+        self._peer_step = 0
+        return True
+
     def forward_sharded(self, logits, bias, hs, hs_scale, out_bf16=None):
         """Each rank passes its OWN T tokens (same T on every rank); returns their bf16 outputs
         summed over all ranks' experts."""
@@ -132,6 +160,14 @@ class ExpertParallelMoe:
         if W == 1:
             return self.forward_replicated(logits, bias, hs, hs_scale, out_bf16)
         dev = logits.device
+        peer = getattr(self, "_peer", None)
+        if peer is not None and peer[2].tokens_per_rank == T:
+            from . import moe as _moe
+            if out_bf16 is None:
+                out_bf16 = torch.empty(T, hs.shape[1], dtype=torch.bfloat16, device=dev)
+            self._peer_step += 1
+            return _moe.run_moe_ep(peer[2], self._peer_step, logits, bias, hs, hs_scale, self.w13, self.w13_s,
+                                   self.w2, self.w2_s, self.offset, self.scaling, out_bf16)
         g_logits = self._buffer("g_logits", (W * T, logits.shape[1]), logits.dtype, dev)
         g_hs = self._buffer("g_hs", (W * T, hs.shape[1]), torch.uint8, dev)
         g_sc = self._buffer("g_sc", (W * hs_scale.shape[0], T), hs_scale.dtype, dev)

@@ -55,7 +55,17 @@ def _worker(rank, world, port, q):
                                         mine.hidden_states_scale.to(dev), fd.gemm1_weights, fd.gemm1_weights_scale,
                                         fd.gemm2_weights, fd.gemm2_weights_scale, 0, 2.5)
         ok3, s3 = oracle.check_output(o3, ref3)
-        q.put((rank, ok1 and ok2 and ok3, (s1, s2, s3)))
+        # the same step through the library's peer-memory exchange instead of NCCL, three steps in a row
+        ok4, s4 = True, "peer exchange unavailable"
+        if ep.enable_peer_exchange(32, dev):
+            for _ in range(3):
+                o4 = ep.forward_sharded(mine.routing_logits.to(dev), tok[1], mine.hidden_states.to(dev),
+                                        mine.hidden_states_scale.to(dev))
+                torch.cuda.synchronize()
+                pkg.get_context(rank).check()
+                ok4, s4 = oracle.check_output(o4, ref3)
+                ok4 = ok4 and float((o4.float() - o3.float()).abs().max()) <= 2.0 ** -5
+        q.put((rank, ok1 and ok2 and ok3 and ok4, (s1, s2, s3, s4)))
     finally:
         dist.destroy_process_group()
 

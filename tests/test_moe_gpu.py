@@ -241,3 +241,28 @@ def test_argument_validation(pkg):
         pkg.run_moe(args[0].cpu(), *args[1:], out)
     pkg.run_moe(*args, out)              # the context is still usable afterwards
     pkg.get_context(0).check()
+
+
+def test_peer_wait_runs_out_without_hanging(pkg):
+    """Failure detection without a GPU fault: an expert-parallel step whose 'peer' never publishes
+    (a second local buffer stands in for rank 1).  The flag waits give up after about a second each,
+    the kernels return, the status word reports it, and the context keeps working."""
+    import ctypes
+    moe = __import__("importlib").import_module(pkg.__name__ + ".moe")
+    T = 8
+    inp = pkg.make_inputs(num_tokens=T, seed=31, e_local=2, device=DEV)
+    nbytes = pkg.ep_region_bytes(2, T)
+    mine = torch.zeros(nbytes, dtype=torch.uint8, device=DEV)
+    silent_peer = torch.zeros(nbytes, dtype=torch.uint8, device=DEV)
+    desc = pkg.EpDesc()
+    desc.world_size, desc.rank, desc.tokens_per_rank = 2, 0, T
+    desc.region[0], desc.region[1] = mine.data_ptr(), silent_peer.data_ptr()
+    out = torch.zeros(T, 7168, dtype=torch.bfloat16, device=DEV)
+    pkg.run_moe_ep(desc, 1, *inp.args()[:8], 0, 2.5, out)
+    with pytest.raises(pkg.MoeError, match="105"):
+        pkg.get_context(0).check()
+    # the context is usable afterwards
+    good = torch.empty(T, 7168, dtype=torch.bfloat16, device=DEV)
+    pkg.run_moe(*inp.args(), good)
+    pkg.get_context(0).check()
+    assert bool(torch.isfinite(good.float()).all())
