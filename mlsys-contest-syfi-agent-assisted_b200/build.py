@@ -48,5 +48,33 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+TVMFFI_LIB = os.path.join(CSRC, "libsyfi_moe_tvmffi.so")
+
+
+def build_tvm_ffi_binding(force: bool = False) -> str | None:
+    """Builds csrc/libsyfi_moe_tvmffi.so, which exports the layer as ``__tvm_ffi_run_moe`` (the symbol
+    the reference's harness loads).  Needs the tvm-ffi package for its headers and runtime; returns
+    None when it is not installed.  The main library must have been built first."""
+    try:
+        import tvm_ffi
+    except Exception:
+        return None
+    src = os.path.join(CSRC, "tvm_ffi_binding.cc")
+    if (not force and os.path.exists(TVMFFI_LIB) and os.path.getmtime(TVMFFI_LIB) >= os.path.getmtime(src)
+            and os.path.getmtime(TVMFFI_LIB) >= os.path.getmtime(LIB)):
+        return TVMFFI_LIB
+    root = os.path.dirname(tvm_ffi.__file__)
+    cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-I" + os.path.join(root, "include"),
+           "-I" + os.path.join(root, "3rdparty", "dlpack", "include"), src, "-o", TVMFFI_LIB,
+           "-L" + CSRC, "-lsyfi_moe", "-L" + os.path.join(root, "lib"), "-ltvm_ffi",
+           "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + os.path.join(root, "lib")]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        sys.stderr.write(proc.stdout + proc.stderr)
+        raise RuntimeError("g++ failed building " + TVMFFI_LIB)
+    return TVMFFI_LIB
+
+
 if __name__ == "__main__":
     print(build_library(force="--force" in sys.argv, verbose=True))
+    print(build_tvm_ffi_binding(force="--force" in sys.argv))

@@ -87,3 +87,16 @@ def test_work_model(pkg):
     assert nbytes == 44_050_944 + 512
     flops, nbytes = pkg.algorithmic_work(89, 16, 64)
     assert nbytes == 16 * 44_050_944 + 64 * 22_752 + 512
+
+
+def test_tvm_ffi_binding_exports_the_reference_symbol(pkg):
+    """The optional tvm-ffi shared object exports `__tvm_ffi_run_moe`, the symbol the reference's
+    `TVM_FFI_DLL_EXPORT_TYPED_FUNC(run_moe, ...)` produces (moe/solution/cuda/moe.cu:3260)."""
+    from importlib import import_module
+    build = import_module(pkg.__name__ + ".build")
+    pytest.importorskip("tvm_ffi")
+    pkg.load_library()
+    path = build.build_tvm_ffi_binding()
+    assert path and os.path.exists(path)
+    lib = ctypes.CDLL(path)
+    assert hasattr(lib, "__tvm_ffi_run_moe")

@@ -266,3 +266,23 @@ def test_peer_wait_runs_out_without_hanging(pkg):
     pkg.run_moe(*inp.args(), good)
     pkg.get_context(0).check()
     assert bool(torch.isfinite(good.float()).all())
+
+
+def test_tvm_ffi_entry_point(pkg, oracle):
+    """Calls the layer the way the reference's harness does: through tvm-ffi, `run_moe(*inputs, output)`
+    (moe/scripts/debug_correctness.py:49-55)."""
+    tvm_ffi = pytest.importorskip("tvm_ffi")
+    build = __import__("importlib").import_module(pkg.__name__ + ".build")
+    pkg.load_library()
+    path = build.build_tvm_ffi_binding()
+    mod = tvm_ffi.load_module(path)
+    inp = pkg.make_inputs(num_tokens=40, seed=23, e_local=8, device=DEV)
+    out = torch.zeros(40, 7168, dtype=torch.bfloat16, device=DEV)
+    u8 = lambda t: t.view(torch.uint8)       # the binding only takes addresses; fp8 travels as bytes
+    mod.run_moe(inp.routing_logits, inp.routing_bias, u8(inp.hidden_states), inp.hidden_states_scale,
+                u8(inp.gemm1_weights), inp.gemm1_weights_scale, u8(inp.gemm2_weights), inp.gemm2_weights_scale,
+                0, 2.5, out)
+    torch.cuda.synchronize()
+    ref, _, _ = oracle.moe_forward(*inp.to("cpu").args())
+    ok, stats = oracle.check_output(out, ref)
+    assert ok, stats
