@@ -204,9 +204,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   tc_fence_after();
   const uint32_t tmem_base = *s_tmem;
   const int total = p.meta[0] * FT;                 // work items
-  const int my_items = static_cast<int>(blockIdx.x) < total ? (total - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  // Effective grid: the launch always has one CTA per SM, but when the items do not fill the last
+  // round, fewer CTAs with equally many items each finish sooner than a last round that keeps only a
+  // handful of SMs busy (a single SM cannot pull more than about 1.4x its fair share of HBM).  Only
+  // taken when it costs at most a fifth of the SMs; the rest of the CTAs exit at once.
+  int eff_grid = static_cast<int>(gridDim.x);
+  {
+    const int rounds = (total + eff_grid - 1) / eff_grid;
+    const int even = rounds > 0 ? (total + rounds - 1) / rounds : eff_grid;   // CTAs needed for `rounds` each
+    if (even * 5 >= eff_grid * 4) eff_grid = even;
+  }
+  const int my_items = (static_cast<int>(blockIdx.x) < eff_grid && static_cast<int>(blockIdx.x) < total)
+                           ? (total - blockIdx.x + eff_grid - 1) / eff_grid : 0;
   const int u_begin = 0, u_end = my_items * STEPS;    // this CTA's steps, item after item
-  auto item_at = [&](int u) { return static_cast<int>(blockIdx.x + (u / STEPS) * gridDim.x); };
+  auto item_at = [&](int u) { return static_cast<int>(blockIdx.x + (u / STEPS) * eff_grid); };
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (one thread)
