@@ -65,7 +65,19 @@ def _worker(rank, world, port, q):
                 pkg.get_context(rank).check()
                 ok4, s4 = oracle.check_output(o4, ref3)
                 ok4 = ok4 and float((o4.float() - o3.float()).abs().max()) <= 2.0 ** -5
-        q.put((rank, ok1 and ok2 and ok3 and ok4, (s1, s2, s3, s4)))
+        # load-imbalance configuration in miniature: skewed logits (hot experts), per-rank weights,
+        # expert offset 32 * rank, replicated tokens, partial outputs summed over the ranks
+        skew = pkg.make_inputs(num_tokens=192, seed=0, e_local=32, local_expert_offset=32 * rank, device=dev,
+                               hot_experts=16, weight_seed=rank)
+        ep5 = pkg.ExpertParallelMoe(skew.gemm1_weights, skew.gemm1_weights_scale, skew.gemm2_weights,
+                                    skew.gemm2_weights_scale, 32 * rank, 2.5)
+        o5 = ep5.forward_replicated(skew.routing_logits, skew.routing_bias, skew.hidden_states,
+                                    skew.hidden_states_scale)
+        pkg.get_context(rank).check()
+        acc5, _, _ = oracle.moe_forward(*skew.args(), return_f32=True)
+        dist.all_reduce(acc5)
+        ok5, s5 = oracle.check_output(o5, acc5.to(torch.bfloat16))
+        q.put((rank, ok1 and ok2 and ok3 and ok4 and ok5, (s1, s2, s3, s4, s5)))
     finally:
         dist.destroy_process_group()
 
