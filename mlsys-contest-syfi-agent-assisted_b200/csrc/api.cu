@@ -202,9 +202,9 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
   // only exist on the device: 32 rows while the layer is bound by streaming weights (measured faster up
   // to 1024 tokens: 8 accumulator slots in flight, two K blocks per barrier round), 64 rows beyond.
   int token_tile = (T64 <= 1024) ? 32 : 64;
-  if (const char* ov = getenv("SYFI_MOE_TOKEN_TILE")) {   // tuning knob: force 32 or 64
+  if (const char* ov = getenv("SYFI_MOE_TOKEN_TILE")) {   // tuning knob: force 32, 64 or 128
     const int v = atoi(ov);
-    if (v == 32 || v == 64) token_tile = v;
+    if (v == 32 || v == 64 || v == 128) token_tile = v;
   }
   const bool maps_valid = ctx->map_w13 == w13 && ctx->map_w2 == w2 && ctx->map_ws == ws.a_perm &&
                           ctx->map_e_local == e_local && ctx->map_token_tile == token_tile;

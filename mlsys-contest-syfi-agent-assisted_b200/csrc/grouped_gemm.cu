@@ -57,10 +57,14 @@ template <int MODE, int NT> struct Cfg {
   // tcgen05.commit (about 90 cycles), so with small N the issue loop, not the tensor pipe, sets
   // the pace; handing over two K blocks per barrier round halves the waits and commits per byte.
   static constexpr int kKps = 2;
-  static constexpr int kGroups = MODE == 1 ? (NT == 32 ? 3 : 2) : (NT == 32 ? 4 : 3);   // smem ring depth
+  static constexpr int kGroups = NT == 128 ? 2 : MODE == 1 ? (NT == 32 ? 3 : 2) : (NT == 32 ? 4 : 3);   // smem ring depth
   static constexpr int kGroupBytes = kKps * kStageBytes;
   static constexpr int kSlots = kTmemCols / (2 * NT);                           // accumulator-pair slots
-  static constexpr int kPairs = kSlots / kKps;                                  // slot groups signalled together
+  // K blocks per TMEM ring entry.  The 128-row token tile fills half of TMEM with one K block's
+  // accumulator pair, so there the MMA thread and the epilogue hand slots over one K block at a time
+  // (the shared-memory ring still moves two, for the K-adjacent request pattern).
+  static constexpr int kTKps = NT == 128 ? 1 : kKps;
+  static constexpr int kPairs = kSlots / kTKps;                                 // TMEM ring entries
   static constexpr int kScaleBufs = MODE == 2 ? 2 : 1;   // mode 2 prefetches the next item's scales
   static constexpr int kColSplit = NT / 32;               // epilogue warps per TMEM lane quarter
   static constexpr int kThreads = 64 + 128 * kColSplit;   // producer warp + MMA warp + epilogue warps
@@ -69,7 +73,9 @@ template <int MODE, int NT> struct Cfg {
                                     8 * (2 * kGroups + 2 * kPairs) +
                                     kMaxLocalExperts * static_cast<int>(sizeof(ExpertWork)) + 16;
   static_assert(kSmemBytes <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
-  static_assert(kKBlocks % kKps == 0 && kSlots % kKps == 0, "steps must tile the K blocks and the slots");
+  static_assert(kKBlocks % kKps == 0 && kSlots % kTKps == 0 && kKps % kTKps == 0,
+                "steps must tile the K blocks and the slots");
+  static_assert(kThreads <= 1024, "too many epilogue warps");
 };
 
 struct GemmArgs {
@@ -144,7 +150,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   constexpr int KB = C::kKBlocks;
   constexpr int STEPS = KB / KPS;
   constexpr int FT = C::kFeatTiles;
-  constexpr int PAIRS = C::kPairs;        // TMEM ring entries, each kKps accumulator-pair slots
+  constexpr int TKPS = C::kTKps;
+  constexpr int PAIRS = C::kPairs;        // TMEM ring entries, each kTKps accumulator-pair slots
   constexpr int kBTile = C::kBTile;
 
   extern __shared__ uint8_t smem_raw[];
@@ -289,35 +296,40 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         // instead of one per term; mode 1 needs two because up and gate are different A tiles.
         const uint32_t idesc = umma_idesc_e4m3_m128(MODE == 1 ? static_cast<uint32_t>(im.n) : 2u * NT);
         for (int step = s_first; step < s_last; ++step) {
-          if (!mbar_wait_bounded(&full[g], ph, s_abort, kStatusWaitTimeoutMma) ||
-              !mbar_wait_bounded(&tempty[pr], pph ^ 1u, s_abort, kStatusWaitTimeoutMma)) { alive = false; break; }
-          tc_fence_after();
+          if (!mbar_wait_bounded(&full[g], ph, s_abort, kStatusWaitTimeoutMma)) { alive = false; break; }
           TRACE(1, step);
 #pragma unroll
-          for (int k = 0; k < KPS; ++k) {
-            const uint32_t st = smem_u32(smem + g * C::kGroupBytes + k * C::kStageBytes);
-            const uint32_t d0 = tmem_base + (pr * KPS + k) * (2 * NT);
-            if (MODE == 1) {
-              const uint64_t a0 = umma_smem_desc_sw128(st);
-              const uint64_t a1 = umma_smem_desc_sw128(st + kATile);
-              const uint64_t b0 = umma_smem_desc_sw128(st + 2 * kATile);
+          for (int tk = 0; tk < KPS / TKPS && alive; ++tk) {
+            if (!mbar_wait_bounded(&tempty[pr], pph ^ 1u, s_abort, kStatusWaitTimeoutMma)) { alive = false; break; }
+            tc_fence_after();
 #pragma unroll
-              for (int k4 = 0; k4 < 4; ++k4) {
-                // 32 bytes of K per MMA: +2 in the 16-byte-unit address field
-                umma_f8(d0, a0 + 2 * k4, b0 + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
-                umma_f8(d0 + NT, a1 + 2 * k4, b0 + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
+            for (int k2 = 0; k2 < TKPS; ++k2) {
+              const int k = tk * TKPS + k2;
+              const uint32_t st = smem_u32(smem + g * C::kGroupBytes + k * C::kStageBytes);
+              const uint32_t d0 = tmem_base + (pr * TKPS + k2) * (2 * NT);
+              if (MODE == 1) {
+                const uint64_t a0 = umma_smem_desc_sw128(st);
+                const uint64_t a1 = umma_smem_desc_sw128(st + kATile);
+                const uint64_t b0 = umma_smem_desc_sw128(st + 2 * kATile);
+#pragma unroll
+                for (int k4 = 0; k4 < 4; ++k4) {
+                  // 32 bytes of K per MMA: +2 in the 16-byte-unit address field
+                  umma_f8(d0, a0 + 2 * k4, b0 + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
+                  umma_f8(d0 + NT, a1 + 2 * k4, b0 + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
+                }
+              } else {
+                const uint64_t a0 = umma_smem_desc_sw128(st);
+                const uint64_t b0 = umma_smem_desc_sw128(st + kATile);   // hi rows, then lo rows
+#pragma unroll
+                for (int k4 = 0; k4 < 4; ++k4) umma_f8(d0, a0 + 2 * k4, b0 + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
               }
-            } else {
-              const uint64_t a0 = umma_smem_desc_sw128(st);
-              const uint64_t b0 = umma_smem_desc_sw128(st + kATile);   // hi rows, then lo rows
-#pragma unroll
-              for (int k4 = 0; k4 < 4; ++k4) umma_f8(d0, a0 + 2 * k4, b0 + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
             }
+            if (tk == KPS / TKPS - 1) umma_commit(&empty[g]);
+            umma_commit(&tfull[pr]);
+            if (++pr == PAIRS) { pr = 0; pph ^= 1u; }
           }
-          umma_commit(&empty[g]);
-          umma_commit(&tfull[pr]);
+          if (!alive) break;
           if (++g == G) { g = 0; ph ^= 1u; }
-          if (++pr == PAIRS) { pr = 0; pph ^= 1u; }
         }
       }
     }
@@ -408,51 +420,97 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       }
       if (et == 0) TRACE(2, 1001);
 
-      float acc0[CN];                        // mode 1: up,   mode 2: output
-      float acc1[MODE == 1 ? CN : 1];        // mode 1: gate
+      // accumulators as packed f32 pairs (columns 2i, 2i + 1) while the K loop runs
+      uint64_t acc0p[CN / 2];                   // mode 1: up,   mode 2: output
+      uint64_t acc1p[MODE == 1 ? CN / 2 : 1];   // mode 1: gate
 #pragma unroll
-      for (int j = 0; j < CN; ++j) acc0[j] = 0.0f;
+      for (int j = 0; j < CN / 2; ++j) acc0p[j] = 0ull;
       if (MODE == 1) {
 #pragma unroll
-        for (int j = 0; j < CN; ++j) acc1[j] = 0.0f;
+        for (int j = 0; j < CN / 2; ++j) acc1p[j] = 0ull;
       }
 
-      for (int step = s_first; step < s_last && ok; ++step) {
+      // One promotion step: sixteen columns of one or both accumulators of a K block into the registers,
+      // two columns per instruction.  `sa` points at the sixteen activation scales (16-byte aligned).
+      auto promote16 = [&](const uint32_t (&r0)[16], const uint32_t (&r1)[16], int cbase, const float* sa,
+                           uint64_t ws0, uint64_t ws1, int sel) {   // mode 1: sel 0 = up, 1 = gate, 2 = both
+        const ulonglong2* sp = reinterpret_cast<const ulonglong2*>(sa);
+        const uint64_t inv_ratio = f32x2_pack(1.0f / kLoRatio, 1.0f / kLoRatio);
+#pragma unroll
+        for (int j4 = 0; j4 < 4; ++j4) {
+          const ulonglong2 a4 = sp[j4];         // scales of four columns
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int j = j4 * 4 + h * 2, ai = (cbase + j) / 2;
+            const uint64_t a = h == 0 ? a4.x : a4.y;
+            const uint64_t v0 = f32x2_pack_bits(r0[j], r0[j + 1]);
+            if (MODE == 1) {
+              if (sel != 1) acc0p[ai] = f32x2_fma(v0, f32x2_mul(a, ws0), acc0p[ai]);
+              if (sel != 0) acc1p[ai] = f32x2_fma(f32x2_pack_bits(r1[j], r1[j + 1]), f32x2_mul(a, ws1), acc1p[ai]);
+            } else {
+              const uint64_t v = f32x2_fma(f32x2_pack_bits(r1[j], r1[j + 1]), inv_ratio, v0);
+              acc0p[ai] = f32x2_fma(v, f32x2_mul(a, ws0), acc0p[ai]);
+            }
+          }
+        }
+      };
+      for (int ts = s_first * (KPS / TKPS); ts < s_last * (KPS / TKPS) && ok; ++ts) {
         if (!mbar_wait_bounded(&tfull[pr], pph, s_abort, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
         tc_fence_after();
-        if (et == 0) TRACE(2, step);
+        if (et == 0) TRACE(2, ts);
 #pragma unroll
-        for (int k = 0; k < KPS; ++k) {
-          const int kb = step * KPS + k;
-          const uint32_t t0 = lane_addr + (pr * KPS + k) * (2 * NT) + c0;
-          const float ws0 = s_ws[kb];
-          const float ws1 = (MODE == 1) ? s_ws[64 + kb] : 0.0f;
+        for (int k = 0; k < TKPS; ++k) {
+          const int kb = ts * TKPS + k;
+          const uint32_t t0 = lane_addr + (pr * TKPS + k) * (2 * NT) + c0;
+          const uint64_t ws0 = f32x2_pack(s_ws[kb], s_ws[kb]);
+          const uint64_t ws1 = (MODE == 1) ? f32x2_pack(s_ws[64 + kb], s_ws[64 + kb]) : 0ull;
           const float* sa = s_act + kb * NT + c0;
-          if (c0 < n) {                       // this thread's 32 columns: four loads in flight, one wait
-            uint32_t v0[2][16], v1[2][16];
-            tmem_ld16(t0, v0[0]);
-            tmem_ld16(t0 + NT, v1[0]);
-            if (c0 + 16 < n) {
-              tmem_ld16(t0 + 16, v0[1]);
-              tmem_ld16(t0 + NT + 16, v1[1]);
-            }
-            tmem_ld_wait();
+          if (c0 < n) {
+            if (NT == 128 && MODE == 1) {
+              // 18 warps share the register file and 64 registers of a thread hold accumulators: eight
+              // columns of one accumulator at a time
 #pragma unroll
-            for (int c = 0; c < 2; ++c) {
-              if (c0 + c * 16 < n) {
-#pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                  const int col = c * 16 + j;
-                  const float a = sa[col];
-                  if (MODE == 1) {
-                    acc0[col] = fmaf(__uint_as_float(v0[c][j]), a * ws0, acc0[col]);
-                    acc1[col] = fmaf(__uint_as_float(v1[c][j]), a * ws1, acc1[col]);
-                  } else {
-                    const float v = fmaf(__uint_as_float(v1[c][j]), 1.0f / kLoRatio, __uint_as_float(v0[c][j]));
-                    acc0[col] = fmaf(v, a * ws0, acc0[col]);
-                  }
+              for (int c = 0; c < 4; ++c) {
+                if (c0 + c * 8 < n) {
+                  const ulonglong2* sp = reinterpret_cast<const ulonglong2*>(sa + c * 8);
+                  const ulonglong2 s03 = sp[0], s47 = sp[1];
+                  uint32_t r[8];
+                  tmem_ld8(t0 + c * 8, r);
+                  tmem_ld_wait();
+                  acc0p[c * 4 + 0] = f32x2_fma(f32x2_pack_bits(r[0], r[1]), f32x2_mul(s03.x, ws0), acc0p[c * 4 + 0]);
+                  acc0p[c * 4 + 1] = f32x2_fma(f32x2_pack_bits(r[2], r[3]), f32x2_mul(s03.y, ws0), acc0p[c * 4 + 1]);
+                  acc0p[c * 4 + 2] = f32x2_fma(f32x2_pack_bits(r[4], r[5]), f32x2_mul(s47.x, ws0), acc0p[c * 4 + 2]);
+                  acc0p[c * 4 + 3] = f32x2_fma(f32x2_pack_bits(r[6], r[7]), f32x2_mul(s47.y, ws0), acc0p[c * 4 + 3]);
+                  tmem_ld8(t0 + NT + c * 8, r);
+                  tmem_ld_wait();
+                  acc1p[c * 4 + 0] = f32x2_fma(f32x2_pack_bits(r[0], r[1]), f32x2_mul(s03.x, ws1), acc1p[c * 4 + 0]);
+                  acc1p[c * 4 + 1] = f32x2_fma(f32x2_pack_bits(r[2], r[3]), f32x2_mul(s03.y, ws1), acc1p[c * 4 + 1]);
+                  acc1p[c * 4 + 2] = f32x2_fma(f32x2_pack_bits(r[4], r[5]), f32x2_mul(s47.x, ws1), acc1p[c * 4 + 2]);
+                  acc1p[c * 4 + 3] = f32x2_fma(f32x2_pack_bits(r[6], r[7]), f32x2_mul(s47.y, ws1), acc1p[c * 4 + 3]);
                 }
               }
+            } else if (NT == 128) {
+#pragma unroll
+              for (int c = 0; c < 2; ++c) {
+                if (c0 + c * 16 < n) {
+                  uint32_t r0[16], r1[16];
+                  tmem_ld16(t0 + c * 16, r0);
+                  tmem_ld16(t0 + NT + c * 16, r1);
+                  tmem_ld_wait();
+                  promote16(r0, r1, c * 16, sa + c * 16, ws0, ws1, 2);
+                }
+              }
+            } else {                          // this thread's 32 columns: four loads in flight, one wait
+              uint32_t v0[2][16], v1[2][16];
+              tmem_ld16(t0, v0[0]);
+              tmem_ld16(t0 + NT, v1[0]);
+              if (c0 + 16 < n) {
+                tmem_ld16(t0 + 16, v0[1]);
+                tmem_ld16(t0 + NT + 16, v1[1]);
+              }
+              tmem_ld_wait();
+              promote16(v0[0], v1[0], 0, sa, ws0, ws1, 2);
+              if (c0 + 16 < n) promote16(v0[1], v1[1], 16, sa + 16, ws0, ws1, 2);
             }
           }
         }
@@ -463,6 +521,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       }
       if (et == 0) TRACE(2, 1002);
       const int n_out = ok ? n : 0;           // a failed item stores nothing
+      float acc0[CN];
+      float acc1[MODE == 1 ? CN : 1];
+#pragma unroll
+      for (int j = 0; j < CN / 2; ++j) f32x2_unpack(acc0p[j], acc0[2 * j], acc0[2 * j + 1]);
+      if (MODE == 1) {
+#pragma unroll
+        for (int j = 0; j < CN / 2; ++j) f32x2_unpack(acc1p[j], acc1[2 * j], acc1[2 * j + 1]);
+      }
 
       if (MODE == 1) {
         // SwiGLU, then the per-row amax over the 128 features of this tile.  The fast exp and
@@ -566,14 +632,17 @@ cudaError_t gemm_set_attributes() {
   cudaError_t e;
   if ((e = set_smem_attr<1, 32>()) != cudaSuccess) return e;
   if ((e = set_smem_attr<1, 64>()) != cudaSuccess) return e;
+  if ((e = set_smem_attr<1, 128>()) != cudaSuccess) return e;
   if ((e = set_smem_attr<2, 32>()) != cudaSuccess) return e;
-  return set_smem_attr<2, 64>();
+  if ((e = set_smem_attr<2, 64>()) != cudaSuccess) return e;
+  return set_smem_attr<2, 128>();
 }
 
 cudaError_t launch_gemm1(const GemmLaunch& g, const float* w13_scale, int e_local, const Workspace& ws, int num_sms,
                          cudaStream_t st) {
   GemmArgs a{ws.work, ws.meta, ws.a_scale, w13_scale, ws.c_hi, ws.c_lo, ws.c_scale, nullptr, ws.row_cap, e_local,
              ws.status, ws.trace, ws.trace + 6 * 4096};
+  if (g.token_tile == 128) return launch_gemm<1, 128>(g, a, num_sms, st);
   return g.token_tile == 32 ? launch_gemm<1, 32>(g, a, num_sms, st) : launch_gemm<1, 64>(g, a, num_sms, st);
 }
 
@@ -581,6 +650,7 @@ cudaError_t launch_gemm2(const GemmLaunch& g, const float* w2_scale, int e_local
                          cudaStream_t st) {
   GemmArgs a{ws.work, ws.meta, ws.c_scale, w2_scale, nullptr, nullptr, nullptr, ws.o_rows, ws.row_cap, e_local,
              ws.status, ws.trace + 3 * 4096, ws.trace + 7 * 4096};
+  if (g.token_tile == 128) return launch_gemm<2, 128>(g, a, num_sms, st);
   return g.token_tile == 32 ? launch_gemm<2, 32>(g, a, num_sms, st) : launch_gemm<2, 64>(g, a, num_sms, st);
 }
 

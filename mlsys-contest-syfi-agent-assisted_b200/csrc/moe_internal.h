@@ -19,7 +19,7 @@ constexpr int kMaxLocalExperts = 32;
 constexpr int kHBlocks = kHidden / kBlock;   // 56
 constexpr int kIBlocks = kInter / kBlock;    // 16
 constexpr int kRowPad = 16;                  // each expert's row range is padded to this
-constexpr int kMaxTokenTile = 64;            // largest token tile (MMA N) any GEMM variant uses
+constexpr int kMaxTokenTile = 128;           // largest token tile (MMA N) any GEMM variant uses
 constexpr int kMaxGrid = 256;                // upper bound of the GEMM kernels' persistent grid
 constexpr float kLoRatio = 28.0f;            // scale(hi) / scale(lo) of the two-term e4m3 intermediate
 
@@ -83,7 +83,7 @@ struct GemmLaunch {
   CUtensorMap tm_b1;   // GEMM2: c_lo (unused by GEMM1)
   CUtensorMap tm_b0s;  // same tensors with a 16-row box: tiles of <= 16 rows pull half the bytes
   CUtensorMap tm_b1s;
-  int token_tile;      // 32 or 64: token rows per work item, must match the row-list kernel's
+  int token_tile;      // 32, 64 or 128: token rows per work item, must match the row-list kernel's
 };
 
 // Programmatic dependent launch: the kernel may be scheduled while its predecessor in the stream is

@@ -123,6 +123,23 @@ def test_prefill_chunk_matches_oracle(pkg, oracle):
     assert ok, (ostats, stats)
 
 
+def test_every_token_tile_gives_the_same_bits(pkg, oracle, monkeypatch):
+    """The GEMM kernels exist for token tiles of 32, 64 and 128 rows (the library picks by batch size, the
+    environment variable forces one).  The tile changes the work split, never the arithmetic of an output
+    element, so all three must agree bit for bit, and with the oracle within tolerance; 600 tokens over 8
+    experts give every expert several full tiles and a ragged last one."""
+    inp = pkg.make_inputs(num_tokens=600, seed=11, e_local=8, local_expert_offset=16, device=DEV)
+    ref, _, _ = oracle.moe_forward(*inp.args())
+    outs = []
+    for tile in (32, 64, 128):
+        monkeypatch.setenv("SYFI_MOE_TOKEN_TILE", str(tile))
+        out, stats = _run(pkg, inp)
+        ok, ostats = oracle.check_output(out, ref)
+        assert ok, (tile, ostats, stats)
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+
+
 @pytest.mark.parametrize("name", ["e4_off36", "e8_t16"])
 def test_layer_matches_published_reference_vectors(name, pkg, oracle, golden_dir):
     """CPU-generated inputs, output compared with what the definition's published reference produced."""
