@@ -67,6 +67,28 @@ int syfi_moe_forward(syfi_moe_ctx* ctx, const void* routing_logits, const void* 
                      int64_t num_tokens, int32_t num_local_experts, int64_t local_expert_offset,
                      double routed_scaling_factor, void* output, void* stream);
 
+/* One-off weight pre-packing, the layout neighbour of the GEMM loaders (the reference reads the weights
+ * as given through raw pointers, moe.cu:3045-3053, with its GEMM1 tensor map over that layout,
+ * moe.cu:2941-2978).  Rewrites gemm1_weights [E_local, 4096, 7168] and gemm2_weights [E_local, 7168, 2048]
+ * (e4m3, row-major) into buffers of the same sizes in which the 128 x 128-byte tile a work item needs per
+ * K block is 16 KB of consecutive memory, already in the swizzled shared-memory order, and the tiles of a
+ * work item follow each other in consumption order:
+ *   gemm1_packed: [expert][feature tile 0..15][K block 0..55][up tile, gate tile]
+ *   gemm2_packed: [expert][feature tile 0..55][K block 0..15][tile]
+ *   inside a tile: byte b of row r at  r * 128 + (((b >> 4) ^ (r & 7)) << 4) + (b & 15)
+ * Enqueued on `stream`; in-place packing is rejected.  The scales are not touched. */
+int syfi_moe_prepack_weights(syfi_moe_ctx* ctx, const void* gemm1_weights, const void* gemm2_weights,
+                             int32_t num_local_experts, void* gemm1_packed, void* gemm2_packed, void* stream);
+
+/* syfi_moe_forward on weights packed by syfi_moe_prepack_weights (same arguments otherwise, same
+ * results bit for bit): the weight stream becomes sequential, which HBM and L2 serve faster. */
+int syfi_moe_forward_prepacked(syfi_moe_ctx* ctx, const void* routing_logits, const void* routing_bias,
+                               const void* hidden_states, const void* hidden_states_scale,
+                               const void* gemm1_packed, const void* gemm1_weights_scale, const void* gemm2_packed,
+                               const void* gemm2_weights_scale, int64_t num_tokens, int32_t num_local_experts,
+                               int64_t local_expert_offset, double routed_scaling_factor, void* output,
+                               void* stream);
+
 /* Same, but writes the un-rounded f32 [T, 7168] partial sum of this rank's experts instead of
  * bf16 — what an expert-parallel rank feeds to the cross-rank reduction (the reference has no
  * multi-GPU path; its only hook is local_expert_offset, moe.cu:182-185, 250-256). */

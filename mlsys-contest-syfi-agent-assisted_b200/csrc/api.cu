@@ -32,6 +32,7 @@ struct syfi_moe_ctx {
   const void* map_w2 = nullptr;
   const void* map_ws = nullptr;      // workspace generation the maps were built for (a_perm pointer)
   int map_e_local = 0, map_token_tile = 0;
+  bool map_packed = false;
   // second stream of syfi_moe_forward_host: the hidden states travel while the router runs
   cudaStream_t copy_stream = nullptr;
   cudaEvent_t ev_copy_begin = nullptr, ev_copy_done = nullptr;
@@ -161,6 +162,25 @@ int alloc_workspace(Workspace& ws, int64_t max_tokens) {
   return SYFI_MOE_OK;
 }
 
+constexpr int kFlagOutF32 = 1;      // run_layer flags
+constexpr int kFlagPrepacked = 2;
+
+// f32 matrix [rows, cols] (cols contiguous), box [rows, box_cols], no swizzle: the per-K-block scales of a
+// token tile, fetched with one load.
+int make_scale_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return fail(SYFI_MOE_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available");
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 4};
+  const cuuint32_t box[2] = {box_cols, (cuuint32_t)rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(SYFI_MOE_ERR_CUDA, "cuTensorMapEncodeTiled (scales) failed with CUresult %d", (int)r);
+  return SYFI_MOE_OK;
+}
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int validate(syfi_moe_ctx* ctx, const void* const* ptrs, int nptrs, int64_t T, int32_t e_local, int64_t offset,
@@ -192,8 +212,10 @@ int ensure_capacity(syfi_moe_ctx* ctx, int64_t T) {
 
 int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const void* hs, const void* hs_scale,
               const void* w13, const void* w13_scale, const void* w2, const void* w2_scale, int64_t T64,
-              int32_t e_local, int64_t offset, double scaling, void* out, int out_is_f32, cudaStream_t st) {
+              int32_t e_local, int64_t offset, double scaling, void* out, int flags, cudaStream_t st) {
   Workspace& ws = ctx->ws;
+  const int out_is_f32 = flags & kFlagOutF32;
+  const bool packed = (flags & kFlagPrepacked) != 0;   // w13 / w2 point at pre-packed weights
   const int T = (int)T64;
   GemmLaunch& g1 = ctx->g1;
   GemmLaunch& g2 = ctx->g2;
@@ -207,25 +229,36 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
     if (v == 32 || v == 64 || v == 128) token_tile = v;
   }
   const bool maps_valid = ctx->map_w13 == w13 && ctx->map_w2 == w2 && ctx->map_ws == ws.a_perm &&
-                          ctx->map_e_local == e_local && ctx->map_token_tile == token_tile;
+                          ctx->map_e_local == e_local && ctx->map_token_tile == token_tile &&
+                          ctx->map_packed == packed;
   if (!maps_valid) {
   ctx->map_w13 = nullptr;
   g1.token_tile = g2.token_tile = token_tile;
-  if ((rc = make_map(&g1.tm_w, w13, (uint64_t)e_local * 2 * kInter, kHidden, 128))) return rc;
+  g1.w_packed = packed ? static_cast<const uint8_t*>(w13) : nullptr;
+  g2.w_packed = packed ? static_cast<const uint8_t*>(w2) : nullptr;
+  if (packed) {   // the producer fetches packed tiles with untiled copies: no weight tensor map
+    memset(&g1.tm_w, 0, sizeof(g1.tm_w));
+    memset(&g2.tm_w, 0, sizeof(g2.tm_w));
+  } else {
+    if ((rc = make_map(&g1.tm_w, w13, (uint64_t)e_local * 2 * kInter, kHidden, 128))) return rc;
+    if ((rc = make_map(&g2.tm_w, w2, (uint64_t)e_local * kHidden, kInter, 128))) return rc;
+  }
   if ((rc = make_map(&g1.tm_b0, ws.a_perm, ws.row_cap, kHidden, token_tile))) return rc;
   g1.tm_b1 = g1.tm_b0;
   if ((rc = make_map(&g1.tm_b0s, ws.a_perm, ws.row_cap, kHidden, 16))) return rc;
   g1.tm_b1s = g1.tm_b0s;
-  if ((rc = make_map(&g2.tm_w, w2, (uint64_t)e_local * kHidden, kInter, 128))) return rc;
   if ((rc = make_map(&g2.tm_b0, ws.c_hi, ws.row_cap, kInter, token_tile))) return rc;
   if ((rc = make_map(&g2.tm_b1, ws.c_lo, ws.row_cap, kInter, token_tile))) return rc;
   if ((rc = make_map(&g2.tm_b0s, ws.c_hi, ws.row_cap, kInter, 16))) return rc;
   if ((rc = make_map(&g2.tm_b1s, ws.c_lo, ws.row_cap, kInter, 16))) return rc;
+  if ((rc = make_scale_map(&g2.tm_sc, ws.c_scale, kIBlocks, ws.row_cap, token_tile))) return rc;
+  g1.tm_sc = g2.tm_sc;
   ctx->map_w13 = w13;
   ctx->map_w2 = w2;
   ctx->map_ws = ws.a_perm;
   ctx->map_e_local = e_local;
   ctx->map_token_tile = token_tile;
+  ctx->map_packed = packed;
   }
 
   const int grid = ctx->num_sms < kMaxGrid ? ctx->num_sms : kMaxGrid;
@@ -265,7 +298,7 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
 
 int forward_common(syfi_moe_ctx* ctx, const void* logits, const void* bias, const void* hs, const void* hs_scale,
                    const void* w13, const void* w13_scale, const void* w2, const void* w2_scale, int64_t T,
-                   int32_t e_local, int64_t offset, double scaling, void* out, int out_is_f32, void* stream) {
+                   int32_t e_local, int64_t offset, double scaling, void* out, int flags, void* stream) {
   const void* ptrs[] = {logits, bias, hs, hs_scale, w13, w13_scale, w2, w2_scale, out};
   int rc = validate(ctx, ptrs, 9, T, e_local, offset, scaling);
   if (rc) return rc;
@@ -275,7 +308,7 @@ int forward_common(syfi_moe_ctx* ctx, const void* logits, const void* bias, cons
   if (!guard.ok) return fail(SYFI_MOE_ERR_CUDA, "cannot select device %d", ctx->ws.device);
   if ((rc = ensure_capacity(ctx, T))) return rc;
   return run_layer(ctx, logits, bias, hs, hs_scale, w13, w13_scale, w2, w2_scale, T, e_local, offset, scaling, out,
-                   out_is_f32, static_cast<cudaStream_t>(stream));
+                   flags, static_cast<cudaStream_t>(stream));
 }
 
 }  // namespace
@@ -347,6 +380,37 @@ int syfi_moe_forward(syfi_moe_ctx* ctx, const void* routing_logits, const void* 
   return forward_common(ctx, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
                         gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, num_tokens, num_local_experts,
                         local_expert_offset, routed_scaling_factor, output, 0, stream);
+}
+
+int syfi_moe_prepack_weights(syfi_moe_ctx* ctx, const void* gemm1_weights, const void* gemm2_weights,
+                             int32_t num_local_experts, void* gemm1_packed, void* gemm2_packed, void* stream) {
+  if (!ctx) return fail(SYFI_MOE_ERR_INVALID, "context is null");
+  if (num_local_experts < 1 || num_local_experts > kMaxLocalExperts)
+    return fail(SYFI_MOE_ERR_INVALID, "num_local_experts %d must be in [1, %d]", num_local_experts, kMaxLocalExperts);
+  const void* ptrs[] = {gemm1_weights, gemm2_weights, gemm1_packed, gemm2_packed};
+  for (int i = 0; i < 4; ++i) {
+    if (!ptrs[i]) return fail(SYFI_MOE_ERR_INVALID, "tensor argument %d is null", i);
+    if (!aligned16(ptrs[i])) return fail(SYFI_MOE_ERR_INVALID, "tensor argument %d is not 16-byte aligned", i);
+  }
+  if (gemm1_weights == gemm1_packed || gemm2_weights == gemm2_packed)
+    return fail(SYFI_MOE_ERR_INVALID, "packing in place is not supported");
+  DeviceGuard guard(ctx->ws.device);
+  if (!guard.ok) return fail(SYFI_MOE_ERR_CUDA, "cannot select device %d", ctx->ws.device);
+  CU_TRY(launch_prepack(static_cast<const uint8_t*>(gemm1_weights), static_cast<const uint8_t*>(gemm2_weights),
+                        num_local_experts, static_cast<uint8_t*>(gemm1_packed), static_cast<uint8_t*>(gemm2_packed),
+                        static_cast<cudaStream_t>(stream)));
+  return SYFI_MOE_OK;
+}
+
+int syfi_moe_forward_prepacked(syfi_moe_ctx* ctx, const void* routing_logits, const void* routing_bias,
+                               const void* hidden_states, const void* hidden_states_scale,
+                               const void* gemm1_packed, const void* gemm1_weights_scale, const void* gemm2_packed,
+                               const void* gemm2_weights_scale, int64_t num_tokens, int32_t num_local_experts,
+                               int64_t local_expert_offset, double routed_scaling_factor, void* output,
+                               void* stream) {
+  return forward_common(ctx, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_packed,
+                        gemm1_weights_scale, gemm2_packed, gemm2_weights_scale, num_tokens, num_local_experts,
+                        local_expert_offset, routed_scaling_factor, output, kFlagPrepacked, stream);
 }
 
 int syfi_moe_forward_partial_f32(syfi_moe_ctx* ctx, const void* routing_logits, const void* routing_bias,

@@ -65,12 +65,16 @@ template <int MODE, int NT> struct Cfg {
   // (the shared-memory ring still moves two, for the K-adjacent request pattern).
   static constexpr int kTKps = NT == 128 ? 1 : kKps;
   static constexpr int kPairs = kSlots / kTKps;                                 // TMEM ring entries
-  static constexpr int kScaleBufs = MODE == 2 ? 2 : 1;   // mode 2 prefetches the next item's scales
-  static constexpr int kColSplit = NT / 32;               // epilogue warps per TMEM lane quarter
+  static constexpr int kScaleBufs = MODE == 2 ? 3 : 1;   // mode 2 prefetches the scales two items ahead
+  // Epilogue warps per TMEM lane quarter: each owns 16 token columns (32 at the 128-row tile, where the
+  // thread limit of a CTA caps the split).  Two or more warps per scheduler hide the latency of the
+  // promotion chain and of the SwiGLU / requantisation epilogue, which a single warp runs back to back:
+  // measured 3-8 % faster per call than 32 columns per warp; 8 columns per warp was no better than 16.
+  static constexpr int kColSplit = NT == 128 ? 4 : NT / 16;
   static constexpr int kThreads = 64 + 128 * kColSplit;   // producer warp + MMA warp + epilogue warps
   static constexpr int kSmemBytes = 1024 /* alignment slack */ + kGroups * kGroupBytes +
                                     4 * (kScaleBufs * (kKBlocks * NT + 128) + 4 * NT + 2 * NT) +
-                                    8 * (2 * kGroups + 2 * kPairs) +
+                                    8 * (2 * kGroups + 2 * kPairs + 3) +
                                     kMaxLocalExperts * static_cast<int>(sizeof(ExpertWork)) + 16;
   static_assert(kSmemBytes <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
   static_assert(kKBlocks % kKps == 0 && kSlots % kTKps == 0 && kKps % kTKps == 0,
@@ -79,6 +83,10 @@ template <int MODE, int NT> struct Cfg {
 };
 
 struct GemmArgs {
+  // Pre-packed weights (see prepack.cu) or nullptr.  When set, the weight tiles of a work item are
+  // consecutive 16 KB images of what the tiled loads would have written to shared memory, and the
+  // producer fetches them with untiled bulk copies instead of going through the weight tensor map.
+  const uint8_t* w_packed;
   const ExpertWork* work;
   const int* meta;
   const float* act_scale;   // [K blocks][row_cap] scales of the token-side operand
@@ -143,7 +151,8 @@ template <int MODE, int NT>
 __global__ void __launch_bounds__((Cfg<MODE, NT>::kThreads), 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_b0,
                     const __grid_constant__ CUtensorMap tm_b1, const __grid_constant__ CUtensorMap tm_b0s,
-                    const __grid_constant__ CUtensorMap tm_b1s, const GemmArgs p) {
+                    const __grid_constant__ CUtensorMap tm_b1s, const __grid_constant__ CUtensorMap tm_sc,
+                    const GemmArgs p) {
   using C = Cfg<MODE, NT>;
   constexpr int G = C::kGroups;           // smem ring entries, each kKps K blocks
   constexpr int KPS = C::kKps;
@@ -153,6 +162,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   constexpr int TKPS = C::kTKps;
   constexpr int PAIRS = C::kPairs;        // TMEM ring entries, each kTKps accumulator-pair slots
   constexpr int kBTile = C::kBTile;
+  // Layout of one ring entry (KPS K blocks).  Mode 1: per K block [up tile][gate tile][token tile].
+  // Mode 2: the weight tiles of all K blocks first (adjacent, so pre-packed weights arrive as one
+  // copy), then per K block [hi tile][lo tile].
+  auto w_off = [](int k) { return MODE == 1 ? k * C::kStageBytes : k * kATile; };
+  auto b_off = [](int k) { return MODE == 1 ? k * C::kStageBytes + 2 * kATile : KPS * kATile + k * 2 * kBTile; };
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
@@ -165,7 +179,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   uint64_t* empty = full + G;
   uint64_t* tfull = empty + G;
   uint64_t* tempty = tfull + PAIRS;
-  ExpertWork* s_work = reinterpret_cast<ExpertWork*>(tempty + PAIRS);
+  uint64_t* sfull = tempty + PAIRS;       // [3] mode 2: a scale buffer has landed
+  ExpertWork* s_work = reinterpret_cast<ExpertWork*>(sfull + 3);
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_work + kMaxLocalExperts);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
 
@@ -186,13 +201,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   if (threadIdx.x == 0) {
     for (int i = 0; i < G; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
     for (int i = 0; i < PAIRS; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 4 * C::kColSplit); }
+    for (int i = 0; i < 3; ++i) mbar_init(&sfull[i], 1);
     *s_abort = 0;
     fence_barrier_init();
-    tma_prefetch_desc(&tm_w);
+    if (p.w_packed == nullptr) tma_prefetch_desc(&tm_w);
     tma_prefetch_desc(&tm_b0);
     if (MODE == 2) tma_prefetch_desc(&tm_b1);
     tma_prefetch_desc(&tm_b0s);
     if (MODE == 2) tma_prefetch_desc(&tm_b1s);
+    if (MODE == 2) tma_prefetch_desc(&tm_sc);
   }
   if (warp == 1) {
     tmem_alloc(s_tmem, kTmemCols);
@@ -255,22 +272,31 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           // back: L2 serves a row's 256 contiguous bytes far faster than two separate 128-byte visits.
           uint8_t* st0 = smem + g * C::kGroupBytes;
           const int x0 = step * KPS * 128;
+          if (p.w_packed != nullptr) {
+            if (MODE == 1) {            // 32 KB per K block: up tile, gate tile
+              const uint8_t* src = p.w_packed + (static_cast<size_t>(im.expert * FT + im.ft) * KB + step * KPS) * (2 * kATile);
 #pragma unroll
-          for (int k = 0; k < KPS; ++k) tma_load_2d(st0 + k * C::kStageBytes, &tm_w, &full[g], x0 + k * 128, wrow, pol_w);
-          if (MODE == 1) {
-#pragma unroll
-            for (int k = 0; k < KPS; ++k)
-              tma_load_2d(st0 + k * C::kStageBytes + kATile, &tm_w, &full[g], x0 + k * 128, wrow + kInter, pol_w);
-#pragma unroll
-            for (int k = 0; k < KPS; ++k)
-              tma_load_2d(st0 + k * C::kStageBytes + 2 * kATile, mb0, &full[g], x0 + k * 128, im.row_start, pol_b);
+              for (int k = 0; k < KPS; ++k)
+                bulk_load(st0 + w_off(k), src + static_cast<size_t>(k) * 2 * kATile, 2 * kATile, &full[g], pol_w);
+            } else {                    // the K blocks of a step are adjacent: one copy
+              const uint8_t* src = p.w_packed + (static_cast<size_t>(im.expert * FT + im.ft) * KB + step * KPS) * kATile;
+              bulk_load(st0, src, KPS * kATile, &full[g], pol_w);
+            }
           } else {
 #pragma unroll
-            for (int k = 0; k < KPS; ++k)
-              tma_load_2d(st0 + k * C::kStageBytes + kATile, mb0, &full[g], x0 + k * 128, im.row_start, pol_b);
+            for (int k = 0; k < KPS; ++k) tma_load_2d(st0 + w_off(k), &tm_w, &full[g], x0 + k * 128, wrow, pol_w);
+            if (MODE == 1) {
+#pragma unroll
+              for (int k = 0; k < KPS; ++k)
+                tma_load_2d(st0 + w_off(k) + kATile, &tm_w, &full[g], x0 + k * 128, wrow + kInter, pol_w);
+            }
+          }
+#pragma unroll
+          for (int k = 0; k < KPS; ++k) tma_load_2d(st0 + b_off(k), mb0, &full[g], x0 + k * 128, im.row_start, pol_b);
+          if (MODE == 2) {
 #pragma unroll
             for (int k = 0; k < KPS; ++k)
-              tma_load_2d(st0 + k * C::kStageBytes + kATile + kBTile, mb1, &full[g], x0 + k * 128, im.row_start, pol_b);
+              tma_load_2d(st0 + b_off(k) + kBTile, mb1, &full[g], x0 + k * 128, im.row_start, pol_b);
           }
           ++it;
           if (++g == G) { g = 0; ph ^= 1u; }
@@ -305,12 +331,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 #pragma unroll
             for (int k2 = 0; k2 < TKPS; ++k2) {
               const int k = tk * TKPS + k2;
-              const uint32_t st = smem_u32(smem + g * C::kGroupBytes + k * C::kStageBytes);
+              const uint32_t gb = smem_u32(smem + g * C::kGroupBytes);
               const uint32_t d0 = tmem_base + (pr * TKPS + k2) * (2 * NT);
               if (MODE == 1) {
-                const uint64_t a0 = umma_smem_desc_sw128(st);
-                const uint64_t a1 = umma_smem_desc_sw128(st + kATile);
-                const uint64_t b0 = umma_smem_desc_sw128(st + 2 * kATile);
+                const uint64_t a0 = umma_smem_desc_sw128(gb + w_off(k));
+                const uint64_t a1 = umma_smem_desc_sw128(gb + w_off(k) + kATile);
+                const uint64_t b0 = umma_smem_desc_sw128(gb + b_off(k));
 #pragma unroll
                 for (int k4 = 0; k4 < 4; ++k4) {
                   // 32 bytes of K per MMA: +2 in the 16-byte-unit address field
@@ -318,8 +344,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
                   umma_f8(d0 + NT, a1 + 2 * k4, b0 + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
                 }
               } else {
-                const uint64_t a0 = umma_smem_desc_sw128(st);
-                const uint64_t b0 = umma_smem_desc_sw128(st + kATile);   // hi rows, then lo rows
+                const uint64_t a0 = umma_smem_desc_sw128(gb + w_off(k));
+                const uint64_t b0 = umma_smem_desc_sw128(gb + b_off(k));   // hi rows, then lo rows
 #pragma unroll
                 for (int k4 = 0; k4 < 4; ++k4) umma_f8(d0, a0 + 2 * k4, b0 + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
               }
@@ -341,7 +367,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     constexpr int CS = C::kColSplit;
     constexpr int CN = NT / CS;
     constexpr int kEpi = 128 * CS;          // epilogue threads
-    static_assert(CN == 32, "the drain below moves 32 columns per thread and step");
+    static_assert(CN == 16 || CN == 32, "the drain below moves 16 or 32 columns per thread and step");
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     const int c0 = ((warp - 2) >> 2) * CN;  // first column of this thread's share
     const int et = threadIdx.x - 64;        // 0..kEpi-1 among the epilogue threads
@@ -350,15 +376,25 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     bool ok = true;
     int sbuf = 0;
     int cached_row_start = -1;              // token tile whose activation scales sit in shared memory (mode 1)
-    if (MODE == 2 && u_begin < u_end) {
-      const Item nx = decode_item<FT, NT>(s_work, p.e_local, item_at(u_begin));
-      for (int i = et; i < KB * NT; i += kEpi) {
-        const int kb = i / NT, j = i % NT;
-        if (j < nx.n) cp_async_f32(s_scales + i, p.act_scale + static_cast<size_t>(kb) * p.row_cap + nx.row_start + j);
+    // Mode 2 fetches an item's scales two items ahead of their use, with two loads issued by one thread:
+    // the [16 K blocks x NT rows] activation scales through a tensor map and the 16 weight scales as a
+    // 64-byte bulk copy, both counted on sfull[buf].  (While the weight stream saturates HBM a small read
+    // waits several microseconds behind everything the TMA rings have in flight, and per-thread cp.async
+    // requests stalled their issuing warps for 1000-3000 cycles per item.)
+    auto prefetch_scales = [&](int uu, int buf) {
+      if (MODE == 2 && et == 0 && uu < u_end) {
+        const Item nx = decode_item<FT, NT>(s_work, p.e_local, item_at(uu));
+        float* d_act = s_scales + buf * kScaleStride;
+        mbar_arrive_expect_tx(&sfull[buf], (KB * NT + KB) * 4);
+        tma_load_2d(d_act, &tm_sc, &sfull[buf], nx.row_start, 0, l2_policy_evict_last());
+        bulk_load(d_act + KB * NT, p.w_scale + (static_cast<size_t>(nx.expert) * kHBlocks + nx.ft) * kIBlocks,
+                  KB * 4, &sfull[buf], l2_policy_evict_last());
       }
-      if (et < KB)
-        cp_async_f32(s_scales + KB * NT + et,
-                     p.w_scale + (static_cast<size_t>(nx.expert) * kHBlocks + nx.ft) * kIBlocks + et);
+    };
+    uint32_t sph = 0;                       // phase bits of sfull[0..2]
+    if (MODE == 2) {
+      prefetch_scales(u_begin, 0);
+      prefetch_scales(u_begin + STEPS, 1);
     }
     // After a failed wait a warp keeps walking the work list and still joins every named
     // barrier below (doing no other work), so the epilogue warps can never strand each other.
@@ -378,17 +414,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         // the activation scales depend on the token tile only: consecutive items of a CTA mostly
         // share it (same expert, next feature tile), so they are reloaded only when it changes
         if (im.row_start != cached_row_start) {
-          constexpr int kIters = KB * NT / kEpi;
-          static_assert(kIters * kEpi == KB * NT, "scale staging must divide evenly");
+          constexpr int kIters = (KB * NT + kEpi - 1) / kEpi;
           float tmp[kIters];
 #pragma unroll
           for (int r = 0; r < kIters; ++r) {   // all loads in flight before the first store
             const int i = et + r * kEpi;
             const int kb = i / NT, j = i % NT;
-            tmp[r] = (j < n) ? __ldg(p.act_scale + static_cast<size_t>(kb) * p.row_cap + im.row_start + j) : 0.0f;
+            tmp[r] = (i < KB * NT && j < n) ? __ldg(p.act_scale + static_cast<size_t>(kb) * p.row_cap + im.row_start + j) : 0.0f;
           }
 #pragma unroll
-          for (int r = 0; r < kIters; ++r) s_act[et + r * kEpi] = tmp[r];
+          for (int r = 0; r < kIters; ++r)
+            if (et + r * kEpi < KB * NT) s_act[et + r * kEpi] = tmp[r];
           cached_row_start = ok ? im.row_start : -1;
         }
         if (et < KB && ok) {
@@ -397,26 +433,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         }
         named_bar_sync(1, kEpi);
       } else {
-        // Scales of this item were requested with cp.async while the previous item ran (the very
-        // first item's just before the loop); one barrier publishes them and retires the buffer
-        // the item before used, which then receives the next item's scales.  Columns >= n are
-        // never read, so they are not filled.
+        // Scales of this item were requested two items ago (the first two before the loop); the
+        // barrier retires the buffer the previous item used, which then receives the scales of the
+        // item after next.  Columns >= n hold other rows' scales and are never read.
         s_act = s_scales + sbuf * kScaleStride;
         s_ws = s_act + KB * NT;
-        cp_async_wait_all();
+        if (ok && !mbar_wait_bounded(&sfull[sbuf], (sph >> sbuf) & 1u, s_abort, kStatusWaitTimeoutEpilogue)) ok = false;
+        sph ^= 1u << sbuf;
+        if (et == 0) TRACE(2, 1003);
         named_bar_sync(1, kEpi);
-        if (u < u_end && ok) {                // u already points at the next segment
-          const Item nx = decode_item<FT, NT>(s_work, p.e_local, item_at(u));
-          float* d_act = s_scales + (sbuf ^ 1) * kScaleStride;
-          for (int i = et; i < KB * NT; i += kEpi) {
-            const int kb = i / NT, j = i % NT;
-            if (j < nx.n) cp_async_f32(d_act + i, p.act_scale + static_cast<size_t>(kb) * p.row_cap + nx.row_start + j);
-          }
-          if (et < KB)
-            cp_async_f32(d_act + KB * NT + et,
-                         p.w_scale + (static_cast<size_t>(nx.expert) * kHBlocks + nx.ft) * kIBlocks + et);
-        }
-        sbuf ^= 1;
+        if (et == 0) TRACE(2, 1004);
+        prefetch_scales(u + STEPS, sbuf == 0 ? 2 : sbuf - 1);   // u already points at the next item
+        sbuf = sbuf == 2 ? 0 : sbuf + 1;
       }
       if (et == 0) TRACE(2, 1001);
 
@@ -466,7 +494,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           const uint64_t ws1 = (MODE == 1) ? f32x2_pack(s_ws[64 + kb], s_ws[64 + kb]) : 0ull;
           const float* sa = s_act + kb * NT + c0;
           if (c0 < n) {
-            if (NT == 128 && MODE == 1) {
+            if constexpr (CN == 16) {         // both accumulators of this thread's 16 columns in flight
+              uint32_t r0[16], r1[16];
+              tmem_ld16(t0, r0);
+              tmem_ld16(t0 + NT, r1);
+              tmem_ld_wait();
+              promote16(r0, r1, 0, sa, ws0, ws1, 2);
+            } else if constexpr (NT == 128 && MODE == 1) {
               // 18 warps share the register file and 64 registers of a thread hold accumulators: eight
               // columns of one accumulator at a time
 #pragma unroll
@@ -489,7 +523,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
                   acc1p[c * 4 + 3] = f32x2_fma(f32x2_pack_bits(r[6], r[7]), f32x2_mul(s47.y, ws1), acc1p[c * 4 + 3]);
                 }
               }
-            } else if (NT == 128) {
+            } else if constexpr (NT == 128) {
 #pragma unroll
               for (int c = 0; c < 2; ++c) {
                 if (c0 + c * 16 < n) {
@@ -617,7 +651,7 @@ template <int MODE, int NT>
 cudaError_t launch_gemm(const GemmLaunch& g, const GemmArgs& a, int num_sms, cudaStream_t st) {
   return launch_dependent(grouped_gemm_kernel<MODE, NT>, dim3(num_sms), dim3(Cfg<MODE, NT>::kThreads),
                           static_cast<size_t>(Cfg<MODE, NT>::kSmemBytes), st, g.tm_w, g.tm_b0, g.tm_b1, g.tm_b0s,
-                          g.tm_b1s, a);
+                          g.tm_b1s, g.tm_sc, a);
 }
 
 template <int MODE, int NT>
@@ -640,7 +674,7 @@ cudaError_t gemm_set_attributes() {
 
 cudaError_t launch_gemm1(const GemmLaunch& g, const float* w13_scale, int e_local, const Workspace& ws, int num_sms,
                          cudaStream_t st) {
-  GemmArgs a{ws.work, ws.meta, ws.a_scale, w13_scale, ws.c_hi, ws.c_lo, ws.c_scale, nullptr, ws.row_cap, e_local,
+  GemmArgs a{g.w_packed, ws.work, ws.meta, ws.a_scale, w13_scale, ws.c_hi, ws.c_lo, ws.c_scale, nullptr, ws.row_cap, e_local,
              ws.status, ws.trace, ws.trace + 6 * 4096};
   if (g.token_tile == 128) return launch_gemm<1, 128>(g, a, num_sms, st);
   return g.token_tile == 32 ? launch_gemm<1, 32>(g, a, num_sms, st) : launch_gemm<1, 64>(g, a, num_sms, st);
@@ -648,7 +682,7 @@ cudaError_t launch_gemm1(const GemmLaunch& g, const float* w13_scale, int e_loca
 
 cudaError_t launch_gemm2(const GemmLaunch& g, const float* w2_scale, int e_local, const Workspace& ws, int num_sms,
                          cudaStream_t st) {
-  GemmArgs a{ws.work, ws.meta, ws.c_scale, w2_scale, nullptr, nullptr, nullptr, ws.o_rows, ws.row_cap, e_local,
+  GemmArgs a{g.w_packed, ws.work, ws.meta, ws.c_scale, w2_scale, nullptr, nullptr, nullptr, ws.o_rows, ws.row_cap, e_local,
              ws.status, ws.trace + 3 * 4096, ws.trace + 7 * 4096};
   if (g.token_tile == 128) return launch_gemm<2, 128>(g, a, num_sms, st);
   return g.token_tile == 32 ? launch_gemm<2, 32>(g, a, num_sms, st) : launch_gemm<2, 64>(g, a, num_sms, st);

@@ -83,6 +83,8 @@ struct GemmLaunch {
   CUtensorMap tm_b1;   // GEMM2: c_lo (unused by GEMM1)
   CUtensorMap tm_b0s;  // same tensors with a 16-row box: tiles of <= 16 rows pull half the bytes
   CUtensorMap tm_b1s;
+  CUtensorMap tm_sc;   // GEMM2: c_scale as f32 [16, row_cap], box 16 x token_tile (one load per work item)
+  const uint8_t* w_packed = nullptr;   // pre-packed weights (tm_w unused) or nullptr
   int token_tile;      // 32, 64 or 128: token rows per work item, must match the row-list kernel's
 };
 
@@ -117,6 +119,11 @@ cudaError_t launch_gemm1(const GemmLaunch& g, const float* w13_scale, int e_loca
                          cudaStream_t st);
 cudaError_t launch_gemm2(const GemmLaunch& g, const float* w2_scale, int e_local, const Workspace& ws, int num_sms,
                          cudaStream_t st);
+// Weight pre-packing (prepack.cu): [E, rows, K] row-major e4m3 -> per (expert, 128-row feature tile, 128-byte K
+// block) one 16 KB tile holding the rows' 128 bytes with the 128-byte shared-memory swizzle already applied;
+// GEMM1's up and gate tiles of the same features interleave per K block.
+cudaError_t launch_prepack(const uint8_t* w13, const uint8_t* w2, int e_local, uint8_t* w13_packed,
+                           uint8_t* w2_packed, cudaStream_t st);
 cudaError_t launch_combine(int T, const Workspace& ws, void* out, int out_is_f32, cudaStream_t st);
 cudaError_t gemm_set_attributes();
 

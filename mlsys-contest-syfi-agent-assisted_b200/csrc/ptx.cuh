@@ -198,11 +198,14 @@ __device__ __forceinline__ uint32_t umma_idesc_e4m3_m128(uint32_t n) {
 }
 
 // ------------------------------------------------------------- cp.async (4 B)
-__device__ __forceinline__ void cp_async_f32(float* smem_dst, const float* gmem_src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() {
-  asm volatile("cp.async.wait_all;" ::: "memory");
+// Untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16 bytes),
+// completion counted in bytes on an mbarrier like the tiled loads.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar,
+                                          uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+      :: "r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
 }
 
 // ------------------------------------------------------------ small helpers

@@ -35,6 +35,8 @@ ABI = {
     "syfi_moe_destroy": (ctypes.c_int, [_vp]),
     "syfi_moe_forward": (ctypes.c_int, [_vp] + [_vp] * 8 + [_i64, _i32, _i64, _f64, _vp, _vp]),
     "syfi_moe_forward_partial_f32": (ctypes.c_int, [_vp] + [_vp] * 8 + [_i64, _i32, _i64, _f64, _vp, _vp]),
+    "syfi_moe_prepack_weights": (ctypes.c_int, [_vp, _vp, _vp, _i32, _vp, _vp, _vp]),
+    "syfi_moe_forward_prepacked": (ctypes.c_int, [_vp] + [_vp] * 8 + [_i64, _i32, _i64, _f64, _vp, _vp]),
     "syfi_moe_forward_host": (ctypes.c_int, [_vp] + [_vp] * 8 + [_i64, _i32, _i64, _f64, _vp, _vp]),
     "syfi_moe_route": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i32, _i64, _f64, _vp, _vp, _vp]),
     "syfi_moe_ep_region_bytes": (_i64, [_i32, _i64]),
@@ -247,6 +249,66 @@ def run_moe(routing_logits, routing_bias, hidden_states, hidden_states_scale, ge
               hidden_states_scale.data_ptr(), gemm1_weights.data_ptr(), gemm1_weights_scale.data_ptr(),
               gemm2_weights.data_ptr(), gemm2_weights_scale.data_ptr(), T, E, off, float(routed_scaling_factor),
               output.data_ptr(), _stream_ptr(stream, ctx.device)))
+    return output
+
+
+class PackedWeights:
+    """Weights rewritten by :func:`prepack_weights`: the two packed byte tensors (same sizes as the
+    originals) and the expert count.  Pass ``packed.gemm1`` / ``packed.gemm2`` to :func:`run_moe_prepacked`
+    in place of the weight tensors."""
+
+    def __init__(self, gemm1, gemm2, num_local_experts):
+        self.gemm1, self.gemm2, self.num_local_experts = gemm1, gemm2, int(num_local_experts)
+
+
+def prepack_weights(gemm1_weights, gemm2_weights, *, stream=None) -> PackedWeights:
+    """One-off re-layout of the expert weights for :func:`run_moe_prepacked` (see ``syfi_moe_prepack_weights``
+    in the C header for the layout).  The originals are left untouched and may be freed afterwards."""
+    f8 = torch.float8_e4m3fn
+    if not isinstance(gemm1_weights, torch.Tensor) or gemm1_weights.dim() != 3 or gemm1_weights.device.type != "cuda":
+        raise ValueError("gemm1_weights must be a 3-D CUDA tensor [E_local, 4096, 7168]")
+    E, dev = gemm1_weights.shape[0], gemm1_weights.device
+    if E < 1 or E > MAX_LOCAL_EXPERTS:
+        raise ValueError(f"number of local experts must be in [1, {MAX_LOCAL_EXPERTS}], got {E}")
+    _expect(gemm1_weights, "gemm1_weights", f8, (E, 2 * INTER, HIDDEN), dev)
+    _expect(gemm2_weights, "gemm2_weights", f8, (E, HIDDEN, INTER), dev)
+    p1 = torch.empty(E * 2 * INTER * HIDDEN, dtype=torch.uint8, device=dev)
+    p2 = torch.empty(E * HIDDEN * INTER, dtype=torch.uint8, device=dev)
+    ctx = get_context(dev.index if dev.index is not None else torch.cuda.current_device(), 1)
+    _check(ctx.lib.syfi_moe_prepack_weights(ctx.handle, gemm1_weights.data_ptr(), gemm2_weights.data_ptr(), E,
+                                            p1.data_ptr(), p2.data_ptr(), _stream_ptr(stream, ctx.device)))
+    return PackedWeights(p1, p2, E)
+
+
+def run_moe_prepacked(routing_logits, routing_bias, hidden_states, hidden_states_scale, packed: PackedWeights,
+                      gemm1_weights_scale, gemm2_weights_scale, local_expert_offset, routed_scaling_factor, output,
+                      *, stream=None):
+    """:func:`run_moe` on weights packed once by :func:`prepack_weights`; bit-identical results."""
+    if not isinstance(packed, PackedWeights):
+        raise ValueError("packed must come from prepack_weights()")
+    E, dev = packed.num_local_experts, packed.gemm1.device
+    if not isinstance(routing_logits, torch.Tensor) or routing_logits.dim() != 2:
+        raise ValueError("routing_logits must be a 2-D tensor [T, 256]")
+    T = routing_logits.shape[0]
+    off = int(local_expert_offset)
+    if off < 0 or off + E > E_GLOBAL:
+        raise ValueError(f"local experts [{off}, {off + E}) outside [0, {E_GLOBAL})")
+    f8 = torch.float8_e4m3fn
+    _expect(routing_logits, "routing_logits", torch.float32, (T, E_GLOBAL), dev)
+    _expect(routing_bias, "routing_bias", torch.bfloat16, (E_GLOBAL,), dev)
+    _expect(hidden_states, "hidden_states", f8, (T, HIDDEN), dev)
+    _expect(hidden_states_scale, "hidden_states_scale", torch.float32, (HIDDEN // 128, T), dev)
+    _expect(gemm1_weights_scale, "gemm1_weights_scale", torch.float32, (E, 2 * INTER // 128, HIDDEN // 128), dev)
+    _expect(gemm2_weights_scale, "gemm2_weights_scale", torch.float32, (E, HIDDEN // 128, INTER // 128), dev)
+    _expect(output, "output", torch.bfloat16, (T, HIDDEN), dev)
+    if T == 0:
+        return output
+    ctx = get_context(dev.index if dev.index is not None else torch.cuda.current_device(), T)
+    _check(ctx.lib.syfi_moe_forward_prepacked(
+        ctx.handle, routing_logits.data_ptr(), routing_bias.data_ptr(), hidden_states.data_ptr(),
+        hidden_states_scale.data_ptr(), packed.gemm1.data_ptr(), gemm1_weights_scale.data_ptr(),
+        packed.gemm2.data_ptr(), gemm2_weights_scale.data_ptr(), T, E, off, float(routed_scaling_factor),
+        output.data_ptr(), _stream_ptr(stream, ctx.device)))
     return output
 
 

@@ -140,6 +140,50 @@ def test_every_token_tile_gives_the_same_bits(pkg, oracle, monkeypatch):
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
 
 
+def _swizzled_tiles(x):
+    """x: [..., 128 rows, 8 chunks, 16 bytes] -> chunk c of row r moved to chunk c ^ (r & 7)."""
+    r = torch.arange(128, device=x.device)[:, None]
+    c = torch.arange(8, device=x.device)[None, :]
+    return x[..., r, c ^ (r & 7), :]
+
+
+def test_prepacked_weight_layout(pkg):
+    """Every byte of the packed buffers is where the header says: tiles of 128 rows x 128 bytes in
+    (expert, feature tile, K block[, up/gate]) order with the 128-byte swizzle inside a tile."""
+    E = 2
+    g = torch.Generator(device=DEV).manual_seed(5)
+    w13 = torch.randint(0, 256, (E, 4096, 7168), dtype=torch.uint8, device=DEV, generator=g)
+    w2 = torch.randint(0, 256, (E, 7168, 2048), dtype=torch.uint8, device=DEV, generator=g)
+    packed = pkg.prepack_weights(w13.view(torch.float8_e4m3fn), w2.view(torch.float8_e4m3fn))
+    torch.cuda.synchronize()
+    # [e, half, ft, r, kb, chunk, byte] -> [e, ft, kb, half, r, chunk, byte]
+    want13 = _swizzled_tiles(w13.view(E, 2, 16, 128, 56, 8, 16).permute(0, 2, 4, 1, 3, 5, 6)).reshape(-1)
+    # [e, ft, r, kb, chunk, byte] -> [e, ft, kb, r, chunk, byte]
+    want2 = _swizzled_tiles(w2.view(E, 56, 128, 16, 8, 16).permute(0, 1, 3, 2, 4, 5)).reshape(-1)
+    assert torch.equal(packed.gemm1, want13)
+    assert torch.equal(packed.gemm2, want2)
+
+
+@pytest.mark.parametrize("T,E,off,tile", [(1, 8, 0, None), (64, 32, 0, None), (333, 8, 24, None), (333, 8, 24, 128),
+                                          (1500, 8, 8, None)])
+def test_prepacked_forward_is_bit_identical(T, E, off, tile, pkg, monkeypatch):
+    """The packed path changes how weight tiles reach shared memory, not one arithmetic operation."""
+    if tile is not None:
+        monkeypatch.setenv("SYFI_MOE_TOKEN_TILE", str(tile))
+    inp = pkg.make_inputs(num_tokens=T, seed=21, e_local=E, local_expert_offset=off, device=DEV)
+    out, _ = _run(pkg, inp)
+    packed = pkg.prepack_weights(inp.gemm1_weights, inp.gemm2_weights)
+    out_p = torch.full_like(out, float("nan"))
+    pkg.run_moe_prepacked(inp.routing_logits, inp.routing_bias, inp.hidden_states, inp.hidden_states_scale, packed,
+                          inp.gemm1_weights_scale, inp.gemm2_weights_scale, off, inp.routed_scaling_factor, out_p)
+    pkg.get_context(0).check()
+    assert torch.isfinite(out_p.float()).all()
+    assert torch.equal(out, out_p)
+    # and back on the plain path with the same context (the cached tensor maps must be rebuilt)
+    out2, _ = _run(pkg, inp)
+    assert torch.equal(out, out2)
+
+
 @pytest.mark.parametrize("name", ["e4_off36", "e8_t16"])
 def test_layer_matches_published_reference_vectors(name, pkg, oracle, golden_dir):
     """CPU-generated inputs, output compared with what the definition's published reference produced."""
