@@ -139,7 +139,8 @@ int alloc_workspace(Workspace& ws, int64_t max_tokens) {
   CU_TRY(dev_alloc(&ws.topk_idx, T * kTopK, &total));
   CU_TRY(dev_alloc(&ws.topk_w, T * kTopK, &total));
   CU_TRY(dev_alloc(&ws.local_mask, T, &total));
-  CU_TRY(dev_alloc(&ws.counts, kMaxLocalExperts, &total));
+  CU_TRY(dev_alloc(&ws.counts, 2 * kMaxLocalExperts, &total));
+  ws.ready = ws.counts + kMaxLocalExperts;
   CU_TRY(dev_alloc(&ws.meta, kMetaInts, &total));
   CU_TRY(dev_alloc(&ws.status, 4, &total));
   CU_TRY(dev_alloc(&ws.trace, 8 * 4096, &total));

@@ -71,10 +71,10 @@ template <int MODE, int NT> struct Cfg {
   // promotion chain and of the SwiGLU / requantisation epilogue, which a single warp runs back to back:
   // measured 3-8 % faster per call than 32 columns per warp; 8 columns per warp was no better than 16.
   static constexpr int kColSplit = NT == 128 ? 4 : NT / 16;
-  static constexpr int kThreads = 64 + 128 * kColSplit;   // producer warp + MMA warp + epilogue warps
+  static constexpr int kThreads = 64 + 128 * kColSplit + 32;   // producer, MMA, epilogue warps, publisher warp
   static constexpr int kSmemBytes = 1024 /* alignment slack */ + kGroups * kGroupBytes +
                                     4 * (kScaleBufs * (kKBlocks * NT + 128) + 4 * NT + 2 * NT) +
-                                    8 * (2 * kGroups + 2 * kPairs + 3) +
+                                    8 * (2 * kGroups + 2 * kPairs + 6) +
                                     kMaxLocalExperts * static_cast<int>(sizeof(ExpertWork)) + 16;
   static_assert(kSmemBytes <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
   static_assert(kKBlocks % kKps == 0 && kSlots % kTKps == 0 && kKps % kTKps == 0,
@@ -97,6 +97,7 @@ struct GemmArgs {
   float* o_rows;            // mode 2 output [row_cap][7168]
   int row_cap;
   int e_local;
+  int* ready;               // [32] GEMM1 items finished per expert: mode 1 increments, mode 2 waits on it
   int* status;
   long long* trace;         // [3][4096] timeline of CTA 0 when built with SYFI_TRACE, else unused
   long long* trace_cta;     // [grid][5] per-CTA start/end (globaltimer, clock64) and SM id, SYFI_TRACE only
@@ -180,9 +181,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   uint64_t* tfull = empty + G;
   uint64_t* tempty = tfull + PAIRS;
   uint64_t* sfull = tempty + PAIRS;       // [3] mode 2: a scale buffer has landed
-  ExpertWork* s_work = reinterpret_cast<ExpertWork*>(sfull + 3);
+  uint64_t* sempty = sfull + 3;           // [3] mode 2: the epilogue is done with a scale buffer
+  ExpertWork* s_work = reinterpret_cast<ExpertWork*>(sempty + 3);
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_work + kMaxLocalExperts);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+  int* s_done = reinterpret_cast<int*>(s_tmem + 2);   // mode 1: epilogue warps that finished storing an item (running total); mode 2: items cleared for loading
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int trace_n = 0;
@@ -201,8 +204,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   if (threadIdx.x == 0) {
     for (int i = 0; i < G; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
     for (int i = 0; i < PAIRS; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 4 * C::kColSplit); }
-    for (int i = 0; i < 3; ++i) mbar_init(&sfull[i], 1);
+    for (int i = 0; i < 3; ++i) { mbar_init(&sfull[i], 1); mbar_init(&sempty[i], 4 * C::kColSplit); }
     *s_abort = 0;
+    *s_done = 0;
     fence_barrier_init();
     if (p.w_packed == nullptr) tma_prefetch_desc(&tm_w);
     tma_prefetch_desc(&tm_b0);
@@ -215,9 +219,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     tmem_alloc(s_tmem, kTmemCols);
     tmem_relinquish();
   }
-  // everything above touched only this CTA's own resources; from here on the kernel reads what the
-  // kernels before it in the stream produced
-  pdl_wait();
+  // Everything above touched only this CTA's own resources; from here on the kernel reads what the
+  // kernels before it in the stream produced.  Mode 1 waits for them as a whole.  Mode 2 does not wait
+  // for GEMM1 as a whole: its CTAs start on the SMs GEMM1 has already left and its producer waits, per
+  // work item, until GEMM1 has finished that item's expert (p.ready), so the tail of GEMM1 and the head
+  // of GEMM2 overlap.  This cannot deadlock: a GEMM2 CTA only exists once every GEMM1 CTA has started
+  // (that is when GEMM1 triggers its dependents), and GEMM1 CTAs wait for nothing.  The row tables and
+  // counters GEMM2 reads here were complete before GEMM1 passed its own wait.
+  if (MODE == 1) pdl_wait();
   pdl_trigger();
   if (threadIdx.x >= 64 && threadIdx.x < 64 + kMaxLocalExperts) {
     const int e = threadIdx.x - 64;
@@ -251,6 +260,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       const uint64_t pol_w = p.meta[0] > p.meta[3] ? l2_policy_evict_last() : l2_policy_evict_first();
       const uint64_t pol_b = l2_policy_evict_last();
       uint32_t it = 0, g = 0, ph = 0;      // step counter, ring entry, its phase
+      uint32_t n_items = 0;                // items started (mode 2: selects the scale buffer)
       bool alive = true;
       for (int u = u_begin; u < u_end && alive;) {
         const int w = item_at(u), s_first = u % STEPS, s_last = min(STEPS, s_first + (u_end - u));
@@ -264,6 +274,30 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         const CUtensorMap* mb1 = small ? &tm_b1s : &tm_b1;
         const uint32_t b_bytes = small ? 16 * 128 : kBTile;
         const uint32_t group_tx = KPS * (MODE == 1 ? 2 * kATile + b_bytes : kATile + 2 * b_bytes);
+        if (MODE == 2) {
+          // This item's expert must have left GEMM1 before its rows and scales are read; the helper
+          // warp checks that (see there) and counts cleared items in shared memory, so the producer
+          // itself never waits for a round trip to L2 nor executes a proxy fence with its ring in flight.
+          if (*reinterpret_cast<volatile int*>(s_done) <= static_cast<int>(n_items)) {
+            const long long t0 = clock64();
+            while (*reinterpret_cast<volatile int*>(s_done) <= static_cast<int>(n_items)) {
+              if (*s_abort != 0) { alive = false; break; }
+              if (clock64() - t0 > (1ll << 32)) { *s_abort = kStatusDependencyTimeout; alive = false; break; }
+            }
+            if (!alive) break;
+          }
+          __threadfence_block();
+          // scales of the item: [16 K blocks x NT rows] activation scales through a tensor map and the
+          // 16 weight scales as a 64-byte bulk copy, into the buffer the epilogue released three items ago
+          const uint32_t sb = n_items % 3u, sp = (n_items / 3u) & 1u;
+          if (!mbar_wait_bounded(&sempty[sb], sp ^ 1u, s_abort, kStatusWaitTimeoutProducer)) { alive = false; break; }
+          float* d_act = s_scales + sb * kScaleStride;
+          mbar_arrive_expect_tx(&sfull[sb], (KB * NT + KB) * 4);
+          tma_load_2d(d_act, &tm_sc, &sfull[sb], im.row_start, 0, pol_b);
+          bulk_load(d_act + KB * NT, p.w_scale + (static_cast<size_t>(im.expert) * kHBlocks + im.ft) * kIBlocks,
+                    KB * 4, &sfull[sb], pol_b);
+          ++n_items;
+        }
         for (int step = s_first; step < s_last; ++step) {
           if (!mbar_wait_bounded(&empty[g], ph ^ 1u, s_abort, kStatusWaitTimeoutProducer)) { alive = false; break; }
           TRACE(0, step);
@@ -360,6 +394,56 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       }
     }
     __syncwarp();
+  } else if (warp == 2 + 4 * C::kColSplit) {
+    // ------------------------------------------------ publisher (mode 1, one thread)
+    // GEMM2 reads an expert's rows once p.ready[expert] has counted all of the expert's GEMM1 items.
+    // An item counts when every epilogue warp has issued its stores (s_done) and a gpu-scope fence has
+    // made them visible; that fence waits for the stores to be acknowledged (microseconds while HBM is
+    // saturated), which is why it runs here and not in an epilogue warp.
+    if (MODE == 1 && lane == 0) {
+      int done_target = 0;
+      for (int u = u_begin; u < u_end; u += STEPS) {
+        const Item im = decode_item<FT, NT>(s_work, p.e_local, item_at(u));
+        done_target += 4 * C::kColSplit;
+        const long long t0 = clock64();
+        bool seen = true;
+        while (*reinterpret_cast<volatile int*>(s_done) < done_target) {
+          if (*s_abort != 0 || clock64() - t0 > (1ll << 33)) { seen = false; break; }
+          __nanosleep(200);
+        }
+        if (!seen || *s_abort != 0) break;          // a failed item is never published
+        __threadfence();
+        fence_proxy_async_all();
+        red_release_gpu_add(p.ready + im.expert, 1);
+      }
+    }
+    // ------------------------------------------------ dependency helper (mode 2, one thread)
+    // Clears this CTA's items one by one: item i may be loaded once GEMM1 has counted all items of its
+    // expert.  The acquire load and the proxy fence (generic-proxy stores of GEMM1 before async-proxy
+    // loads of this kernel) run here; the producer only reads the count of cleared items (s_done).
+    if (MODE == 2 && lane == 0) {
+      int cleared = 0, ready_expert = -1;
+      for (int u = u_begin; u < u_end; u += STEPS) {
+        const Item im = decode_item<FT, NT>(s_work, p.e_local, item_at(u));
+        if (im.expert != ready_expert) {
+          const int need = (kInter / 128) * s_work[im.expert].tiles;
+          const long long t0 = clock64();
+          bool seen = true;
+          while (ld_acquire_gpu(p.ready + im.expert) < need) {
+            if (*s_abort != 0) { seen = false; break; }
+            if (clock64() - t0 > (1ll << 31)) { *s_abort = kStatusDependencyTimeout; seen = false; break; }
+            __nanosleep(100);
+          }
+          if (!seen) break;
+          fence_proxy_async_all();
+          ready_expert = im.expert;
+        }
+        ++cleared;
+        __threadfence_block();
+        *reinterpret_cast<volatile int*>(s_done) = cleared;
+      }
+    }
+    __syncwarp();
   } else {
     // ------------------------------------------------ promotion + epilogue warps
     // CS warps share each TMEM lane quarter and split the tile's columns between them, so a thread
@@ -376,26 +460,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     bool ok = true;
     int sbuf = 0;
     int cached_row_start = -1;              // token tile whose activation scales sit in shared memory (mode 1)
-    // Mode 2 fetches an item's scales two items ahead of their use, with two loads issued by one thread:
-    // the [16 K blocks x NT rows] activation scales through a tensor map and the 16 weight scales as a
-    // 64-byte bulk copy, both counted on sfull[buf].  (While the weight stream saturates HBM a small read
-    // waits several microseconds behind everything the TMA rings have in flight, and per-thread cp.async
-    // requests stalled their issuing warps for 1000-3000 cycles per item.)
-    auto prefetch_scales = [&](int uu, int buf) {
-      if (MODE == 2 && et == 0 && uu < u_end) {
-        const Item nx = decode_item<FT, NT>(s_work, p.e_local, item_at(uu));
-        float* d_act = s_scales + buf * kScaleStride;
-        mbar_arrive_expect_tx(&sfull[buf], (KB * NT + KB) * 4);
-        tma_load_2d(d_act, &tm_sc, &sfull[buf], nx.row_start, 0, l2_policy_evict_last());
-        bulk_load(d_act + KB * NT, p.w_scale + (static_cast<size_t>(nx.expert) * kHBlocks + nx.ft) * kIBlocks,
-                  KB * 4, &sfull[buf], l2_policy_evict_last());
-      }
-    };
-    uint32_t sph = 0;                       // phase bits of sfull[0..2]
-    if (MODE == 2) {
-      prefetch_scales(u_begin, 0);
-      prefetch_scales(u_begin + STEPS, 1);
-    }
+    uint32_t sph = 0;                       // phase bits of sfull[0..2] (mode 2)
     // After a failed wait a warp keeps walking the work list and still joins every named
     // barrier below (doing no other work), so the epilogue warps can never strand each other.
     for (int u = u_begin; u < u_end;) {
@@ -433,18 +498,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         }
         named_bar_sync(1, kEpi);
       } else {
-        // Scales of this item were requested two items ago (the first two before the loop); the
-        // barrier retires the buffer the previous item used, which then receives the scales of the
-        // item after next.  Columns >= n hold other rows' scales and are never read.
+        // The producer requested this item's scales when it started the item (it runs about one item
+        // ahead of the epilogue); the buffer goes back to it after the K loop.  Columns >= n hold other
+        // rows' scales and are never read.
         s_act = s_scales + sbuf * kScaleStride;
         s_ws = s_act + KB * NT;
         if (ok && !mbar_wait_bounded(&sfull[sbuf], (sph >> sbuf) & 1u, s_abort, kStatusWaitTimeoutEpilogue)) ok = false;
         sph ^= 1u << sbuf;
-        if (et == 0) TRACE(2, 1003);
-        named_bar_sync(1, kEpi);
-        if (et == 0) TRACE(2, 1004);
-        prefetch_scales(u + STEPS, sbuf == 0 ? 2 : sbuf - 1);   // u already points at the next item
-        sbuf = sbuf == 2 ? 0 : sbuf + 1;
       }
       if (et == 0) TRACE(2, 1001);
 
@@ -554,6 +614,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         if (++pr == PAIRS) { pr = 0; pph ^= 1u; }
       }
       if (et == 0) TRACE(2, 1002);
+      if (MODE == 2) {                        // the scale buffer goes back to the producer
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sempty[sbuf]);
+        sbuf = sbuf == 2 ? 0 : sbuf + 1;
+      }
       const int n_out = ok ? n : 0;           // a failed item stores nothing
       float acc0[CN];
       float acc1[MODE == 1 ? CN : 1];
@@ -615,6 +680,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             *reinterpret_cast<uint32_t*>(p.c_lo + off) = lp;
           }
         }
+        // Hand the item to the publisher warp, which makes it visible to GEMM2 (see there): waiting
+        // here for the stores to be acknowledged would stall the promotion of the next item.
+        __threadfence_block();
+        __syncwarp();
+        if (lane == 0) atomicAdd(s_done, 1);
       } else {
         const int qrow = lane & 3;
         float* o = p.o_rows + static_cast<size_t>(im.row_start + c0 + qrow) * kHidden + ft * 128 + q * 32 + (lane >> 2) * 4;
@@ -675,7 +745,7 @@ cudaError_t gemm_set_attributes() {
 cudaError_t launch_gemm1(const GemmLaunch& g, const float* w13_scale, int e_local, const Workspace& ws, int num_sms,
                          cudaStream_t st) {
   GemmArgs a{g.w_packed, ws.work, ws.meta, ws.a_scale, w13_scale, ws.c_hi, ws.c_lo, ws.c_scale, nullptr, ws.row_cap, e_local,
-             ws.status, ws.trace, ws.trace + 6 * 4096};
+             ws.ready, ws.status, ws.trace, ws.trace + 6 * 4096};
   if (g.token_tile == 128) return launch_gemm<1, 128>(g, a, num_sms, st);
   return g.token_tile == 32 ? launch_gemm<1, 32>(g, a, num_sms, st) : launch_gemm<1, 64>(g, a, num_sms, st);
 }
@@ -683,7 +753,7 @@ cudaError_t launch_gemm1(const GemmLaunch& g, const float* w13_scale, int e_loca
 cudaError_t launch_gemm2(const GemmLaunch& g, const float* w2_scale, int e_local, const Workspace& ws, int num_sms,
                          cudaStream_t st) {
   GemmArgs a{g.w_packed, ws.work, ws.meta, ws.c_scale, w2_scale, nullptr, nullptr, nullptr, ws.o_rows, ws.row_cap, e_local,
-             ws.status, ws.trace + 3 * 4096, ws.trace + 7 * 4096};
+             ws.ready, ws.status, ws.trace + 3 * 4096, ws.trace + 7 * 4096};
   if (g.token_tile == 128) return launch_gemm<2, 128>(g, a, num_sms, st);
   return g.token_tile == 32 ? launch_gemm<2, 32>(g, a, num_sms, st) : launch_gemm<2, 64>(g, a, num_sms, st);
 }

@@ -31,6 +31,7 @@ enum : int {
   kStatusWaitTimeoutEpilogue = 103,
   kStatusBadIndex = 104,
   kStatusPeerTimeout = 105,   // a flag another rank should have raised did not arrive in time
+  kStatusDependencyTimeout = 106,   // GEMM2 waited in vain for GEMM1 to finish an expert
 };
 
 // Device-side control block (one int array); the GEMM kernels read the tile count from it.
@@ -59,6 +60,7 @@ struct Workspace {
   float* topk_w = nullptr;        // [T, 8]
   uint32_t* local_mask = nullptr; // [T] bit e set when local expert e was selected
   int* counts = nullptr;          // [32] rows per local expert
+  int* ready = nullptr;           // [32] GEMM1 work items finished per local expert (counts + 32: zeroed together)
   int* meta = nullptr;            // [kMetaInts]
   int* status = nullptr;          // [4]
   long long* trace = nullptr;     // [2][3][4096] GEMM1 / GEMM2 timeline of CTA 0 (only written by SYFI_TRACE builds)

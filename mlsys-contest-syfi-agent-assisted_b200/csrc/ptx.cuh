@@ -67,6 +67,21 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
   }
 }
 
+// Cross-CTA hand-off through a counter in global memory: the writers' data stores happen before the
+// release increment, the reader's acquire load happens before its dependent loads.  The proxy fence
+// orders generic-proxy accesses against async-proxy ones (TMA), which otherwise have no mutual order.
+__device__ __forceinline__ void fence_proxy_async_all() {
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
+__device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
 // ----------------------------------------------------------------------- TMA
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
   uint64_t p;

@@ -139,7 +139,8 @@ route_kernel(const float* __restrict__ logits, const __nv_bfloat16* __restrict__
 
 cudaError_t launch_router(const float* logits, const void* bias_bf16, int T, int e_local, int expert_offset,
                           float scaling, const Workspace& ws, cudaStream_t st) {
-  cudaError_t e = cudaMemsetAsync(ws.counts, 0, sizeof(int) * kMaxLocalExperts, st);
+  // rows per expert and, behind them, the GEMM1 -> GEMM2 readiness counters
+  cudaError_t e = cudaMemsetAsync(ws.counts, 0, sizeof(int) * 2 * kMaxLocalExperts, st);
   if (e != cudaSuccess) return e;
   const int blocks = (T + kWarpsPerBlock - 1) / kWarpsPerBlock;
   route_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>(logits, static_cast<const __nv_bfloat16*>(bias_bf16), T,
