@@ -33,6 +33,8 @@ struct syfi_moe_ctx {
   const void* map_ws = nullptr;      // workspace generation the maps were built for (a_perm pointer)
   int map_e_local = 0, map_token_tile = 0;
   bool map_packed = false;
+  // true while the row counters of the workspace are known to be zero at the point of the next launch
+  bool counters_clean = false;
   // second stream of syfi_moe_forward_host: the hidden states travel while the router runs
   cudaStream_t copy_stream = nullptr;
   cudaEvent_t ev_copy_begin = nullptr, ev_copy_done = nullptr;
@@ -139,8 +141,10 @@ int alloc_workspace(Workspace& ws, int64_t max_tokens) {
   CU_TRY(dev_alloc(&ws.topk_idx, T * kTopK, &total));
   CU_TRY(dev_alloc(&ws.topk_w, T * kTopK, &total));
   CU_TRY(dev_alloc(&ws.local_mask, T, &total));
-  CU_TRY(dev_alloc(&ws.counts, 2 * kMaxLocalExperts, &total));
+  CU_TRY(dev_alloc(&ws.counts, 3 * kMaxLocalExperts, &total));
   ws.ready = ws.counts + kMaxLocalExperts;
+  ws.counts_last = ws.counts + 2 * kMaxLocalExperts;
+  CU_TRY(cudaMemset(ws.counts, 0, 3 * kMaxLocalExperts * sizeof(int)));
   CU_TRY(dev_alloc(&ws.meta, kMetaInts, &total));
   CU_TRY(dev_alloc(&ws.status, 4, &total));
   CU_TRY(dev_alloc(&ws.trace, 8 * 4096, &total));
@@ -208,6 +212,7 @@ int ensure_capacity(syfi_moe_ctx* ctx, int64_t T) {
   // growing frees buffers that earlier calls may still be using
   CU_TRY(cudaDeviceSynchronize());
   ctx->map_w13 = nullptr;   // cached tensor maps point into the old workspace
+  ctx->counters_clean = false;
   return alloc_workspace(ctx->ws, T);
 }
 
@@ -268,7 +273,11 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
   ctx->timing_valid = false;
 #define STAGE_MARK(i) do { if (timed) CU_TRY(cudaEventRecord(ctx->ev[i], st)); } while (0)
   STAGE_MARK(0);
-  CU_TRY(launch_router(static_cast<const float*>(logits), bias, T, e_local, (int)offset, (float)scaling, ws, st));
+  // counters_clean: the previous chain on this workspace was enqueued completely, so its gather kernel
+  // has left (or will have left, in stream order) the row counters at zero
+  const bool clean = ctx->counters_clean;
+  ctx->counters_clean = false;
+  CU_TRY(launch_router(static_cast<const float*>(logits), bias, T, e_local, (int)offset, (float)scaling, ws, clean, st));
   ctx->launches += 1;
   STAGE_MARK(1);
   CU_TRY(launch_build_rows(T, e_local, (int)offset, token_tile, ws, st));
@@ -294,6 +303,7 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
   STAGE_MARK(6);
 #undef STAGE_MARK
   ctx->timing_valid = timed;
+  ctx->counters_clean = true;
   return SYFI_MOE_OK;
 }
 
@@ -556,8 +566,13 @@ int syfi_moe_route(syfi_moe_ctx* ctx, const void* routing_logits, const void* ro
   if ((rc = ensure_capacity(ctx, num_tokens))) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int T = (int)num_tokens;
+  // the router alone leaves its histogram behind: zero it before and after, so that a captured graph
+  // of the whole layer (which relies on finding zeros) stays valid
+  ctx->counters_clean = false;
   CU_TRY(launch_router(static_cast<const float*>(routing_logits), routing_bias, T, num_local_experts,
-                       (int)local_expert_offset, (float)routed_scaling_factor, ctx->ws, st));
+                       (int)local_expert_offset, (float)routed_scaling_factor, ctx->ws, false, st));
+  CU_TRY(cudaMemsetAsync(ctx->ws.counts, 0, sizeof(int) * kMaxLocalExperts, st));
+  ctx->counters_clean = true;
   CU_TRY(cudaMemcpyAsync(topk_idx, ctx->ws.topk_idx, sizeof(int) * T * kTopK, cudaMemcpyDeviceToDevice, st));
   CU_TRY(cudaMemcpyAsync(topk_weights, ctx->ws.topk_w, sizeof(float) * T * kTopK, cudaMemcpyDeviceToDevice, st));
   ctx->launches = 1;
@@ -610,7 +625,7 @@ int syfi_moe_debug_read(syfi_moe_ctx* ctx, const char* name, void* dst_host, int
   const Entry table[] = {
       {"row_token", ws.row_token, R * 4},        {"route_row", ws.route_row, T * kTopK * 4},
       {"expert_work", ws.work, (int64_t)kMaxLocalExperts * (int64_t)sizeof(ExpertWork)},
-      {"meta", ws.meta, kMetaInts * 4},          {"counts", ws.counts, kMaxLocalExperts * 4},
+      {"meta", ws.meta, kMetaInts * 4},          {"counts", ws.counts_last, kMaxLocalExperts * 4},
       {"a_perm", ws.a_perm, R * kHidden},        {"a_scale", ws.a_scale, R * kHBlocks * 4},
       {"c_hi", ws.c_hi, R * kInter},             {"c_lo", ws.c_lo, R * kInter},
       {"c_scale", ws.c_scale, R * kIBlocks * 4}, {"o_rows", ws.o_rows, R * kHidden * 4},

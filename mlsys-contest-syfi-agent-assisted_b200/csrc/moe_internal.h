@@ -61,6 +61,7 @@ struct Workspace {
   uint32_t* local_mask = nullptr; // [T] bit e set when local expert e was selected
   int* counts = nullptr;          // [32] rows per local expert
   int* ready = nullptr;           // [32] GEMM1 work items finished per local expert (counts + 32: zeroed together)
+  int* counts_last = nullptr;     // [32] copy of counts kept after the call (counts itself is re-zeroed for the next)
   int* meta = nullptr;            // [kMetaInts]
   int* status = nullptr;          // [4]
   long long* trace = nullptr;     // [2][3][4096] GEMM1 / GEMM2 timeline of CTA 0 (only written by SYFI_TRACE builds)
@@ -112,7 +113,7 @@ inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 bl
 
 // launchers (each returns the cudaGetLastError() of its launches)
 cudaError_t launch_router(const float* logits, const void* bias_bf16, int T, int e_local, int expert_offset,
-                          float scaling, const Workspace& ws, cudaStream_t st);
+                          float scaling, const Workspace& ws, bool counters_are_zero, cudaStream_t st);
 cudaError_t launch_build_rows(int T, int e_local, int expert_offset, int token_tile, const Workspace& ws,
                               cudaStream_t st);
 cudaError_t launch_gather(const uint8_t* hidden, const float* hidden_scale, int T, const Workspace& ws,

@@ -23,7 +23,7 @@ __global__ void __launch_bounds__(kBuildThreads)
 build_rows_kernel(int T, int e_local, int expert_offset, const uint32_t* __restrict__ local_mask,
                   const int* __restrict__ counts, const int* __restrict__ topk_idx, int* __restrict__ row_token,
                   int* __restrict__ route_row, ExpertWork* __restrict__ work, int* __restrict__ meta, int row_cap,
-                  int token_tile, int* __restrict__ status) {
+                  int token_tile, int* __restrict__ status, int* __restrict__ ready, int* __restrict__ counts_last) {
   __shared__ int s_warp[kBuildThreads / 32];
   const int e = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -40,6 +40,10 @@ build_rows_kernel(int T, int e_local, int expert_offset, const uint32_t* __restr
     rows_total += cp; tiles_total += nt; routed += c; active += (c > 0);
   }
   const int cnt_pad = (cnt + kRowPad - 1) / kRowPad * kRowPad;
+  // the GEMM1 -> GEMM2 readiness counters start every call at zero (nothing of the previous call is
+  // still running: the router in front of this kernel is an ordinary launch)
+  if (tid == 0) { ready[e] = 0; counts_last[e] = cnt; }
+  if (e == 0 && tid >= e_local && tid < kMaxLocalExperts) { ready[tid] = 0; counts_last[tid] = 0; }
   if (rows_total > row_cap) {  // sizing bug: refuse to write out of bounds
     if (tid == 0) { atomicExch(status, kStatusBadIndex); if (e == 0) { meta[0] = 0; meta[1] = 0; meta[2] = 0; meta[3] = 0; } }
     return;
@@ -89,9 +93,12 @@ constexpr int kGatherThreads = 224;  // 7168 B per row = 448 x 16 B = 2 per thre
 __global__ void __launch_bounds__(kGatherThreads)
 gather_rows_kernel(const uint8_t* __restrict__ hidden, const float* __restrict__ hidden_scale, int T,
                    const int* __restrict__ row_token, const int* __restrict__ meta, uint8_t* __restrict__ a_perm,
-                   float* __restrict__ a_scale, int row_cap) {
+                   float* __restrict__ a_scale, int row_cap, int* __restrict__ counts) {
   pdl_wait();
   pdl_trigger();
+  // every reader of the per-expert row counters (the row-list kernel) has finished: zero them for the
+  // router of the next call
+  if (blockIdx.x == 0 && threadIdx.x < kMaxLocalExperts) counts[threadIdx.x] = 0;
   const int rows_total = meta[1];
   const int tid = threadIdx.x;
   for (int r = blockIdx.x; r < rows_total; r += gridDim.x) {
@@ -118,7 +125,7 @@ cudaError_t launch_build_rows(int T, int e_local, int expert_offset, int token_t
                               cudaStream_t st) {
   return launch_dependent(build_rows_kernel, dim3(e_local), dim3(kBuildThreads), 0, st, T, e_local, expert_offset,
                           ws.local_mask, ws.counts, ws.topk_idx, ws.row_token, ws.route_row, ws.work, ws.meta,
-                          ws.row_cap, token_tile, ws.status);
+                          ws.row_cap, token_tile, ws.status, ws.ready, ws.counts_last);
 }
 
 cudaError_t launch_gather(const uint8_t* hidden, const float* hidden_scale, int T, const Workspace& ws,
@@ -126,7 +133,7 @@ cudaError_t launch_gather(const uint8_t* hidden, const float* hidden_scale, int 
   const int max_rows = 8 * T + kRowPad * kMaxLocalExperts;
   const int grid = max_rows < 148 * 8 ? max_rows : 148 * 8;
   return launch_dependent(gather_rows_kernel, dim3(grid), dim3(kGatherThreads), 0, st, hidden, hidden_scale, T,
-                          ws.row_token, ws.meta, ws.a_perm, ws.a_scale, ws.row_cap);
+                          ws.row_token, ws.meta, ws.a_perm, ws.a_scale, ws.row_cap, ws.counts);
 }
 
 }  // namespace syfi

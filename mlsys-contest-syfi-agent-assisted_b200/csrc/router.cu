@@ -138,10 +138,14 @@ route_kernel(const float* __restrict__ logits, const __nv_bfloat16* __restrict__
 }  // namespace
 
 cudaError_t launch_router(const float* logits, const void* bias_bf16, int T, int e_local, int expert_offset,
-                          float scaling, const Workspace& ws, cudaStream_t st) {
-  // rows per expert and, behind them, the GEMM1 -> GEMM2 readiness counters
-  cudaError_t e = cudaMemsetAsync(ws.counts, 0, sizeof(int) * 2 * kMaxLocalExperts, st);
-  if (e != cudaSuccess) return e;
+                          float scaling, const Workspace& ws, bool counters_are_zero, cudaStream_t st) {
+  // The per-expert row counters must start at zero.  Inside the layer the kernels further down the
+  // chain leave them zeroed for the next call (gather_rows_kernel, build_rows_kernel), which saves a
+  // memset node in front of every call; any other caller zeroes them here.
+  if (!counters_are_zero) {
+    cudaError_t e = cudaMemsetAsync(ws.counts, 0, sizeof(int) * 2 * kMaxLocalExperts, st);
+    if (e != cudaSuccess) return e;
+  }
   const int blocks = (T + kWarpsPerBlock - 1) / kWarpsPerBlock;
   route_kernel<<<blocks, kWarpsPerBlock * 32, 0, st>>>(logits, static_cast<const __nv_bfloat16*>(bias_bf16), T,
                                                       e_local, expert_offset, scaling, ws.topk_idx, ws.topk_w,
