@@ -39,6 +39,9 @@ struct syfi_moe_ctx {
   cudaStream_t copy_stream = nullptr;
   cudaEvent_t ev_copy_begin = nullptr, ev_copy_done = nullptr;
   cudaEvent_t wait_before_gather = nullptr;   // set by forward_host for one call
+  // host pointer -> device alias of the last call's pinned buffers (logits, bias, output)
+  const void* alias_host[3] = {nullptr, nullptr, nullptr};
+  const void* alias_dev[3] = {nullptr, nullptr, nullptr};
   // gathered token-side tensors of the peer-memory expert-parallel path
   void* ep_gather = nullptr;
   size_t ep_gather_bytes = 0;
@@ -165,6 +168,22 @@ int alloc_workspace(Workspace& ws, int64_t max_tokens) {
   ws.row_cap = (int)row_cap;
   ws.bytes = total;
   return SYFI_MOE_OK;
+}
+
+// Device-side alias of a page-locked host buffer, or nullptr for pageable memory.  The last answer per
+// slot is remembered: the query costs about a microsecond and callers reuse their buffers.
+const void* mapped_alias(syfi_moe_ctx* ctx, int slot, const void* host) {
+  if (ctx->alias_host[slot] == host) return ctx->alias_dev[slot];
+  cudaPointerAttributes attr;
+  const void* dev = nullptr;
+  if (cudaPointerGetAttributes(&attr, host) == cudaSuccess) {
+    if (attr.type == cudaMemoryTypeHost && attr.devicePointer != nullptr) dev = attr.devicePointer;
+  } else {
+    cudaGetLastError();   // unregistered memory is reported as an error by some drivers: not ours to keep
+  }
+  ctx->alias_host[slot] = host;
+  ctx->alias_dev[slot] = dev;
+  return dev;
 }
 
 constexpr int kFlagOutF32 = 1;      // run_layer flags
@@ -477,25 +496,36 @@ int syfi_moe_forward_host(syfi_moe_ctx* ctx, const void* routing_logits_host, co
     CU_TRY(cudaEventCreateWithFlags(&ctx->ev_copy_begin, cudaEventDisableTiming));
     CU_TRY(cudaEventCreateWithFlags(&ctx->ev_copy_done, cudaEventDisableTiming));
   }
+  // Pinned (page-locked) host buffers are mapped into the device's address space: the router then reads
+  // its 64 KB of logits straight from them and the combine kernel writes the output rows straight into
+  // them, which saves two copy operations (and their launch latency) on the critical stream.  Pageable
+  // buffers go through the staging area.
+  const void* logits_dev = mapped_alias(ctx, 0, routing_logits_host);
+  const void* bias_dev = mapped_alias(ctx, 1, routing_bias_host);
+  void* out_dev = const_cast<void*>(mapped_alias(ctx, 2, output_host));
+  const bool direct_in = logits_dev != nullptr && bias_dev != nullptr;
   // router inputs on the caller's stream; hidden states and their scales on a second stream, ordered
   // after whatever the caller's stream did before, and awaited just before the gather kernel
   CU_TRY(cudaEventRecord(ctx->ev_copy_begin, st));
   CU_TRY(cudaStreamWaitEvent(ctx->copy_stream, ctx->ev_copy_begin, 0));
-  CU_TRY(cudaMemcpyAsync(base + o_logits, routing_logits_host, b_logits, cudaMemcpyHostToDevice, st));
-  CU_TRY(cudaMemcpyAsync(base + o_bias, routing_bias_host, b_bias, cudaMemcpyHostToDevice, st));
+  if (!direct_in) {
+    CU_TRY(cudaMemcpyAsync(base + o_logits, routing_logits_host, b_logits, cudaMemcpyHostToDevice, st));
+    CU_TRY(cudaMemcpyAsync(base + o_bias, routing_bias_host, b_bias, cudaMemcpyHostToDevice, st));
+  }
   CU_TRY(cudaMemcpyAsync(base + o_hs, hidden_states_host, b_hs, cudaMemcpyHostToDevice, ctx->copy_stream));
   CU_TRY(cudaMemcpyAsync(base + o_hss, hidden_states_scale_host, b_hss, cudaMemcpyHostToDevice, ctx->copy_stream));
   CU_TRY(cudaEventRecord(ctx->ev_copy_done, ctx->copy_stream));
   ctx->wait_before_gather = ctx->ev_copy_done;
-  int rc = forward_common(ctx, base + o_logits, base + o_bias, base + o_hs, base + o_hss, gemm1_weights,
-                          gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, T, num_local_experts,
-                          local_expert_offset, routed_scaling_factor, base + o_out, 0, stream);
+  int rc = forward_common(ctx, direct_in ? logits_dev : base + o_logits, direct_in ? bias_dev : base + o_bias,
+                          base + o_hs, base + o_hss, gemm1_weights, gemm1_weights_scale, gemm2_weights,
+                          gemm2_weights_scale, T, num_local_experts, local_expert_offset, routed_scaling_factor,
+                          out_dev ? out_dev : base + o_out, 0, stream);
   if (rc) {
     ctx->wait_before_gather = nullptr;
     cudaStreamWaitEvent(st, ctx->ev_copy_done, 0);   // keep the second stream ordered even on failure
     return rc;
   }
-  CU_TRY(cudaMemcpyAsync(output_host, base + o_out, b_out, cudaMemcpyDeviceToHost, st));
+  if (!out_dev) CU_TRY(cudaMemcpyAsync(output_host, base + o_out, b_out, cudaMemcpyDeviceToHost, st));
   CU_TRY(cudaStreamSynchronize(st));
   return SYFI_MOE_OK;
 }

@@ -180,6 +180,13 @@ def _stream_ptr(stream, device: int) -> int:
 
 
 def _expect(t, name, dtype, shape, device=None):
+    # fast path: one expression when everything is as it should be (this runs ten times per call)
+    try:
+        if (t.dtype is dtype and t.shape == shape and t.is_contiguous()
+                and (device is None or (t.device.type == "cpu" if device == "cpu" else t.device == device))):
+            return
+    except AttributeError:
+        pass
     if not isinstance(t, torch.Tensor):
         raise ValueError(f"{name} must be a torch.Tensor")
     if t.dtype != dtype:
