@@ -39,9 +39,6 @@ struct syfi_moe_ctx {
   cudaStream_t copy_stream = nullptr;
   cudaEvent_t ev_copy_begin = nullptr, ev_copy_done = nullptr;
   cudaEvent_t wait_before_gather = nullptr;   // set by forward_host for one call
-  // host pointer -> device alias of the last call's pinned buffers (logits, bias, output)
-  const void* alias_host[3] = {nullptr, nullptr, nullptr};
-  const void* alias_dev[3] = {nullptr, nullptr, nullptr};
   // gathered token-side tensors of the peer-memory expert-parallel path
   void* ep_gather = nullptr;
   size_t ep_gather_bytes = 0;
@@ -170,20 +167,16 @@ int alloc_workspace(Workspace& ws, int64_t max_tokens) {
   return SYFI_MOE_OK;
 }
 
-// Device-side alias of a page-locked host buffer, or nullptr for pageable memory.  The last answer per
-// slot is remembered: the query costs about a microsecond and callers reuse their buffers.
-const void* mapped_alias(syfi_moe_ctx* ctx, int slot, const void* host) {
-  if (ctx->alias_host[slot] == host) return ctx->alias_dev[slot];
+// Device-side alias of a page-locked host buffer, or nullptr for pageable memory.  Asked on every call
+// (about a microsecond each): an address can change hands between a pinned and a pageable allocation.
+const void* mapped_alias(const void* host) {
   cudaPointerAttributes attr;
-  const void* dev = nullptr;
   if (cudaPointerGetAttributes(&attr, host) == cudaSuccess) {
-    if (attr.type == cudaMemoryTypeHost && attr.devicePointer != nullptr) dev = attr.devicePointer;
+    if (attr.type == cudaMemoryTypeHost && attr.devicePointer != nullptr) return attr.devicePointer;
   } else {
     cudaGetLastError();   // unregistered memory is reported as an error by some drivers: not ours to keep
   }
-  ctx->alias_host[slot] = host;
-  ctx->alias_dev[slot] = dev;
-  return dev;
+  return nullptr;
 }
 
 constexpr int kFlagOutF32 = 1;      // run_layer flags
@@ -500,9 +493,9 @@ int syfi_moe_forward_host(syfi_moe_ctx* ctx, const void* routing_logits_host, co
   // its 64 KB of logits straight from them and the combine kernel writes the output rows straight into
   // them, which saves two copy operations (and their launch latency) on the critical stream.  Pageable
   // buffers go through the staging area.
-  const void* logits_dev = mapped_alias(ctx, 0, routing_logits_host);
-  const void* bias_dev = mapped_alias(ctx, 1, routing_bias_host);
-  void* out_dev = const_cast<void*>(mapped_alias(ctx, 2, output_host));
+  const void* logits_dev = mapped_alias(routing_logits_host);
+  const void* bias_dev = mapped_alias(routing_bias_host);
+  void* out_dev = const_cast<void*>(mapped_alias(output_host));
   const bool direct_in = logits_dev != nullptr && bias_dev != nullptr;
   // router inputs on the caller's stream; hidden states and their scales on a second stream, ordered
   // after whatever the caller's stream did before, and awaited just before the gather kernel

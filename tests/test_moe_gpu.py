@@ -268,16 +268,21 @@ def test_expert_slices_sum_to_full_layer(pkg, oracle):
     assert err <= 1e-4 * float(full.abs().max()), err
 
 
-def test_host_entry_point_matches_device_entry_point(pkg):
+@pytest.mark.parametrize("pinned", [True, False])
+def test_host_entry_point_matches_device_entry_point(pinned, pkg):
+    """Pinned buffers are read and written by the kernels directly, pageable ones go through the staging
+    area; a second call with other buffers of the other kind must not reuse a remembered mapping."""
     inp = pkg.make_inputs(num_tokens=64, seed=16, e_local=8, device=DEV)
     dev_out, _ = _run(pkg, inp)
-    host = [t.cpu().pin_memory() for t in (inp.routing_logits, inp.routing_bias, inp.hidden_states,
-                                           inp.hidden_states_scale)]
-    out = torch.empty(64, 7168, dtype=torch.bfloat16).pin_memory()
-    pkg.run_moe_host(*host, inp.gemm1_weights, inp.gemm1_weights_scale, inp.gemm2_weights,
-                     inp.gemm2_weights_scale, 0, 2.5, out)
-    pkg.get_context(0).check()
-    assert torch.equal(out.view(torch.int16), dev_out.cpu().view(torch.int16))
+    place = (lambda t: t.pin_memory()) if pinned else (lambda t: t.clone())
+    host = [place(t.cpu()) for t in (inp.routing_logits, inp.routing_bias, inp.hidden_states,
+                                     inp.hidden_states_scale)]
+    for _ in range(2):
+        out = place(torch.zeros(64, 7168, dtype=torch.bfloat16))
+        pkg.run_moe_host(*host, inp.gemm1_weights, inp.gemm1_weights_scale, inp.gemm2_weights,
+                         inp.gemm2_weights_scale, 0, 2.5, out)
+        pkg.get_context(0).check()
+        assert torch.equal(out.view(torch.int16), dev_out.cpu().view(torch.int16))
 
 
 def test_zero_tokens_is_a_no_op(pkg):
