@@ -170,7 +170,10 @@ int syfi_moe_last_routing(syfi_moe_ctx* ctx, int64_t num_tokens, int32_t* topk_i
 /* Synchronises `stream`, then reads the device status word and the work counters of the most
  * recent forward: stats[0] = token tiles, [1] = padded rows, [2] = routed (token, local expert)
  * rows, [3] = active local experts (stats may be null).  Returns SYFI_MOE_ERR_DEVICE when a
- * kernel gave up on a bounded wait (the reference's mbarrier waits spin for ever, moe.cu:1298-1305). */
+ * kernel gave up on a bounded wait (the reference's mbarrier waits spin for ever, moe.cu:1298-1305);
+ * the message names the status word: 101/102/103 = a GEMM kernel's producer/MMA/epilogue wait expired,
+ * 104 = row table overflow, 105 = a peer rank's flag did not arrive, 106 = GEMM2 waited in vain for
+ * GEMM1 to finish an expert. */
 int syfi_moe_check(syfi_moe_ctx* ctx, int32_t* stats4, void* stream);
 
 /* Test hook: copies a named workspace buffer of the most recent forward into HOST memory

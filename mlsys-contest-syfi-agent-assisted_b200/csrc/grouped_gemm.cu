@@ -26,13 +26,16 @@
 //       o[h, r] = sum_k W2[e, h0 + h, k] * (hi[r, k] + lo[r, k] / 28) * s[r, kb] * w2s[e, hb, kb]
 //     two accumulators (hi and lo) share the weight tile in shared memory.
 //
-// Pipeline per CTA (persistent over work items, 6 warps): warp 0 = TMA producer (weights
-// with an evict-first L2 policy, token-side tiles evict-last), warp 1 = MMA issuer and TMEM
-// owner, warps 2-5 = promotion/epilogue (one TMEM lane quarter each).  Shared-memory stages
-// form a ring guarded by full/empty mbarriers; the 512 TMEM columns form a ring of
-// 512 / (2 NT) accumulator-pair slots (tfull/tempty), so the MMAs of several K blocks are in
-// flight while earlier blocks are promoted: the issue -> commit -> tcgen05.ld -> release round
-// trip costs about 1.5 us and has to be hidden behind 4 to 8 K blocks to keep up with HBM.
+// Pipeline per CTA (persistent over work items): warp 0 = TMA producer (weights with an
+// evict-first L2 policy when streamed once, token-side tiles evict-last), warp 1 = MMA issuer
+// and TMEM owner, then the promotion/epilogue warps (a warp reads one TMEM lane quarter; the
+// tile's columns are split between two or four warps per quarter), and a last warp that keeps
+// the cross-kernel bookkeeping off everybody else's path (mode 1: publishes finished items to
+// GEMM2; mode 2: waits for GEMM1 to finish an item's expert).  Shared-memory stages form a
+// ring guarded by full/empty mbarriers; the 512 TMEM columns form a ring of 512 / (2 NT)
+// accumulator-pair slots (tfull/tempty), so the MMAs of several K blocks are in flight while
+// earlier blocks are promoted: the issue -> commit -> tcgen05.ld -> release round trip costs
+// about 1.5 us and has to be hidden behind 4 to 8 K blocks to keep up with HBM.
 // Every wait is bounded: on expiry the CTA raises an abort flag, all roles leave their
 // loops, TMEM is released and the status word reports the failure to the host.
 #include <cuda_fp16.h>
