@@ -252,8 +252,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   }
   const int my_items = (static_cast<int>(blockIdx.x) < eff_grid && static_cast<int>(blockIdx.x) < total)
                            ? (total - blockIdx.x + eff_grid - 1) / eff_grid : 0;
-  const int u_begin = 0, u_end = my_items * STEPS;    // this CTA's steps, item after item
-  auto item_at = [&](int u) { return static_cast<int>(blockIdx.x + (u / STEPS) * eff_grid); };
+  auto item_of = [&](int i) { return static_cast<int>(blockIdx.x) + i * eff_grid; };   // this CTA's i-th item
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (one thread)
@@ -265,10 +264,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       uint32_t it = 0, g = 0, ph = 0;      // step counter, ring entry, its phase
       uint32_t n_items = 0;                // items started (mode 2: selects the scale buffer)
       bool alive = true;
-      for (int u = u_begin; u < u_end && alive;) {
-        const int w = item_at(u), s_first = u % STEPS, s_last = min(STEPS, s_first + (u_end - u));
-        u += s_last - s_first;
-        const Item im = decode_item<FT, NT>(s_work, p.e_local, w);
+      for (int i = 0; i < my_items && alive; ++i) {
+        const Item im = decode_item<FT, NT>(s_work, p.e_local, item_of(i));
         const int wrow = im.expert * C::kRowsPerExpert + im.ft * 128;
         // Tiles of at most 16 rows use the 16-row box: the token-side tiles come from L2 through the
         // same SM port as the weights, so every byte not fetched is bandwidth for the weight stream.
@@ -301,7 +298,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
                     KB * 4, &sfull[sb], pol_b);
           ++n_items;
         }
-        for (int step = s_first; step < s_last; ++step) {
+        for (int step = 0; step < STEPS; ++step) {
           if (!mbar_wait_bounded(&empty[g], ph ^ 1u, s_abort, kStatusWaitTimeoutProducer)) { alive = false; break; }
           TRACE(0, step);
           mbar_arrive_expect_tx(&full[g], group_tx);
@@ -350,15 +347,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     if (lane == 0) {
       uint32_t g = 0, ph = 0, pr = 0, pph = 0;   // smem ring entry / phase, TMEM ring entry / phase
       bool alive = true;
-      for (int u = u_begin; u < u_end && alive;) {
-        const int w = item_at(u), s_first = u % STEPS, s_last = min(STEPS, s_first + (u_end - u));
-        u += s_last - s_first;
-        const Item im = decode_item<FT, NT>(s_work, p.e_local, w);
+      for (int i = 0; i < my_items && alive; ++i) {
+        const Item im = decode_item<FT, NT>(s_work, p.e_local, item_of(i));
         // Mode 2 issues ONE MMA of N = 2 NT per 32 bytes of K over the adjacent hi and lo tiles
         // (the columns past the tile's n rows hold other rows' data and are never read back)
         // instead of one per term; mode 1 needs two because up and gate are different A tiles.
         const uint32_t idesc = umma_idesc_e4m3_m128(MODE == 1 ? static_cast<uint32_t>(im.n) : 2u * NT);
-        for (int step = s_first; step < s_last; ++step) {
+        for (int step = 0; step < STEPS; ++step) {
           if (!mbar_wait_bounded(&full[g], ph, s_abort, kStatusWaitTimeoutMma)) { alive = false; break; }
           TRACE(1, step);
 #pragma unroll
@@ -405,8 +400,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     // saturated), which is why it runs here and not in an epilogue warp.
     if (MODE == 1 && lane == 0) {
       int done_target = 0;
-      for (int u = u_begin; u < u_end; u += STEPS) {
-        const Item im = decode_item<FT, NT>(s_work, p.e_local, item_at(u));
+      for (int i = 0; i < my_items; ++i) {
+        const Item im = decode_item<FT, NT>(s_work, p.e_local, item_of(i));
         done_target += 4 * C::kColSplit;
         const long long t0 = clock64();
         bool seen = true;
@@ -426,8 +421,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     // loads of this kernel) run here; the producer only reads the count of cleared items (s_done).
     if (MODE == 2 && lane == 0) {
       int cleared = 0, ready_expert = -1;
-      for (int u = u_begin; u < u_end; u += STEPS) {
-        const Item im = decode_item<FT, NT>(s_work, p.e_local, item_at(u));
+      for (int i = 0; i < my_items; ++i) {
+        const Item im = decode_item<FT, NT>(s_work, p.e_local, item_of(i));
         if (im.expert != ready_expert) {
           const int need = (kInter / 128) * s_work[im.expert].tiles;
           const long long t0 = clock64();
@@ -466,10 +461,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     uint32_t sph = 0;                       // phase bits of sfull[0..2] (mode 2)
     // After a failed wait a warp keeps walking the work list and still joins every named
     // barrier below (doing no other work), so the epilogue warps can never strand each other.
-    for (int u = u_begin; u < u_end;) {
-      const int w = item_at(u), s_first = u % STEPS, s_last = min(STEPS, s_first + (u_end - u));
-      u += s_last - s_first;
-      const Item im = decode_item<FT, NT>(s_work, p.e_local, w);
+    for (int i = 0; i < my_items; ++i) {
+      const Item im = decode_item<FT, NT>(s_work, p.e_local, item_of(i));
       const int ft = im.ft;
       const int n = ok ? im.n : 0;
       if (et == 0) TRACE(2, 1000);
@@ -545,7 +538,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           }
         }
       };
-      for (int ts = s_first * (KPS / TKPS); ts < s_last * (KPS / TKPS) && ok; ++ts) {
+      for (int ts = 0; ts < STEPS * (KPS / TKPS) && ok; ++ts) {
         if (!mbar_wait_bounded(&tfull[pr], pph, s_abort, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
         tc_fence_after();
         if (et == 0) TRACE(2, ts);
