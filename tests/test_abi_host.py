@@ -44,6 +44,23 @@ def test_no_cpu_fallback(pkg):
         pkg.run_moe(*inp.args(), out)
 
 
+def test_prepacking_refuses_host_tensors_and_foreign_objects(pkg):
+    """The packed-weights path has no CPU side either, and run_moe_prepacked only takes what
+    prepack_weights returned."""
+    f8 = torch.float8_e4m3fn
+    w13 = torch.zeros(1, 4096, 7168, dtype=torch.uint8).view(f8)
+    w2 = torch.zeros(1, 7168, 2048, dtype=torch.uint8).view(f8)
+    with pytest.raises(ValueError, match="CUDA tensor"):
+        pkg.prepack_weights(w13, w2)
+    with pytest.raises(ValueError, match="prepack_weights"):
+        pkg.run_moe_prepacked(None, None, None, None, (w13, w2), None, None, 0, 2.5, None)
+    lib = ctypes.CDLL(pkg.library_path())
+    lib.syfi_moe_prepack_weights.restype = ctypes.c_int
+    assert lib.syfi_moe_prepack_weights(None, None, None, 1, None, None, None) == 1   # SYFI_MOE_ERR_INVALID
+    lib.syfi_moe_last_error.restype = ctypes.c_char_p
+    assert b"context is null" in lib.syfi_moe_last_error()
+
+
 def test_last_error_is_empty_string_initially(pkg):
     lib = pkg.load_library()
     assert isinstance(lib.syfi_moe_last_error(), bytes)
