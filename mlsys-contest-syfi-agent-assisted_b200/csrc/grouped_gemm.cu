@@ -124,11 +124,14 @@ struct Item {
   int expert, ft, row_start, n;
 };
 
-// Work item w -> (expert, feature tile, token tile); see ExpertWork for the numbering.
+// Work item w -> (expert, feature tile, token tile); see ExpertWork for the numbering.  A CTA's items
+// come in increasing order, so each role resumes the search at the expert of its previous item
+// (`e_hint`, start at 0): scanning the table from the front costs over a thousand cycles per item and
+// role once the later experts are reached, which the short GEMM2 items do not hide.
 template <int FT, int NT>
-__device__ __forceinline__ Item decode_item(const ExpertWork* s_work, int e_local, int w) {
+__device__ __forceinline__ Item decode_item(const ExpertWork* s_work, int e_local, int w, int& e_hint) {
   Item it{0, 0, 0, 0};
-  for (int e = 0; e < e_local; ++e) {
+  for (int e = e_hint; e < e_local; ++e) {
     const ExpertWork ew = s_work[e];
     const int base = ew.tile_off * FT;
     if (w < base + ew.tiles * FT) {
@@ -138,6 +141,7 @@ __device__ __forceinline__ Item decode_item(const ExpertWork* s_work, int e_loca
       it.ft = local / ew.tiles;
       it.row_start = ew.row_off + ti * NT;
       it.n = min(NT, ew.rows_pad - ti * NT);
+      e_hint = e;
       return it;
     }
   }
@@ -263,9 +267,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       const uint64_t pol_b = l2_policy_evict_last();
       uint32_t it = 0, g = 0, ph = 0;      // step counter, ring entry, its phase
       uint32_t n_items = 0;                // items started (mode 2: selects the scale buffer)
+      int e_hint = 0;
       bool alive = true;
       for (int i = 0; i < my_items && alive; ++i) {
-        const Item im = decode_item<FT, NT>(s_work, p.e_local, item_of(i));
+        const Item im = decode_item<FT, NT>(s_work, p.e_local, item_of(i), e_hint);
         const int wrow = im.expert * C::kRowsPerExpert + im.ft * 128;
         // Tiles of at most 16 rows use the 16-row box: the token-side tiles come from L2 through the
         // same SM port as the weights, so every byte not fetched is bandwidth for the weight stream.
@@ -346,9 +351,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     // --------------------------------------------------------------- MMA issuer (one thread)
     if (lane == 0) {
       uint32_t g = 0, ph = 0, pr = 0, pph = 0;   // smem ring entry / phase, TMEM ring entry / phase
+      int e_hint = 0;
       bool alive = true;
       for (int i = 0; i < my_items && alive; ++i) {
-        const Item im = decode_item<FT, NT>(s_work, p.e_local, item_of(i));
+        const Item im = decode_item<FT, NT>(s_work, p.e_local, item_of(i), e_hint);
         // Mode 2 issues ONE MMA of N = 2 NT per 32 bytes of K over the adjacent hi and lo tiles
         // (the columns past the tile's n rows hold other rows' data and are never read back)
         // instead of one per term; mode 1 needs two because up and gate are different A tiles.
@@ -399,9 +405,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     // made them visible; that fence waits for the stores to be acknowledged (microseconds while HBM is
     // saturated), which is why it runs here and not in an epilogue warp.
     if (MODE == 1 && lane == 0) {
-      int done_target = 0;
+      int done_target = 0, e_hint = 0;
       for (int i = 0; i < my_items; ++i) {
-        const Item im = decode_item<FT, NT>(s_work, p.e_local, item_of(i));
+        const Item im = decode_item<FT, NT>(s_work, p.e_local, item_of(i), e_hint);
         done_target += 4 * C::kColSplit;
         const long long t0 = clock64();
         bool seen = true;
@@ -420,9 +426,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     // expert.  The acquire load and the proxy fence (generic-proxy stores of GEMM1 before async-proxy
     // loads of this kernel) run here; the producer only reads the count of cleared items (s_done).
     if (MODE == 2 && lane == 0) {
-      int cleared = 0, ready_expert = -1;
+      int cleared = 0, ready_expert = -1, e_hint = 0;
       for (int i = 0; i < my_items; ++i) {
-        const Item im = decode_item<FT, NT>(s_work, p.e_local, item_of(i));
+        const Item im = decode_item<FT, NT>(s_work, p.e_local, item_of(i), e_hint);
         if (im.expert != ready_expert) {
           const int need = (kInter / 128) * s_work[im.expert].tiles;
           const long long t0 = clock64();
@@ -458,11 +464,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     bool ok = true;
     int sbuf = 0;
     int cached_row_start = -1;              // token tile whose activation scales sit in shared memory (mode 1)
+    int e_hint = 0;
     uint32_t sph = 0;                       // phase bits of sfull[0..2] (mode 2)
     // After a failed wait a warp keeps walking the work list and still joins every named
     // barrier below (doing no other work), so the epilogue warps can never strand each other.
     for (int i = 0; i < my_items; ++i) {
-      const Item im = decode_item<FT, NT>(s_work, p.e_local, item_of(i));
+      const Item im = decode_item<FT, NT>(s_work, p.e_local, item_of(i), e_hint);
       const int ft = im.ft;
       const int n = ok ? im.n : 0;
       if (et == 0) TRACE(2, 1000);
