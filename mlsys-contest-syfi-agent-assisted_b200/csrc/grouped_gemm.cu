@@ -635,14 +635,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       if (MODE == 1) {
         // SwiGLU, then the per-row amax over the 128 features of this tile.  The fast exp and
         // divide are a few ulp off the exact ones, far below the 8-bit requantisation that follows.
+        // (n is a multiple of 16, so validity is decided per block of sixteen columns and the
+        // sixteen columns inside a block run without branches between them)
 #pragma unroll
-        for (int j = 0; j < CN; ++j) {
-          if (c0 + j < n_out) {
-            const float gt = acc1[j];
-            const float cv = gt * __fdividef(1.0f, 1.0f + __expf(-gt)) * acc0[j];
-            acc0[j] = cv;
-            const uint32_t m = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(cv)));
-            if (lane == 0) s_red[q * NT + c0 + j] = __uint_as_float(m);
+        for (int jb = 0; jb < CN; jb += 16) {
+          if (c0 + jb < n_out) {
+            float mx[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float gt = acc1[jb + j];
+              const float cv = gt * __fdividef(1.0f, 1.0f + __expf(-gt)) * acc0[jb + j];
+              acc0[jb + j] = cv;
+              mx[j] = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(cv))));
+            }
+            if (lane == 0) {
+              float4* dst = reinterpret_cast<float4*>(s_red + q * NT + c0 + jb);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) dst[j] = make_float4(mx[4 * j], mx[4 * j + 1], mx[4 * j + 2], mx[4 * j + 3]);
+            }
           }
         }
         named_bar_sync(2, kEpi);
@@ -661,7 +671,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         const size_t qoff = static_cast<size_t>(ft) * 128 + q * 32 + (lane >> 2) * 4;
 #pragma unroll
         for (int j = 0; j < CN; j += 4) {
-          if (c0 + j < n_out) {
+          if (c0 + (j & ~15) < n_out) {
             uint32_t hp = 0, lp = 0;
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
