@@ -78,7 +78,7 @@ template <int MODE, int NT> struct Cfg {
   static constexpr int kSmemBytes = 1024 /* alignment slack */ + kGroups * kGroupBytes +
                                     4 * (kScaleBufs * (kKBlocks * NT + 128) + 4 * NT + 2 * NT) +
                                     8 * (2 * kGroups + 2 * kPairs + 6) +
-                                    kMaxLocalExperts * static_cast<int>(sizeof(ExpertWork)) + 16;
+                                    kMaxLocalExperts * static_cast<int>(sizeof(ExpertWork)) + 32;
   static_assert(kSmemBytes <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
   static_assert(kKBlocks % kKps == 0 && kSlots % kTKps == 0 && kKps % kTKps == 0,
                 "steps must tile the K blocks and the slots");
@@ -192,6 +192,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   ExpertWork* s_work = reinterpret_cast<ExpertWork*>(sempty + 3);
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_work + kMaxLocalExperts);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+  int* s_meta = reinterpret_cast<int*>(s_tmem + 3);   // [2] token tiles, active experts (copied from p.meta)
   int* s_done = reinterpret_cast<int*>(s_tmem + 2);   // mode 1: epilogue warps that finished storing an item (running total); mode 2: items cleared for loading
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -235,15 +236,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   // counters GEMM2 reads here were complete before GEMM1 passed its own wait.
   if (MODE == 1) pdl_wait();
   pdl_trigger();
+  // the work table and the two counters every role needs, fetched in one round trip
   if (threadIdx.x >= 64 && threadIdx.x < 64 + kMaxLocalExperts) {
     const int e = threadIdx.x - 64;
     s_work[e] = (e < p.e_local) ? p.work[e] : ExpertWork{0, 0, 0, 0};
+  } else if (threadIdx.x == 64 + kMaxLocalExperts) {
+    s_meta[0] = p.meta[0];                          // token tiles
+    s_meta[1] = p.meta[3];                          // active experts
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *s_tmem;
-  const int total = p.meta[0] * FT;                 // work items
+  const int total = s_meta[0] * FT;                 // work items
   // Effective grid: the launch always has one CTA per SM, but when the items do not fill the last
   // round, fewer CTAs with equally many items each finish sooner than a last round that keeps only a
   // handful of SMs busy (a single SM cannot pull more than about 1.4x its fair share of HBM).  Only
@@ -263,7 +268,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     if (lane == 0) {
       // a weight tile is re-read by the other token tiles of its expert (from L2) only when the
       // expert has several tiles; with a single tile per expert it is streamed exactly once
-      const uint64_t pol_w = p.meta[0] > p.meta[3] ? l2_policy_evict_last() : l2_policy_evict_first();
+      const uint64_t pol_w = s_meta[0] > s_meta[1] ? l2_policy_evict_last() : l2_policy_evict_first();
       const uint64_t pol_b = l2_policy_evict_last();
       uint32_t it = 0, g = 0, ph = 0;      // step counter, ring entry, its phase
       uint32_t n_items = 0;                // items started (mode 2: selects the scale buffer)
