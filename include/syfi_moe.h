@@ -100,8 +100,10 @@ int syfi_moe_forward_partial_f32(syfi_moe_ctx* ctx, const void* routing_logits, 
                                  double routed_scaling_factor, void* output_f32, void* stream);
 
 /* Same as syfi_moe_forward but every tensor argument except the four weight tensors is a HOST
- * pointer (pinned memory makes the copies asynchronous): inputs are copied to the device, the
- * layer runs, the bf16 output is copied back and the stream is synchronised before returning.
+ * pointer: inputs travel to the device, the layer runs, the bf16 output travels back and the stream is
+ * synchronised before returning.  Page-locked (pinned) buffers are used through their device mapping where
+ * that saves a copy (the router reads logits and bias from them, the last kernel writes the output rows
+ * into them) and make the remaining copies asynchronous; pageable buffers are staged.
  * The reference's harness does these copies outside the kernel (moe/scripts/debug_correctness.py:35-55). */
 int syfi_moe_forward_host(syfi_moe_ctx* ctx, const void* routing_logits_host, const void* routing_bias_host,
                           const void* hidden_states_host, const void* hidden_states_scale_host,
