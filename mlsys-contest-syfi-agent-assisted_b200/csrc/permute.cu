@@ -17,8 +17,9 @@ namespace syfi {
 
 namespace {
 
-constexpr int kBuildThreads = 256;
-
+// kBuildThreads tokens are ranked per pass; a pass costs two dependent round trips to memory (the
+// masks, then the routes of the tokens that hit), so large batches use the largest CTA.
+template <int kBuildThreads>
 __global__ void __launch_bounds__(kBuildThreads)
 build_rows_kernel(int T, int e_local, int expert_offset, const uint32_t* __restrict__ local_mask,
                   const int* __restrict__ counts, const int* __restrict__ topk_idx, int* __restrict__ row_token,
@@ -30,15 +31,24 @@ build_rows_kernel(int T, int e_local, int expert_offset, const uint32_t* __restr
   pdl_wait();
   pdl_trigger();
 
-  int row_off = 0, tile_off = 0, rows_total = 0, tiles_total = 0, routed = 0, active = 0, cnt = 0;
-  for (int i = 0; i < e_local; ++i) {
-    const int c = counts[i];
-    const int cp = (c + kRowPad - 1) / kRowPad * kRowPad;
-    const int nt = (cp + token_tile - 1) / token_tile;
-    if (i < e) { row_off += cp; tile_off += nt; }
-    if (i == e) cnt = c;
-    rows_total += cp; tiles_total += nt; routed += c; active += (c > 0);
+  // lane i of every warp owns expert i: padded rows, token tiles, and their prefix sums by warp scans
+  // (a serial loop over the experts with its integer divisions costs microseconds at the head of the chain)
+  const unsigned full = 0xffffffffu;
+  const int c_lane = (lane < e_local) ? counts[lane] : 0;
+  const int cp_lane = (c_lane + kRowPad - 1) / kRowPad * kRowPad;
+  const int nt_lane = (cp_lane + token_tile - 1) / token_tile;
+  int rows_incl = cp_lane, tiles_incl = nt_lane;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int r = __shfl_up_sync(full, rows_incl, d), tl = __shfl_up_sync(full, tiles_incl, d);
+    if (lane >= d) { rows_incl += r; tiles_incl += tl; }
   }
+  const int rows_total = __shfl_sync(full, rows_incl, 31), tiles_total = __shfl_sync(full, tiles_incl, 31);
+  const int routed = __reduce_add_sync(full, c_lane);
+  const int active = __popc(__ballot_sync(full, c_lane > 0));
+  const int row_off = __shfl_sync(full, rows_incl - cp_lane, e);
+  const int tile_off = __shfl_sync(full, tiles_incl - nt_lane, e);
+  const int cnt = __shfl_sync(full, c_lane, e);
   const int cnt_pad = (cnt + kRowPad - 1) / kRowPad * kRowPad;
   // the GEMM1 -> GEMM2 readiness counters start every call at zero (nothing of the previous call is
   // still running: the router in front of this kernel is an ordinary launch)
@@ -123,7 +133,11 @@ gather_rows_kernel(const uint8_t* __restrict__ hidden, const float* __restrict__
 
 cudaError_t launch_build_rows(int T, int e_local, int expert_offset, int token_tile, const Workspace& ws,
                               cudaStream_t st) {
-  return launch_dependent(build_rows_kernel, dim3(e_local), dim3(kBuildThreads), 0, st, T, e_local, expert_offset,
+  if (T <= 256)
+    return launch_dependent(build_rows_kernel<256>, dim3(e_local), dim3(256), 0, st, T, e_local, expert_offset,
+                            ws.local_mask, ws.counts, ws.topk_idx, ws.row_token, ws.route_row, ws.work, ws.meta,
+                            ws.row_cap, token_tile, ws.status, ws.ready, ws.counts_last);
+  return launch_dependent(build_rows_kernel<1024>, dim3(e_local), dim3(1024), 0, st, T, e_local, expert_offset,
                           ws.local_mask, ws.counts, ws.topk_idx, ws.row_token, ws.route_row, ws.work, ws.meta,
                           ws.row_cap, token_tile, ws.status, ws.ready, ws.counts_last);
 }
