@@ -17,11 +17,64 @@ namespace syfi {
 namespace {
 
 constexpr int kCombineThreads = 256;
+constexpr int kSegments = kHidden / (kCombineThreads * 4);  // 7 segments of 1024 features per row
+static_assert(kSegments * kCombineThreads * 4 == kHidden, "row must split evenly");
+
+// One CTA per (token, 1024-feature segment), one float4 per thread and route: the eight routes' loads are
+// all in flight at once (a loop over the routes with the whole row per thread pays eight dependent
+// round trips to memory, which is what this kernel's duration consists of at small batches).
+__global__ void __launch_bounds__(kCombineThreads)
+combine_segments_kernel(int T, const int* __restrict__ route_row, const float* __restrict__ topk_w,
+               const float* __restrict__ o_rows, void* __restrict__ out, int out_is_f32, int row_cap) {
+  const int t = blockIdx.x, seg = blockIdx.y;
+  pdl_wait();
+  pdl_trigger();
+  if (t >= T) return;
+  const int col4 = seg * kCombineThreads + threadIdx.x;        // float4 index inside the row
+  int rows[kTopK];
+  float w[kTopK];
+#pragma unroll
+  for (int k = 0; k < kTopK; ++k) {
+    rows[k] = route_row[t * kTopK + k];
+    w[k] = topk_w[t * kTopK + k];
+  }
+  float4 v[kTopK];
+#pragma unroll
+  for (int k = 0; k < kTopK; ++k) {
+    const bool valid = rows[k] >= 0 && rows[k] < row_cap;
+    v[k] = valid ? __ldg(reinterpret_cast<const float4*>(o_rows + static_cast<size_t>(rows[k]) * kHidden) + col4)
+                 : make_float4(0.f, 0.f, 0.f, 0.f);
+    if (!valid) w[k] = 0.0f;
+  }
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int k = 0; k < kTopK; ++k) {                            // fixed order: deterministic sum
+    if (rows[k] >= 0 && rows[k] < row_cap) {
+      acc.x = fmaf(w[k], v[k].x, acc.x);
+      acc.y = fmaf(w[k], v[k].y, acc.y);
+      acc.z = fmaf(w[k], v[k].z, acc.z);
+      acc.w = fmaf(w[k], v[k].w, acc.w);
+    }
+  }
+  if (out_is_f32) {
+    reinterpret_cast<float4*>(static_cast<float*>(out) + static_cast<size_t>(t) * kHidden)[col4] = acc;
+  } else {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y);
+    const __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z, acc.w);
+    uint2 pk;
+    pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+    pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+    reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(out) + static_cast<size_t>(t) * kHidden)[col4] = pk;
+  }
+}
+
 constexpr int kVecPerThread = kHidden / (kCombineThreads * 4);  // 7
 static_assert(kVecPerThread * kCombineThreads * 4 == kHidden, "row must split evenly");
 
+// One CTA per token, seven float4 per thread and route, the routes one after the other: fewer, fatter CTAs
+// for large batches, where the kernel is bound by HBM and not by its chain of dependent reads.
 __global__ void __launch_bounds__(kCombineThreads)
-combine_kernel(int T, const int* __restrict__ route_row, const float* __restrict__ topk_w,
+combine_rows_kernel(int T, const int* __restrict__ route_row, const float* __restrict__ topk_w,
                const float* __restrict__ o_rows, void* __restrict__ out, int out_is_f32, int row_cap) {
   const int t = blockIdx.x;
   pdl_wait();
@@ -67,7 +120,10 @@ combine_kernel(int T, const int* __restrict__ route_row, const float* __restrict
 }  // namespace
 
 cudaError_t launch_combine(int T, const Workspace& ws, void* out, int out_is_f32, cudaStream_t st) {
-  return launch_dependent(combine_kernel, dim3(T), dim3(kCombineThreads), 0, st, T, ws.route_row, ws.topk_w,
+  if (T <= 512)   // latency-bound sizes: 7 CTAs per token, all eight routes' loads in flight
+    return launch_dependent(combine_segments_kernel, dim3(T, kSegments), dim3(kCombineThreads), 0, st, T,
+                            ws.route_row, ws.topk_w, ws.o_rows, out, out_is_f32, ws.row_cap);
+  return launch_dependent(combine_rows_kernel, dim3(T), dim3(kCombineThreads), 0, st, T, ws.route_row, ws.topk_w,
                           ws.o_rows, out, out_is_f32, ws.row_cap);
 }
 
