@@ -62,7 +62,17 @@ build_rows_kernel(int T, int e_local, int expert_offset, const uint32_t* __restr
   int base = 0;
   for (int t0 = 0; t0 < T; t0 += kBuildThreads) {
     const int t = t0 + tid;
-    const bool has = (t < T) && ((local_mask[t] >> e) & 1u);
+    // the token's mask and its eight routes are requested together (the routes are only needed when the
+    // mask hits, but asking afterwards costs a second dependent round trip per pass)
+    uint32_t m = 0;
+    int4 r0 = make_int4(-1, -1, -1, -1), r1 = r0;
+    if (t < T) {
+      m = local_mask[t];
+      const int4* rp = reinterpret_cast<const int4*>(topk_idx + t * kTopK);
+      r0 = __ldg(rp);
+      r1 = __ldg(rp + 1);
+    }
+    const bool has = (m >> e) & 1u;
     const unsigned b = __ballot_sync(0xffffffffu, has);
     if (lane == 0) s_warp[warp] = __popc(b);
     __syncthreads();
@@ -77,9 +87,10 @@ build_rows_kernel(int T, int e_local, int expert_offset, const uint32_t* __restr
       const int row = row_off + base + before + __popc(b & ((1u << lane) - 1u));
       row_token[row] = t;
       const int ge = e + expert_offset;
+      const int routes[kTopK] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
 #pragma unroll
       for (int k = 0; k < kTopK; ++k)
-        if (topk_idx[t * kTopK + k] == ge) route_row[t * kTopK + k] = row;
+        if (routes[k] == ge) route_row[t * kTopK + k] = row;
     }
     base += block_total;
     __syncthreads();

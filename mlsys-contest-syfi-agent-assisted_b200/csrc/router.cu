@@ -98,13 +98,16 @@ route_kernel(const float* __restrict__ logits, const __nv_bfloat16* __restrict__
     for (int i = 1; i < 8; ++i)
       if (v[i] > bv) { bv = v[i]; bi = i; }
     bi += lane * 8;
-#pragma unroll
-    for (int d = 16; d >= 1; d >>= 1) {
-      const float ov = __shfl_xor_sync(full, bv, d);
-      const int oi = __shfl_xor_sync(full, bi, d);
-      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-    }
-    const int owner = bi >> 3, slot = bi & 7;
+    // Warp-wide maximum of the lanes' best values through an order-preserving integer key (one redux
+    // instead of five shuffle steps); ties go to the lowest lane, i.e. the lowest expert index, and
+    // inside a lane the strict '>' above already kept the lowest slot.  (+ 0.0f folds -0 into +0 so
+    // that equal floats have equal keys.)
+    const uint32_t fb = __float_as_uint(bv + 0.0f);
+    const uint32_t key = (fb & 0x80000000u) ? ~fb : (fb | 0x80000000u);
+    const uint32_t kmax = __reduce_max_sync(full, key);
+    const int owner = __ffs(__ballot_sync(full, key == kmax)) - 1;
+    bi = __shfl_sync(full, bi, owner);
+    const int slot = bi & 7;
     float sel = s[0];
 #pragma unroll
     for (int i = 1; i < 8; ++i) sel = (slot == i) ? s[i] : sel;
