@@ -44,7 +44,7 @@ H, I = 7168, 2048
 
 # DRAM bytes (read + write) of one GEMM1 launch at the N = 1 workload, from the ncu capture
 # summarised in profiles/gemm_decode_T64.md (dram__bytes_read.sum + dram__bytes_write.sum).
-GEMM1_NCU_TRAFFIC_BYTES = 475886848
+GEMM1_NCU_TRAFFIC_BYTES = 476318208
 
 
 def measured_peaks():
