@@ -39,6 +39,11 @@ struct syfi_moe_ctx {
   cudaStream_t copy_stream = nullptr;
   cudaEvent_t ev_copy_begin = nullptr, ev_copy_done = nullptr;
   cudaEvent_t wait_before_gather = nullptr;   // set by forward_host for one call
+  // host -> device copies forward_host wants on the second stream; run_layer issues them right after it has
+  // launched the router, so that the GPU starts on the router while the host is still queueing the copies
+  struct PendingCopy { void* dst; const void* src; size_t bytes; };
+  PendingCopy pending[2] = {};
+  int n_pending = 0;
   // gathered token-side tensors of the peer-memory expert-parallel path
   void* ep_gather = nullptr;
   size_t ep_gather_bytes = 0;
@@ -292,6 +297,14 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
   CU_TRY(launch_router(static_cast<const float*>(logits), bias, T, e_local, (int)offset, (float)scaling, ws, clean, st));
   ctx->launches += 1;
   STAGE_MARK(1);
+  if (ctx->n_pending > 0) {         // forward_host: the hidden states travel while the router runs
+    for (int i = 0; i < ctx->n_pending; ++i)
+      CU_TRY(cudaMemcpyAsync(ctx->pending[i].dst, ctx->pending[i].src, ctx->pending[i].bytes, cudaMemcpyHostToDevice,
+                             ctx->copy_stream));
+    ctx->n_pending = 0;
+    CU_TRY(cudaEventRecord(ctx->ev_copy_done, ctx->copy_stream));
+    ctx->wait_before_gather = ctx->ev_copy_done;
+  }
   CU_TRY(launch_build_rows(T, e_local, (int)offset, token_tile, ws, st));
   ctx->launches += 1;
   STAGE_MARK(2);
@@ -505,17 +518,17 @@ int syfi_moe_forward_host(syfi_moe_ctx* ctx, const void* routing_logits_host, co
     CU_TRY(cudaMemcpyAsync(base + o_logits, routing_logits_host, b_logits, cudaMemcpyHostToDevice, st));
     CU_TRY(cudaMemcpyAsync(base + o_bias, routing_bias_host, b_bias, cudaMemcpyHostToDevice, st));
   }
-  CU_TRY(cudaMemcpyAsync(base + o_hs, hidden_states_host, b_hs, cudaMemcpyHostToDevice, ctx->copy_stream));
-  CU_TRY(cudaMemcpyAsync(base + o_hss, hidden_states_scale_host, b_hss, cudaMemcpyHostToDevice, ctx->copy_stream));
-  CU_TRY(cudaEventRecord(ctx->ev_copy_done, ctx->copy_stream));
-  ctx->wait_before_gather = ctx->ev_copy_done;
+  ctx->pending[0] = {base + o_hs, hidden_states_host, b_hs};
+  ctx->pending[1] = {base + o_hss, hidden_states_scale_host, b_hss};
+  ctx->n_pending = 2;
   int rc = forward_common(ctx, direct_in ? logits_dev : base + o_logits, direct_in ? bias_dev : base + o_bias,
                           base + o_hs, base + o_hss, gemm1_weights, gemm1_weights_scale, gemm2_weights,
                           gemm2_weights_scale, T, num_local_experts, local_expert_offset, routed_scaling_factor,
                           out_dev ? out_dev : base + o_out, 0, stream);
   if (rc) {
+    if (ctx->n_pending == 0) cudaStreamWaitEvent(st, ctx->ev_copy_done, 0);   // copies were issued: keep the streams ordered
+    ctx->n_pending = 0;
     ctx->wait_before_gather = nullptr;
-    cudaStreamWaitEvent(st, ctx->ev_copy_done, 0);   // keep the second stream ordered even on failure
     return rc;
   }
   if (!out_dev) CU_TRY(cudaMemcpyAsync(output_host, base + o_out, b_out, cudaMemcpyDeviceToHost, st));
