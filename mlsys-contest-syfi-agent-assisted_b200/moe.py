@@ -173,8 +173,13 @@ def release_contexts():
     _contexts.clear()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream_ptr(stream, device: int) -> int:
     if stream is None:
+        if _raw_stream is not None:      # the handle of torch's current stream without building a Stream object
+            return int(_raw_stream(device))
         stream = torch.cuda.current_stream(device)
     return int(stream.cuda_stream)
 
