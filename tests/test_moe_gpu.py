@@ -123,6 +123,17 @@ def test_prefill_chunk_matches_oracle(pkg, oracle):
     assert ok, (ostats, stats)
 
 
+@pytest.mark.parametrize("T,E,off,seed", [(1000, 32, 224, 3), (513, 31, 1, 7), (4096, 2, 100, 2), (8192, 1, 0, 6)])
+def test_odd_shapes_match_oracle(T, E, off, seed, pkg, oracle):
+    """The last experts of the global range, an odd expert count, and very few experts with many rows each
+    (several token tiles per expert); the oracle runs with torch on the GPU."""
+    inp = pkg.make_inputs(num_tokens=T, seed=seed, e_local=E, local_expert_offset=off, device=DEV)
+    out, stats = _run(pkg, inp)
+    ref, _, _ = oracle.moe_forward(*inp.args())
+    ok, ostats = oracle.check_output(out, ref)
+    assert ok, (ostats, stats)
+
+
 def test_every_token_tile_gives_the_same_bits(pkg, oracle, monkeypatch):
     """The GEMM kernels exist for token tiles of 32, 64 and 128 rows (the library picks by batch size, the
     environment variable forces one).  The tile changes the work split, never the arithmetic of an output
