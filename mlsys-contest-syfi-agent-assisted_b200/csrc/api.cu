@@ -28,6 +28,7 @@ struct syfi_moe_ctx {
   // tensor maps of the last call: they only depend on the operand addresses, the expert count and
   // the token tile, which rarely change between calls (re-encoding costs a few microseconds of host time)
   GemmLaunch g1, g2;
+  PairGemmLaunch p1, p2;             // tensor maps of the CTA-pair kernels (large batches)
   const void* map_w13 = nullptr;
   const void* map_w2 = nullptr;
   const void* map_ws = nullptr;      // workspace generation the maps were built for (a_perm pointer)
@@ -184,6 +185,7 @@ const void* mapped_alias(const void* host) {
   return nullptr;
 }
 
+constexpr int64_t kPairMinTokens = 2048;   // batches from this size on use the CTA-pair GEMM kernels
 constexpr int kFlagOutF32 = 1;      // run_layer flags
 constexpr int kFlagPrepacked = 2;
 
@@ -246,11 +248,14 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
   // Token tile (MMA N) of this call's GEMMs, chosen from the batch size because the per-expert counts
   // only exist on the device: 32 rows while the layer is bound by streaming weights (measured faster up
   // to 1024 tokens: 8 accumulator slots in flight, two K blocks per barrier round), 64 rows beyond.
-  int token_tile = (T64 <= 1024) ? 32 : 64;
-  if (const char* ov = getenv("SYFI_MOE_TOKEN_TILE")) {   // tuning knob: force 32, 64 or 128
+  // Large batches (experts with hundreds of rows each) run the CTA-pair kernels, which cut their own
+  // token tiles (256 rows in GEMM1, 128 in GEMM2); token_tile 256 stands for that configuration here.
+  int token_tile = (T64 <= 1024) ? 32 : (T64 < kPairMinTokens || packed) ? 64 : 256;
+  if (const char* ov = getenv("SYFI_MOE_TOKEN_TILE")) {   // tuning knob: force 32, 64, 128 or (pair kernels) 256
     const int v = atoi(ov);
-    if (v == 32 || v == 64 || v == 128) token_tile = v;
+    if (v == 32 || v == 64 || v == 128 || (v == 256 && !packed)) token_tile = v;
   }
+  const bool pair = token_tile == 256;
   const bool maps_valid = ctx->map_w13 == w13 && ctx->map_w2 == w2 && ctx->map_ws == ws.a_perm &&
                           ctx->map_e_local == e_local && ctx->map_token_tile == token_tile &&
                           ctx->map_packed == packed;
@@ -266,6 +271,14 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
     if ((rc = make_map(&g1.tm_w, w13, (uint64_t)e_local * 2 * kInter, kHidden, 128))) return rc;
     if ((rc = make_map(&g2.tm_w, w2, (uint64_t)e_local * kHidden, kInter, 128))) return rc;
   }
+  if (pair) {
+    ctx->p1.tm_w = g1.tm_w;
+    ctx->p2.tm_w = g2.tm_w;
+    if ((rc = make_map(&ctx->p1.tm_b0, ws.a_perm, ws.row_cap, kHidden, 32))) return rc;
+    ctx->p1.tm_b1 = ctx->p1.tm_b0;
+    if ((rc = make_map(&ctx->p2.tm_b0, ws.c_hi, ws.row_cap, kInter, 32))) return rc;
+    if ((rc = make_map(&ctx->p2.tm_b1, ws.c_lo, ws.row_cap, kInter, 32))) return rc;
+  } else {
   if ((rc = make_map(&g1.tm_b0, ws.a_perm, ws.row_cap, kHidden, token_tile))) return rc;
   g1.tm_b1 = g1.tm_b0;
   if ((rc = make_map(&g1.tm_b0s, ws.a_perm, ws.row_cap, kHidden, 16))) return rc;
@@ -276,6 +289,7 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
   if ((rc = make_map(&g2.tm_b1s, ws.c_lo, ws.row_cap, kInter, 16))) return rc;
   if ((rc = make_scale_map(&g2.tm_sc, ws.c_scale, kIBlocks, ws.row_cap, token_tile))) return rc;
   g1.tm_sc = g2.tm_sc;
+  }
   ctx->map_w13 = w13;
   ctx->map_w2 = w2;
   ctx->map_ws = ws.a_perm;
@@ -305,7 +319,7 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
     CU_TRY(cudaEventRecord(ctx->ev_copy_done, ctx->copy_stream));
     ctx->wait_before_gather = ctx->ev_copy_done;
   }
-  CU_TRY(launch_build_rows(T, e_local, (int)offset, token_tile, ws, st));
+  CU_TRY(launch_build_rows(T, e_local, (int)offset, pair ? 128 : token_tile, ws, st));
   ctx->launches += 1;
   STAGE_MARK(2);
   if (ctx->wait_before_gather) {    // hidden states still on their way from the host (forward_host)
@@ -315,10 +329,12 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
   CU_TRY(launch_gather(static_cast<const uint8_t*>(hs), static_cast<const float*>(hs_scale), T, ws, st));
   ctx->launches += 1;
   STAGE_MARK(3);
-  CU_TRY(launch_gemm1(g1, static_cast<const float*>(w13_scale), e_local, ws, grid, st));
+  if (pair) CU_TRY(launch_pair_gemm1(ctx->p1, static_cast<const float*>(w13_scale), e_local, ws, grid, st));
+  else CU_TRY(launch_gemm1(g1, static_cast<const float*>(w13_scale), e_local, ws, grid, st));
   ctx->launches += 1;
   STAGE_MARK(4);
-  CU_TRY(launch_gemm2(g2, static_cast<const float*>(w2_scale), e_local, ws, grid, st));
+  if (pair) CU_TRY(launch_pair_gemm2(ctx->p2, static_cast<const float*>(w2_scale), e_local, ws, grid, st));
+  else CU_TRY(launch_gemm2(g2, static_cast<const float*>(w2_scale), e_local, ws, grid, st));
   ctx->launches += 1;
   STAGE_MARK(5);
   if (out != nullptr) {   // the expert-parallel path combines straight into the owners' memory instead
@@ -376,6 +392,7 @@ int syfi_moe_create(int device, int64_t max_tokens, syfi_moe_ctx** out_ctx) {
     return fail(SYFI_MOE_ERR_CUDA, "device %d is sm_%d%d; this library is built for sm_100a only", device, prop.major,
                 prop.minor);
   CU_TRY(gemm_set_attributes());
+  CU_TRY(pair_gemm_set_attributes());
   syfi_moe_ctx* ctx = new (std::nothrow) syfi_moe_ctx();
   if (!ctx) return fail(SYFI_MOE_ERR_INVALID, "out of host memory");
   ctx->ws.device = device;

@@ -91,6 +91,13 @@ struct GemmLaunch {
   int token_tile;      // 32, 64 or 128: token rows per work item, must match the row-list kernel's
 };
 
+// Tensor maps of the CTA-pair GEMM kernels (grouped_gemm_pair.cu): token-side operands use 32-row boxes.
+struct PairGemmLaunch {
+  CUtensorMap tm_w;    // weights, 2-D [E * rows_per_expert, K], box 128 x 128
+  CUtensorMap tm_b0;   // GEMM1: a_perm; GEMM2: c_hi; box 32 x 128
+  CUtensorMap tm_b1;   // GEMM2: c_lo (unused by GEMM1)
+};
+
 // Programmatic dependent launch: the kernel may be scheduled while its predecessor in the stream is
 // still running (its CTAs take whatever SM resources are free and run their prologue); it must
 // execute griddepcontrol.wait (pdl_wait() in ptx.cuh) before it touches anything the predecessor
@@ -122,6 +129,13 @@ cudaError_t launch_gemm1(const GemmLaunch& g, const float* w13_scale, int e_loca
                          cudaStream_t st);
 cudaError_t launch_gemm2(const GemmLaunch& g, const float* w2_scale, int e_local, const Workspace& ws, int num_sms,
                          cudaStream_t st);
+// CTA-pair variants for large batches (grouped_gemm_pair.cu); they recompute the token-tile table from
+// ExpertWork::rows_pad, so the row-list kernel's tile size does not matter to them.
+cudaError_t pair_gemm_set_attributes();
+cudaError_t launch_pair_gemm1(const PairGemmLaunch& g, const float* w13_scale, int e_local, const Workspace& ws,
+                              int num_sms, cudaStream_t st);
+cudaError_t launch_pair_gemm2(const PairGemmLaunch& g, const float* w2_scale, int e_local, const Workspace& ws,
+                              int num_sms, cudaStream_t st);
 // Weight pre-packing (prepack.cu): [E, rows, K] row-major e4m3 -> per (expert, 128-row feature tile, 128-byte K
 // block) one 16 KB tile holding the rows' 128 bytes with the 128-byte shared-memory swizzle already applied;
 // GEMM1's up and gate tiles of the same features interleave per K block.

@@ -212,6 +212,132 @@ __device__ __forceinline__ uint32_t umma_idesc_e4m3_m128(uint32_t n) {
   return (1u << 4) | ((n >> 3) << 17) | ((128u >> 4) << 24);
 }
 
+// ------------------------------------------------------------------ CTA pairs
+// Helpers for kernels launched as clusters of two CTAs whose tensor cores work on one tile
+// (tcgen05 cta_group::2).  Addresses named "cluster address" are 32-bit shared::cluster
+// addresses (mapa), which may point into the other CTA of the pair.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+// every thread of both CTAs; orders everything before it (barrier inits included) cluster-wide
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void fence_acq_rel_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Arrive on a barrier in (possibly) the other CTA without a cluster-scope release: for hand-offs whose
+// payload is tensor memory (ordered by tcgen05 fences), not ordinary memory.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+// Like mbar_wait_bounded, for barriers the other CTA of the pair arrives on (cluster-scope acquire);
+// on expiry the failure code is also written into the other CTA's abort flag, so that its roles
+// leave their loops at once instead of running into their own limits one after the other.
+__device__ __forceinline__ bool mbar_wait_bounded_pair(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                       uint32_t peer_abort_cluster_addr, int code,
+                                                       long long limit_cycles = (1ll << 31)) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (*abort_flag != 0) return false;
+    if (clock64() - t0 > limit_cycles) {
+      *abort_flag = code;
+      st_cluster_u32(peer_abort_cluster_addr, static_cast<uint32_t>(code));
+      return false;
+    }
+  }
+}
+// The same for barriers that only this CTA's threads, its own loads or tcgen05.commit signal (CTA-scope
+// acquire), still telling the partner when it gives up.
+__device__ __forceinline__ bool mbar_wait_bounded_tell(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                       uint32_t peer_abort_cluster_addr, int code,
+                                                       long long limit_cycles = (1ll << 31)) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag != 0) return false;
+    if (clock64() - t0 > limit_cycles) {
+      *abort_flag = code;
+      st_cluster_u32(peer_abort_cluster_addr, static_cast<uint32_t>(code));
+      return false;
+    }
+  }
+}
+// Tensor memory of both CTAs of the pair: the same warp of each CTA executes these.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_slot, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_slot)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// D (+)= A * B^T over the pair: M = 256 (each CTA's shared memory holds its 128 rows of A at the
+// descriptor's offset, and its tensor memory receives the matching 128 rows of D), N columns of which
+// each CTA's shared memory holds half the rows of B.  Issued by one thread of the pair's first CTA.
+__device__ __forceinline__ void umma_f8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the mbarrier at this shared-memory offset in every CTA of `cta_mask` once the pair's MMAs
+// issued so far have completed (a signal only: no data is copied between CTAs).
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(cta_mask)
+               : "memory");
+}
+__device__ __forceinline__ uint32_t umma_idesc_e4m3_m256(uint32_t n) {
+  return (1u << 4) | ((n >> 3) << 17) | ((256u >> 4) << 24);
+}
+// Tiled load into THIS CTA's shared memory whose completion is counted on an mbarrier that may live in
+// the other CTA of the pair (cluster address).  One CTA's data only: nothing is multicast.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster_addr,
+                                                 int x, int y, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(x), "r"(y),
+        "l"(policy)
+      : "memory");
+}
+
 // ------------------------------------------------------------- cp.async (4 B)
 // Untiled bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16 bytes),
 // completion counted in bytes on an mbarrier like the tiled loads.
@@ -224,6 +350,13 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, 
 }
 
 // ------------------------------------------------------------ small helpers
+// 16-byte load through the coherent path (not ld.global.nc): for data another kernel that may still be
+// running has written and released
+__device__ __forceinline__ float4 ld_global_f32x4(const float* p) {
+  float4 v;
+  asm volatile("ld.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
