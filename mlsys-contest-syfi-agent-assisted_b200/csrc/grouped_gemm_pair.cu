@@ -5,29 +5,33 @@
 // of the reference, moe/solution/cuda/moe.cu:2194-2350, 1461-1627, 1631-1714; GEMM2 replaces
 // gemm_fp8_fp8_fused_acc_grouped_kernel, moe.cu:1718-1887), with a work split made for experts that own
 // hundreds of rows: the kernel is launched as clusters of two CTAs and every MMA spans the pair
-// (M = 256, N up to 256), so one instruction issue feeds both tensor cores for 128 cycles and a K block
+// (M = 256, N = 256), so one instruction issue feeds both tensor cores for 128 cycles and a K block
 // costs each CTA 32 KB of operand traffic per 4.2 M MACs (the single-CTA kernel with 64-row token tiles
 // moves 40 KB per 2.1 M MACs and is bound by the L2-to-SM rate).  Each CTA loads only its own operand
 // halves; nothing is multicast.
 //
-//   mode 1, work item = (expert, 128 intermediate features, up to 256 token rows):
-//     CTA 0 holds the up rows of W13, CTA 1 the gate rows of the same features (A operand, 128 rows
-//     each); each CTA loads half of the token rows (B operand).  After the K loop CTA 0 owns
-//     up[feature, token] and CTA 1 gate[feature, token]; the CTAs swap halves through distributed shared
-//     memory so that each ends up with both values for half of the tokens, then SwiGLU, the per-row amax
-//     over the 128 features and the two-term e4m3 requantisation run exactly as in the single-CTA kernel.
-//   mode 2, work item = (expert, 256 output features, up to 128 token rows):
-//     CTA r holds the W2 rows of feature tile 2 * pair + r; CTA 0 loads the hi term of the token rows,
-//     CTA 1 the lo term, so the accumulator columns [0, n) are hi products and [n, 2n) lo products.
+//   mode 1 (GEMM1), work item = (expert, 128 intermediate features, up to 256 token rows), TOKEN-MAJOR:
+//     the token rows are the M operand (CTA r holds rows 128 r .. 128 r + 127 of the tile), the weights
+//     the N operand (CTA 0 loads the 128 up rows of W13, CTA 1 the 128 gate rows of the same features).
+//     A tensor-memory lane is a token, columns 0..127 are its up values and 128..255 its gate values:
+//     the block scale of a lane is ONE number per K block (activation scale of the token x weight scale),
+//     SwiGLU needs no exchange, and the row's amax over the 128 features is a reduction inside four
+//     threads.  (With features on the lanes, as in grouped_gemm.cu, every thread needs the scale of each
+//     of its 64 token columns per K block; filling registers with those through the shared-memory pipe,
+//     128 bytes per clock, costs ~1000 cycles per K block and SM against 512 cycles of MMA.)
+//   mode 2 (GEMM2), work item = (expert, 256 output features, up to 128 token rows), feature-major:
+//     CTA r holds the W2 rows of feature tile 2 * pair + r (M operand); CTA 0 loads the hi term of the
+//     token rows, CTA 1 the lo term (N operand), so accumulator columns [0, n) are hi products and
+//     [n, 2n) lo products.
 //
 // Per K block (128 bytes of K) the raw e4m3 products accumulate in tensor memory (4 MMAs of K = 32) and
 // are then promoted into f32 registers with activation scale x weight scale; tensor memory holds two
 // accumulator slots of 256 columns, so the MMAs of block k + 1 run while block k is promoted.
 //
 // Roles per CTA: warp 0 = TMA producer (one thread), warp 1 = tensor memory owner and, in the pair's
-// first CTA, the MMA issuer, warp 2 = scale warp (multiplies the block's activation scales with its
-// weight scale into a small shared-memory ring, which takes a multiply per element off the promotion
-// loop), warp 3 = cross-kernel bookkeeping (as in grouped_gemm.cu), warps 4..19 = promotion / epilogue
+// first CTA, the MMA issuer, warp 2 = scale warp (mode 1: fetches the weight scales of the next item;
+// mode 2: multiplies a K block's activation scales with its weight scale into a shared-memory ring),
+// warp 3 = cross-kernel bookkeeping (as in grouped_gemm.cu), warps 4..19 = promotion / epilogue
 // (a warp reads one tensor-memory lane quarter; four warps share a quarter and split the columns).
 // Barriers another CTA signals: full[] lives in the first CTA and counts the bytes of both CTAs' loads;
 // empty[] and tfull[] exist in both CTAs and are signalled by one tcgen05.commit each; tempty[] lives
@@ -42,27 +46,37 @@ namespace syfi {
 
 namespace {
 
-constexpr int kWTile = 128 * 128;            // weight tile: 128 rows x 128 bytes of K
+constexpr int kTile = 128 * 128;             // operand tile: 128 rows x 128 bytes of K
 constexpr int kBox = 32 * 128;               // token-side TMA box: 32 rows x 128 bytes
-constexpr int kStageBytes = 2 * kWTile;      // one K block: weight tile + up to 128 token-side rows
-constexpr int kScaleRing = 8;                // K blocks of scale products in flight
-constexpr int kScaleEntry = 256;             // floats per ring entry (one per accumulator token column)
+constexpr int kStageBytes = 2 * kTile;       // one K block: M-side tile, then N-side tile
+constexpr int kScaleRing = 16;               // K blocks of scales in flight
 constexpr int kEpiWarps = 16;
 constexpr int kEpiThreads = 32 * kEpiWarps;
 constexpr int kPairThreads = 128 + kEpiThreads;
-constexpr int kSlotCols = 256;               // tensor-memory columns of one accumulator slot
-constexpr int kSlots = 2;
+constexpr int kMaxSlots = 4;
 constexpr int kPairTmemCols = 512;
 constexpr long long kWaitLimit = 1ll << 31;  // cycles before a wait gives up (about a second)
 
 template <int MODE> struct PairCfg {
-  static constexpr int kKBlocks = MODE == 1 ? kHBlocks : kIBlocks;          // 56 / 16
+  static constexpr int kKBlocks = MODE == 1 ? kHBlocks : kIBlocks;              // 56 / 16
   static constexpr int kFeatItems = MODE == 1 ? kInter / 128 : kHidden / 256;   // 16 / 28 per expert and token tile
   static constexpr int kTokTile = MODE == 1 ? 256 : 128;
-  static constexpr int kStages = MODE == 1 ? 4 : 6;
-  static constexpr int kXchgBytes = MODE == 1 ? 128 * 128 * 4 : 0;          // half of a CTA's accumulators
-  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kXchgBytes + kScaleRing * kScaleEntry * 4 +
-                                    (MODE == 1 ? 4 * 128 * 4 + 2 * 128 * 4 : 0) + 8 * 48 +
+  static constexpr int kStages = 6;
+  // Accumulator slots in tensor memory.  Mode 1 issues a K block as two MMA groups of N = 128 (features
+  // 0..63 and 64..127 of the tile, up and gate each) into four slots of 128 columns: a slot is needed again
+  // three groups later, which leaves the hand-off MMA -> promotion -> MMA three quarters of the buffered
+  // MMA time instead of half (measured round trip: ~1500 cycles against ~700 cycles of MMA per K block).
+#ifndef PAIR_HALVES
+#define PAIR_HALVES 1
+#endif
+  static constexpr int kHalves = MODE == 1 ? PAIR_HALVES : 1;   // MMA groups (accumulator slots) per K block
+  static constexpr int kSlots = 2 * kHalves;
+  static constexpr int kSlotCols = kPairTmemCols / kSlots;
+  static constexpr int kScaleEntry = 128;   // floats per ring entry: one per token lane (mode 1) / token column (mode 2)
+  // mode 1: the activation scales of a whole item, [56][128]; mode 2: a ring of K blocks of scale products
+  static constexpr int kScaleFloats = MODE == 1 ? kHBlocks * 128 : kScaleRing * kScaleEntry;
+  static constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kScaleFloats * 4 +
+                                    (MODE == 1 ? 4 * 128 * 4 + 2 * 128 * 4 : 0) + 8 * 64 +
                                     kMaxLocalExperts * static_cast<int>(sizeof(ExpertWork)) + 64;
   static_assert(kSmemBytes <= 232448, "exceeds the 227 KB of shared memory a CTA may use");
   static_assert(kStages % 2 == 0 && kKBlocks % 2 == 0, "stages are filled in K-adjacent pairs");
@@ -101,9 +115,31 @@ struct PairArgs {
 #define ST_WRITE(base, cond) do { } while (0)
 #endif
 
+// Optional timeline of cluster 0's first CTA (compile with -DSYFI_PAIR_TRACE): (tag, clock) pairs per role,
+// role r at p.stats[8192 + r * 4096 ...].
+#ifdef SYFI_PAIR_TRACE
+#define TR_DECL int tr_n = 0
+#define TR(role, tag)                                                                 \
+  do {                                                                                \
+    if (blockIdx.x == 0 && p.stats != nullptr && tr_n < 2040) {                       \
+      p.stats[8192 + (role) * 4096 + 2 * tr_n] = (tag);                               \
+      p.stats[8192 + (role) * 4096 + 2 * tr_n + 1] = clock64();                       \
+      ++tr_n;                                                                         \
+    }                                                                                 \
+  } while (0)
+#else
+#define TR_DECL do { } while (0)
+#define TR(role, tag) do { } while (0)
+#endif
+
 struct PItem {
   int expert, ft, row_start, n;
 };
+
+// bytes the token-side loads of `rows` rows bring in: one 128-row box above 64 rows, else 32-row boxes
+__device__ __forceinline__ int box_bytes(int rows) {
+  return rows > 64 ? kTile : ((rows + 31) >> 5) * kBox;
+}
 
 // Work item w -> (expert, feature item, token tile): expert-major, then feature item, then token tile, so
 // the clusters running side by side share weight tiles and token tiles through L2.
@@ -130,29 +166,33 @@ __device__ __forceinline__ PItem decode_pair_item(const ExpertWork* s_work, int 
 template <int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPairThreads, 1)
 pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_b0,
-                 const __grid_constant__ CUtensorMap tm_b1, const PairArgs p) {
+                 const __grid_constant__ CUtensorMap tm_b1, const __grid_constant__ CUtensorMap tm_b0w,
+                 const __grid_constant__ CUtensorMap tm_b1w, const PairArgs p) {
   using C = PairCfg<MODE>;
   constexpr int G = C::kStages;
   constexpr int KB = C::kKBlocks;
   constexpr int FI = C::kFeatItems;
   constexpr int NT = C::kTokTile;
+  constexpr int SE = C::kScaleEntry;
+  constexpr int kSlots = C::kSlots;
+  constexpr int kSlotCols = C::kSlotCols;
+  constexpr int H = C::kHalves;
+  constexpr int kIssuers = MODE == 1 ? 2 : 1;   // MMA-issuing threads (see mma_role)
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  float* s_xchg = reinterpret_cast<float*>(smem + G * kStageBytes);            // [128 cols][128 features] (mode 1)
-  float* s_scale = reinterpret_cast<float*>(smem + G * kStageBytes + C::kXchgBytes);   // [kScaleRing][256]
-  float* s_red = s_scale + kScaleRing * kScaleEntry;                           // [4][128] (mode 1)
-  float* s_cs = s_red + (MODE == 1 ? 4 * 128 : 0);                             // [128] scale (mode 1)
-  float* s_inv = s_cs + (MODE == 1 ? 128 : 0);                                 // [128] 1 / scale (mode 1)
-  uint64_t* full = reinterpret_cast<uint64_t*>(s_inv + (MODE == 1 ? 128 : 0)); // [G]   first CTA's are used
+  float* s_scale = reinterpret_cast<float*>(smem + G * kStageBytes);           // mode 1: [56][128]; mode 2: [kScaleRing][SE]
+  float* s_red = s_scale + C::kScaleFloats;                                    // [4][128] partial amax (mode 1)
+  float* s_ws = s_red + (MODE == 1 ? 4 * 128 : 0);                             // [2][128] weight scales of an item (mode 1)
+  uint64_t* full = reinterpret_cast<uint64_t*>(s_ws + (MODE == 1 ? 2 * 128 : 0));   // [G]   first CTA's are used
   uint64_t* empty = full + G;                                                  // [G/2] per CTA
-  uint64_t* tfull = empty + G / 2;                                             // [2]   per CTA
-  uint64_t* tempty = tfull + kSlots;                                           // [2]   first CTA's are used
-  uint64_t* sfull = tempty + kSlots;                                           // [8]   per CTA
-  uint64_t* sempty = sfull + kScaleRing;                                       // [8]   per CTA
-  uint64_t* xfull = sempty + kScaleRing;                                       // the partner's halves have arrived
-  uint64_t* xfree = xfull + 1;                                                 // the partner has read what this CTA sent
-  ExpertWork* s_work = reinterpret_cast<ExpertWork*>(xfree + 1);
+  uint64_t* tfull = empty + G / 2;                                             // [4]   per CTA
+  uint64_t* tempty = tfull + kMaxSlots;                                        // [4]   first CTA's are used
+  uint64_t* sfull = tempty + kMaxSlots;                                         // [16]  per CTA
+  uint64_t* sempty = sfull + kScaleRing;                                       // [16]  per CTA
+  uint64_t* wfull = sempty + kScaleRing;                                       // [2]   mode 1: an item's weight scales are there
+  uint64_t* wempty = wfull + 2;                                                // [2]
+  ExpertWork* s_work = reinterpret_cast<ExpertWork*>(wempty + 2);
   uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_work + kMaxLocalExperts);
   volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
   int* s_done = reinterpret_cast<int*>(s_tmem + 2);   // mode 1: epilogue warps done with an item (running total); mode 2: items cleared
@@ -165,17 +205,17 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < G; ++i) mbar_init(&full[i], 1);
-    for (int i = 0; i < G / 2; ++i) mbar_init(&empty[i], 1);
-    for (int i = 0; i < kSlots; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 2 * kEpiWarps); }
+    for (int i = 0; i < G / 2; ++i) mbar_init(&empty[i], kIssuers);   // one commit per MMA issuer
+    for (int i = 0; i < kMaxSlots; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 2 * kEpiWarps); }
     for (int i = 0; i < kScaleRing; ++i) { mbar_init(&sfull[i], 1); mbar_init(&sempty[i], kEpiWarps); }
-    mbar_init(xfull, kEpiWarps);
-    mbar_init(xfree, kEpiWarps);
+    for (int i = 0; i < 2; ++i) { mbar_init(&wfull[i], 1); mbar_init(&wempty[i], kEpiWarps); }
     *s_abort = 0;
     *s_done = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tm_w);
     tma_prefetch_desc(&tm_b0);
-    if (MODE == 2) tma_prefetch_desc(&tm_b1);
+    tma_prefetch_desc(&tm_b0w);
+    if (MODE == 2) { tma_prefetch_desc(&tm_b1); tma_prefetch_desc(&tm_b1w); }
   }
   // both CTAs' barriers exist before anyone signals across the pair
   cluster_sync_all();
@@ -215,6 +255,67 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   const int my_items = cluster_id < total ? (total - cluster_id + n_clusters - 1) / n_clusters : 0;
   auto item_of = [&](int i) { return cluster_id + i * n_clusters; };
 
+  // MMA issue, one thread of the pair's first CTA per K-block parity.  Two issuers (even K blocks -> slot 0,
+  // odd -> slot 1) because an issuer is tied up for the whole execution time of its MMAs (the queue behind
+  // tcgen05.mma is shallow) and then pays its commits and the wait for its slot: with one issuer the tensor
+  // pipe idles during those; with two, one's waits overlap the other's MMAs.  MMAs of different slots are
+  // independent, and tcgen05.commit tracks the MMAs of the committing thread only, so each issuer commits its
+  // own slot and its own half of the stage pair (empty[] counts two arrivals).
+  auto mma_role = [&](const uint32_t par) {
+    uint32_t g = par, ph = 0, sph = 0;      // this issuer's next stage and its phase, phase of its slot(s)
+    uint32_t slot = par * H;                // mode 2 (one issuer): alternates between the two slots
+    int e_hint = 0;
+    bool alive = true;
+    ST_DECL;
+    TR_DECL;
+    const long long st_start = clock64();
+    (void)st_start;
+    for (int i = 0; i < my_items && alive; ++i) {
+      const PItem im = decode_pair_item<FI, NT>(s_work, p.e_local, item_of(i), e_hint);
+      const uint32_t idesc = umma_idesc_e4m3_m256(MODE == 1 ? 256u / H : 2u * im.n);
+      for (int kb = static_cast<int>(par); kb < KB; kb += kIssuers) {
+        ST_BEGIN();
+        if (!mbar_wait_bounded_tell(&full[g], ph, s_abort, peer_abort, kStatusWaitTimeoutMma, kWaitLimit)) { alive = false; break; }
+        ST_END(0);
+        const uint32_t sb = smem_u32(smem + g * kStageBytes);
+        const uint64_t a0 = umma_smem_desc_sw128(sb);
+#pragma unroll
+        for (int h = 0; h < H; ++h) {
+          const uint32_t sl = slot + h;
+          ST_BEGIN();
+          if (!mbar_wait_bounded_tell(&tempty[sl], sph ^ 1u, s_abort, peer_abort, kStatusWaitTimeoutMma, kWaitLimit)) { alive = false; break; }
+          ST_END(1);
+          if (MODE == 1 && par == 0) TR(0, 1);       // operands and slot are there
+          tc_fence_after();
+          const uint64_t b0 = umma_smem_desc_sw128(sb + kTile + h * (kTile / H));
+          const uint32_t d0 = tmem_base + sl * kSlotCols;
+#pragma unroll
+#ifndef PAIR_NO_MMA
+          for (int k4 = 0; k4 < 4; ++k4) umma_f8_pair(d0, a0 + 2 * k4, b0 + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
+#else
+          (void)a0; (void)b0; (void)d0; (void)idesc;
+#endif
+          if (h == H - 1 && (kIssuers == 2 || (g & 1u))) umma_commit_pair(&empty[g >> 1], 3);
+          umma_commit_pair(&tfull[sl], 3);
+          if (MODE == 1 && par == 0) TR(0, 2);       // issued and committed
+        }
+        if (!alive) break;
+        if (kIssuers == 2) {
+          sph ^= 1u;
+        } else {
+          slot ^= static_cast<uint32_t>(H);
+          if (slot == 0) sph ^= 1u;
+        }
+        g += kIssuers;
+        if (g >= static_cast<uint32_t>(G)) { g -= G; ph ^= 1u; }
+      }
+    }
+#ifdef SYFI_PAIR_STATS
+    st_acc[2] = clock64() - st_start;
+#endif
+    ST_WRITE(4, par == 0);
+  };
+
   if (warp < 4) {
     if (warp == 0) {
       // ------------------------------------------------------------ TMA producer (one thread per CTA)
@@ -225,29 +326,55 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
 #pragma unroll
         for (int i = 0; i < G; ++i) full0[i] = mapa_u32(smem_u32(&full[i]), 0);
         uint32_t it = 0, g = 0, ph = 0;        // stage pairs armed, next stage, phase of its empty barrier
+        uint32_t s = 0, sp = 0;                // scale ring entry and phase (mode 1)
+        uint32_t wp = 0;                       // phase bits of wempty[0..1] (mode 1)
         uint32_t n_items = 0;
         int e_hint = 0;
         bool alive = true;
         ST_DECL;
         const long long st_start = clock64();
-        (void)st_start;
+        (void)st_start; (void)s; (void)sp; (void)wp;
         for (int i = 0; i < my_items && alive; ++i) {
           const PItem im = decode_pair_item<FI, NT>(s_work, p.e_local, item_of(i), e_hint);
-          int nh, my_row, wrow;
+          int my_rows, my_row, wrow, tok_off, w_off;
+          uint32_t stage_tx;
           const CUtensorMap* mb;
           if (MODE == 1) {
-            nh = im.n >> 1;                                      // this CTA's half of the token rows
-            my_row = im.row_start + static_cast<int>(rank) * nh;
+            // token tile on the M side: this CTA's rows 128 rank .. of the tile (none when the tile is short)
+            const int cnt0 = min(im.n, 128), cnt1 = im.n - cnt0;
+            my_rows = rank == 0 ? cnt0 : cnt1;
+            my_row = im.row_start + 128 * static_cast<int>(rank);
             wrow = im.expert * 2 * kInter + static_cast<int>(rank) * kInter + im.ft * 128;
-            mb = &tm_b0;
+            mb = my_rows > 64 ? &tm_b0w : &tm_b0;
+            tok_off = 0;
+            w_off = kTile;
+            stage_tx = static_cast<uint32_t>(2 * kTile + box_bytes(cnt0) + box_bytes(cnt1));
           } else {
-            nh = im.n;                                           // all rows of one term
+            my_rows = im.n;                                      // all rows of one term
             my_row = im.row_start;
             wrow = im.expert * kHidden + (2 * im.ft + static_cast<int>(rank)) * 128;
-            mb = rank == 0 ? &tm_b0 : &tm_b1;
+            mb = my_rows > 64 ? (rank == 0 ? &tm_b0w : &tm_b1w) : (rank == 0 ? &tm_b0 : &tm_b1);
+            tok_off = kTile;
+            w_off = 0;
+            stage_tx = 2u * static_cast<uint32_t>(kTile + box_bytes(im.n));
           }
-          const int boxes = (nh + 31) >> 5;
-          const uint32_t stage_tx = 2u * static_cast<uint32_t>(kWTile + boxes * kBox);   // both CTAs' bytes
+          // more than 64 rows: one 128-row box (fewer TMA instructions); else 32-row boxes
+          if (MODE == 1) {
+            // weight scales of the item, [0..55] up block and [64..119] gate block, into the buffer the
+            // epilogue released two items ago
+            const int par = i & 1;
+            if (!mbar_wait_bounded_tell(&wempty[par], ((wp >> par) & 1u) ^ 1u, s_abort, peer_abort,
+                                        kStatusWaitTimeoutProducer, kWaitLimit)) { alive = false; break; }
+            wp ^= 1u << par;
+            mbar_arrive_expect_tx(&wfull[par], 2u * kHBlocks * 4u);
+            bulk_load(s_ws + par * 128, p.w_scale + (static_cast<size_t>(im.expert) * 32 + im.ft) * kHBlocks,
+                      kHBlocks * 4, &wfull[par], pol_b);
+            bulk_load(s_ws + par * 128 + 64, p.w_scale + (static_cast<size_t>(im.expert) * 32 + 16 + im.ft) * kHBlocks,
+                      kHBlocks * 4, &wfull[par], pol_b);
+          }
+          const int boxes = my_rows > 64 ? 1 : (my_rows + 31) >> 5;
+          const int box_pitch = my_rows > 64 ? kTile : kBox;
+          const int box_rows = my_rows > 64 ? 128 : 32;
           if (MODE == 2) {
             // the item's expert must have left GEMM1 (the helper warp checks and counts cleared items)
             if (*reinterpret_cast<volatile int*>(s_done) <= static_cast<int>(n_items)) {
@@ -271,20 +398,32 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
             if (!mbar_wait_bounded_tell(&empty[g >> 1], ph ^ 1u, s_abort, peer_abort, kStatusWaitTimeoutProducer,
                                         kWaitLimit)) { alive = false; break; }
             ST_END(0);
+#ifdef PAIR_NO_LOAD
+            if (rank == 0) { mbar_arrive(&full[g]); mbar_arrive(&full[g + 1]); }
+#else
             if (rank == 0) {
               mbar_arrive_expect_tx(&full[g], stage_tx);
               mbar_arrive_expect_tx(&full[g + 1], stage_tx);
             }
+#endif
             // boxes that continue each other along K are issued back to back (a row's 256 contiguous
             // bytes are served by L2 far faster than two separate 128-byte visits)
             uint8_t* st0 = smem + g * kStageBytes;
             uint8_t* st1 = st0 + kStageBytes;
             const int x0 = kb * 128;
-            tma_load_2d_pair(st0, &tm_w, full0[g], x0, wrow, pol_w);
-            tma_load_2d_pair(st1, &tm_w, full0[g + 1], x0 + 128, wrow, pol_w);
-            for (int b = 0; b < boxes; ++b) {
-              tma_load_2d_pair(st0 + kWTile + b * kBox, mb, full0[g], x0, my_row + 32 * b, pol_b);
-              tma_load_2d_pair(st1 + kWTile + b * kBox, mb, full0[g + 1], x0 + 128, my_row + 32 * b, pol_b);
+#ifndef PAIR_NO_LOAD
+            tma_load_2d_pair(st0 + w_off, &tm_w, full0[g], x0, wrow, pol_w);
+            tma_load_2d_pair(st1 + w_off, &tm_w, full0[g + 1], x0 + 128, wrow, pol_w);
+#endif
+            for (int b = 0; b < (
+#ifdef PAIR_NO_LOAD
+                                 0
+#else
+                                 boxes
+#endif
+                                 ); ++b) {
+              tma_load_2d_pair(st0 + tok_off + b * box_pitch, mb, full0[g], x0, my_row + box_rows * b, pol_b);
+              tma_load_2d_pair(st1 + tok_off + b * box_pitch, mb, full0[g + 1], x0 + 128, my_row + box_rows * b, pol_b);
             }
             ++it;
             g += 2;
@@ -306,55 +445,25 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       }
       __syncwarp();
     } else if (warp == 1) {
-      // --------------------------------------------------------------- MMA issuer (one thread of the pair)
-      if (lane == 0 && rank == 0) {
-        uint32_t g = 0, ph = 0, sl = 0, sph = 0;   // stage / phase, accumulator slot / phase
-        int e_hint = 0;
-        bool alive = true;
-        ST_DECL;
-        const long long st_start = clock64();
-        (void)st_start;
-        for (int i = 0; i < my_items && alive; ++i) {
-          const PItem im = decode_pair_item<FI, NT>(s_work, p.e_local, item_of(i), e_hint);
-          const uint32_t idesc = umma_idesc_e4m3_m256(MODE == 1 ? static_cast<uint32_t>(im.n) : 2u * im.n);
-          for (int kb = 0; kb < KB; ++kb) {
-            ST_BEGIN();
-            if (!mbar_wait_bounded_tell(&full[g], ph, s_abort, peer_abort, kStatusWaitTimeoutMma, kWaitLimit)) { alive = false; break; }
-            ST_END(0);
-            ST_BEGIN();
-            if (!mbar_wait_bounded_tell(&tempty[sl], sph ^ 1u, s_abort, peer_abort, kStatusWaitTimeoutMma, kWaitLimit)) { alive = false; break; }
-            ST_END(1);
-            tc_fence_after();
-            const uint32_t sb = smem_u32(smem + g * kStageBytes);
-            const uint64_t a0 = umma_smem_desc_sw128(sb);
-            const uint64_t b0 = umma_smem_desc_sw128(sb + kWTile);
-            const uint32_t d0 = tmem_base + sl * kSlotCols;
-#pragma unroll
-            for (int k4 = 0; k4 < 4; ++k4) umma_f8_pair(d0, a0 + 2 * k4, b0 + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
-            if (g & 1u) umma_commit_pair(&empty[g >> 1], 3);
-            umma_commit_pair(&tfull[sl], 3);
-            if (++g == G) { g = 0; ph ^= 1u; }
-            if (++sl == kSlots) { sl = 0; sph ^= 1u; }
-          }
-        }
-#ifdef SYFI_PAIR_STATS
-        st_acc[2] = clock64() - st_start;
-#endif
-        ST_WRITE(4, true);
-      }
+      // --------------------------------------------------------------- MMA issuer for the even K blocks
+      if (lane == 0 && rank == 0) mma_role(0);
       __syncwarp();
     } else if (warp == 2) {
       // --------------------------------------------------------------- scale warp
-      // entry s of the ring holds, for one K block, act_scale[row, kb] * w_scale[kb] of every token column
-      // of the item; lane l serves columns 4 l .. 4 l + 3 (and 128 + 4 l .. in mode 1)
-      constexpr int kBatch = 4;
-      uint32_t s = 0, sp = 0;
-      uint32_t n_items = 0;
-      int e_hint = 0;
-      bool alive = true;
-      for (int i = 0; i < my_items && alive; ++i) {
-        const PItem im = decode_pair_item<FI, NT>(s_work, p.e_local, item_of(i), e_hint);
-        if (MODE == 2) {
+      if (MODE == 1) {
+        // ------------------------------------------------------------- MMA issuer for the odd K blocks
+        if (lane == 0 && rank == 0) mma_role(1);
+        __syncwarp();
+      } else {
+        // entry s of the ring holds, for one K block, act_scale[row, kb] * w_scale[kb] of every token column
+        // of the item; lane l serves columns 4 l .. 4 l + 3
+        constexpr int kBatch = 4;
+        uint32_t s = 0, sp = 0;
+        uint32_t n_items = 0;
+        int e_hint = 0;
+        bool alive = true;
+        for (int i = 0; i < my_items && alive; ++i) {
+          const PItem im = decode_pair_item<FI, NT>(s_work, p.e_local, item_of(i), e_hint);
           if (*reinterpret_cast<volatile int*>(s_done) <= static_cast<int>(n_items)) {
             const long long t0 = clock64();
             while (*reinterpret_cast<volatile int*>(s_done) <= static_cast<int>(n_items)) {
@@ -365,38 +474,30 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
           if (!alive) break;
           __threadfence_block();
           ++n_items;
-        }
-        const float* wsp = MODE == 1
-            ? p.w_scale + (static_cast<size_t>(im.expert) * 32 + rank * 16 + im.ft) * kHBlocks
-            : p.w_scale + (static_cast<size_t>(im.expert) * kHBlocks + 2 * im.ft + rank) * kIBlocks;
-        const float ws_a = lane < KB ? __ldg(wsp + lane) : 0.0f;
-        const float ws_b = (MODE == 1 && 32 + lane < KB) ? __ldg(wsp + 32 + lane) : 0.0f;
-        const int col = 4 * lane;
-        const bool v0 = col < im.n, v1 = MODE == 1 && 128 + col < im.n;
-        const float* src = p.act_scale + im.row_start + col;
-        for (int kb0 = 0; kb0 < KB && alive; kb0 += kBatch) {
-          float4 a[kBatch], b[kBatch];
+          const float* wsp = p.w_scale + (static_cast<size_t>(im.expert) * kHBlocks + 2 * im.ft + rank) * kIBlocks;
+          const float ws_a = lane < KB ? __ldg(wsp + lane) : 0.0f;
+          const int col = 4 * lane;
+          const bool v0 = col < im.n;
+          const float* src = p.act_scale + im.row_start + col;
+          for (int kb0 = 0; kb0 < KB && alive; kb0 += kBatch) {
+            float4 a[kBatch];
 #pragma unroll
-          for (int k = 0; k < kBatch; ++k) {
-            const float* sp0 = src + static_cast<size_t>(kb0 + k) * p.row_cap;
-            // plain loads: in mode 2 these scales were written by GEMM1, which may still be running
-            a[k] = v0 ? ld_global_f32x4(sp0) : make_float4(0.f, 0.f, 0.f, 0.f);
-            if (MODE == 1) b[k] = v1 ? ld_global_f32x4(sp0 + 128) : make_float4(0.f, 0.f, 0.f, 0.f);
-          }
+            for (int k = 0; k < kBatch; ++k) {
+              // plain loads: these scales were written by GEMM1, which may still be running
+              a[k] = v0 ? ld_global_f32x4(src + static_cast<size_t>(kb0 + k) * p.row_cap) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
 #pragma unroll
-          for (int k = 0; k < kBatch; ++k) {
-            const int kb = kb0 + k;
-            const float ws = __shfl_sync(0xffffffffu, kb < 32 ? ws_a : ws_b, kb & 31);
-            bool ok = mbar_wait_bounded_tell(&sempty[s], sp ^ 1u, s_abort, peer_abort, kStatusWaitTimeoutProducer, kWaitLimit);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) { alive = false; break; }
-            float* dst = s_scale + s * kScaleEntry + col;
-            *reinterpret_cast<float4*>(dst) = make_float4(a[k].x * ws, a[k].y * ws, a[k].z * ws, a[k].w * ws);
-            if (MODE == 1)
-              *reinterpret_cast<float4*>(dst + 128) = make_float4(b[k].x * ws, b[k].y * ws, b[k].z * ws, b[k].w * ws);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sfull[s]);
-            if (++s == kScaleRing) { s = 0; sp ^= 1u; }
+            for (int k = 0; k < kBatch; ++k) {
+              const float ws = __shfl_sync(0xffffffffu, ws_a, kb0 + k);
+              bool ok = mbar_wait_bounded_tell(&sempty[s], sp ^ 1u, s_abort, peer_abort, kStatusWaitTimeoutProducer, kWaitLimit);
+              ok = __all_sync(0xffffffffu, ok);
+              if (!ok) { alive = false; break; }
+              *reinterpret_cast<float4*>(s_scale + s * SE + col) =
+                  make_float4(a[k].x * ws, a[k].y * ws, a[k].z * ws, a[k].w * ws);
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&sfull[s]);
+              if (++s == kScaleRing) { s = 0; sp ^= 1u; }
+            }
           }
         }
       }
@@ -453,75 +554,225 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     }
   } else {
     // ------------------------------------------------ promotion + epilogue warps
-    // A thread owns one feature (tensor-memory lane) and CN token columns of every accumulator slot.
-    constexpr int CN = MODE == 1 ? 64 : 32;       // token columns per thread
     const int q = warp & 3;                       // lane quarter this warp may read
     const int grp = (warp - 4) >> 2;              // which quarter of the columns
-    const int c0 = grp * CN;                      // first token column of this thread
-    const int f = q * 32 + lane;                  // feature inside the CTA's 128-row tile
+    const int tl = q * 32 + lane;                 // tensor-memory lane: mode 1 token of this CTA, mode 2 feature
     const uint32_t lane_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-    const uint32_t tempty0[kSlots] = {mapa_u32(smem_u32(&tempty[0]), 0), mapa_u32(smem_u32(&tempty[1]), 0)};
-    const uint32_t peer_xfull = mapa_u32(smem_u32(xfull), peer);
-    const uint32_t peer_xfree = mapa_u32(smem_u32(xfree), peer);
-    const uint32_t peer_xchg = mapa_u32(smem_u32(s_xchg), peer);
+    const uint32_t mapa_tempty = mapa_u32(smem_u32(&tempty[0]), 0);   // the first CTA's tempty[0]; the others follow at 8 bytes each
     uint32_t sl = 0, sph = 0;                     // accumulator slot and its phase
     uint32_t s = 0, sp = 0;                       // scale ring entry and its phase
-    uint32_t xph = 0;                             // phase of the exchange barriers (mode 1)
+    uint32_t wp = 0;                              // phase bits of wfull[0..1] (mode 1)
     bool ok = true;
     int e_hint = 0;
     const uint64_t inv_ratio = f32x2_pack(1.0f / kLoRatio, 1.0f / kLoRatio);
     ST_DECL;
+    TR_DECL;
     const long long st_start = clock64();
-    (void)st_start;
-    (void)inv_ratio; (void)xph; (void)peer_xfull; (void)peer_xfree; (void)peer_xchg; (void)f;
+    (void)st_start; (void)inv_ratio; (void)wp;
 
+    if (MODE == 1 && my_items > 0) {
+      // activation scales of the first item (later items: fetched during the previous item's epilogue)
+      int eh = 0;
+      const PItem f = decode_pair_item<FI, NT>(s_work, p.e_local, item_of(0), eh);
+      const int nrows = rank == 0 ? min(f.n, 128) : max(f.n - 128, 0);
+      const float* src = p.act_scale + static_cast<size_t>(grp) * (kHBlocks / 4) * p.row_cap + f.row_start + 128 * rank + tl;
+#pragma unroll
+      for (int k = 0; k < kHBlocks / 4; ++k)
+        s_scale[(grp * (kHBlocks / 4) + k) * 128 + tl] = tl < nrows ? __ldg(src + static_cast<size_t>(k) * p.row_cap) : 0.0f;
+      named_bar_sync(1 + q, 128);
+    }
     for (int i = 0; i < my_items; ++i) {
       const PItem im = decode_pair_item<FI, NT>(s_work, p.e_local, item_of(i), e_hint);
-      const int n = ok ? im.n : 0;
-      uint64_t acc[CN / 2];
-#pragma unroll
-      for (int j = 0; j < CN / 2; ++j) acc[j] = 0ull;
 
-      for (int kb = 0; kb < KB && ok; ++kb) {
-        ST_BEGIN();
-        if (!mbar_wait_bounded_tell(&tfull[sl], sph, s_abort, peer_abort, kStatusWaitTimeoutEpilogue, kWaitLimit)) { ok = false; break; }
-        ST_END(0);
-        tc_fence_after();
-        if (!mbar_wait_bounded_tell(&sfull[s], sp, s_abort, peer_abort, kStatusWaitTimeoutEpilogue, kWaitLimit)) { ok = false; break; }
+      if (MODE == 1) {
+        // ===== token-major: lane = token, columns [32 grp, +32) = up, [128 + 32 grp, +32) = gate
+        const int par = i & 1;
+        const float* ws = s_ws + par * 128;
+        if (ok && !mbar_wait_bounded_tell(&wfull[par], (wp >> par) & 1u, s_abort, peer_abort,
+                                          kStatusWaitTimeoutEpilogue, kWaitLimit)) ok = false;
+        wp ^= 1u << par;
+        float up[32], gt[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) { up[j] = 0.0f; gt[j] = 0.0f; }
+        for (int kb = 0; kb < KB && ok; ++kb) {
+          // block scale of this thread's token: its activation scale (staged in shared memory for the whole
+          // item, see the end of the previous item) times the weight scales of the up and the gate block
+          const float a = s_scale[kb * 128 + tl];
+          const float su = a * ws[kb], sg = a * ws[64 + kb];
 #ifdef SYFI_PAIR_STATS
-        const long long st_p0 = clock64();
+          long long st_p0 = 0;
 #endif
-        const float* sc = s_scale + s * kScaleEntry + c0;
-        const uint32_t t0 = lane_addr + sl * kSlotCols + c0;
+          // H accumulator groups per K block; group h holds features (128 / H) h .. of the tile, up at columns
+          // 0 .. 128 / H - 1 and gate behind them; this thread owns UC = 32 / H of them per group
+          constexpr int UC = 32 / H;
 #pragma unroll
-        for (int ch = 0; ch < CN / 16; ++ch) {
-          if (c0 + ch * 16 < n) {
-            const ulonglong2* sp4 = reinterpret_cast<const ulonglong2*>(sc + ch * 16);
-            if (MODE == 1) {
-              uint32_t r[16];
-              ST_BEGIN();
-#ifndef PAIR_NO_LD
-              tmem_ld16(t0 + ch * 16, r);
-#else
-#pragma unroll
-              for (int z = 0; z < 16; ++z) r[z] = t0 + z;
+          for (int h = 0; h < H; ++h) {
+            ST_BEGIN();
+            if (!mbar_wait_bounded_tell(&tfull[sl], sph, s_abort, peer_abort, kStatusWaitTimeoutEpilogue, kWaitLimit)) { ok = false; break; }
+            ST_END(0);
+            if (warp == 4 && lane == 0) TR(1, 1);     // accumulator complete
+            tc_fence_after();
+#ifdef SYFI_PAIR_STATS
+            st_p0 = clock64();
 #endif
-              const ulonglong2 s0 = sp4[0], s1 = sp4[1], s2 = sp4[2], s3 = sp4[3];
+            const uint32_t t0 = lane_addr + sl * kSlotCols + grp * UC;
+#ifndef PAIR_NO_PROMOTE
+            // scalar FMAs (measured faster here than packed f32x2 ones, whose operand pairs cost extra moves);
+            // the slot goes back to the MMA thread as soon as its last values are in registers
+#if defined(PAIR_LD2)
+            // sixteen up and sixteen gate columns per round: two loads in flight
+#pragma unroll
+            for (int c = 0; c < UC / 16; ++c) {
+              uint32_t ru[16], rg[16];
+              tmem_ld16(t0 + c * 16, ru);
+              tmem_ld16(t0 + 128 / H + c * 16, rg);
               tmem_ld_wait();
-              ST_END(1);
-#ifdef PAIR_NO_FMA
-              if (r[0] == 0x12345678u) acc[ch * 8] = s0.x;
+              if (c == UC / 16 - 1) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster_relaxed(mapa_tempty + 8u * sl);
+              }
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                up[h * UC + c * 16 + j] = fmaf(__uint_as_float(ru[j]), su, up[h * UC + c * 16 + j]);
+                gt[h * UC + c * 16 + j] = fmaf(__uint_as_float(rg[j]), sg, gt[h * UC + c * 16 + j]);
+              }
+            }
 #else
-              acc[ch * 8 + 0] = f32x2_fma(f32x2_pack_bits(r[0], r[1]), s0.x, acc[ch * 8 + 0]);
-              acc[ch * 8 + 1] = f32x2_fma(f32x2_pack_bits(r[2], r[3]), s0.y, acc[ch * 8 + 1]);
-              acc[ch * 8 + 2] = f32x2_fma(f32x2_pack_bits(r[4], r[5]), s1.x, acc[ch * 8 + 2]);
-              acc[ch * 8 + 3] = f32x2_fma(f32x2_pack_bits(r[6], r[7]), s1.y, acc[ch * 8 + 3]);
-              acc[ch * 8 + 4] = f32x2_fma(f32x2_pack_bits(r[8], r[9]), s2.x, acc[ch * 8 + 4]);
-              acc[ch * 8 + 5] = f32x2_fma(f32x2_pack_bits(r[10], r[11]), s2.y, acc[ch * 8 + 5]);
-              acc[ch * 8 + 6] = f32x2_fma(f32x2_pack_bits(r[12], r[13]), s3.x, acc[ch * 8 + 6]);
-              acc[ch * 8 + 7] = f32x2_fma(f32x2_pack_bits(r[14], r[15]), s3.y, acc[ch * 8 + 7]);
+#pragma unroll
+            for (int c = 0; c < 2 * UC / 16; ++c) {
+              const bool is_gate = c >= UC / 16;
+              const int cc = is_gate ? c - UC / 16 : c;
+              uint32_t r[16];
+              tmem_ld16(t0 + (is_gate ? 128 / H : 0) + cc * 16, r);
+              tmem_ld_wait();
+              if (c == 2 * UC / 16 - 1) {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster_relaxed(mapa_tempty + 8u * sl);
+                if (warp == 4 && lane == 0) TR(1, 3);     // slot released
+              }
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                if (!is_gate) up[h * UC + cc * 16 + j] = fmaf(__uint_as_float(r[j]), su, up[h * UC + cc * 16 + j]);
+                else gt[h * UC + cc * 16 + j] = fmaf(__uint_as_float(r[j]), sg, gt[h * UC + cc * 16 + j]);
+              }
+            }
 #endif
-            } else {
+#else
+            up[h] = su; gt[h] = sg; (void)t0;
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster_relaxed(mapa_tempty + 8u * sl);
+#endif
+            if (++sl == kSlots) { sl = 0; sph ^= 1u; }
+#ifdef SYFI_PAIR_STATS
+            st_acc[2] += clock64() - st_p0;
+#endif
+            if (warp == 4 && lane == 0) TR(1, 4);     // promoted
+          }
+          if (!ok) break;
+        }
+        if (ok) {   // the weight scales go back to the producer
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&wempty[par]);
+        }
+        ST_BEGIN();
+        // ---- SwiGLU of this token's 32 features, amax over the token's 128 features (four threads, one per
+        // column quarter), two-term requantisation; the fast exp and divide are a few ulp off the exact ones,
+        // far below the 8-bit requantisation that follows
+        const int my_rows = ok ? (rank == 0 ? min(im.n, 128) : max(im.n - 128, 0)) : 0;
+        // the next item's activation scales are requested now (this thread: 14 K blocks of its token) and
+        // stored once every warp of this lane quarter has left the K loop (the barrier below)
+        float nxt[kHBlocks / 4];
+        {
+          const bool more = i + 1 < my_items;
+          int eh = e_hint;
+          const PItem nx = more ? decode_pair_item<FI, NT>(s_work, p.e_local, item_of(i + 1), eh) : PItem{0, 0, 0, 0};
+          const int nrows = rank == 0 ? min(nx.n, 128) : max(nx.n - 128, 0);
+          const float* src = p.act_scale + static_cast<size_t>(grp) * (kHBlocks / 4) * p.row_cap + nx.row_start + 128 * rank + tl;
+#pragma unroll
+          for (int k = 0; k < kHBlocks / 4; ++k)
+            nxt[k] = (more && tl < nrows) ? __ldg(src + static_cast<size_t>(k) * p.row_cap) : 0.0f;
+        }
+        float c[32];
+        float amax = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float g = gt[j];
+          c[j] = g * __fdividef(1.0f, 1.0f + __expf(-g)) * up[j];
+          amax = fmaxf(amax, fabsf(c[j]));
+        }
+        float* red = s_red;
+        red[grp * 128 + tl] = amax;
+        named_bar_sync(1 + q, 128);             // the four warps that share this lane quarter
+        amax = fmaxf(fmaxf(red[tl], red[128 + tl]), fmaxf(red[256 + tl], red[384 + tl]));
+#pragma unroll
+        for (int k = 0; k < kHBlocks / 4; ++k) s_scale[(grp * (kHBlocks / 4) + k) * 128 + tl] = nxt[k];
+        if (tl < my_rows) {
+          const float scv = fmaxf(amax * (1.0f / 448.0f), 1e-12f);
+          const float inv = 1.0f / scv;
+          const size_t row = static_cast<size_t>(im.row_start) + 128 * rank + tl;
+          if (grp == 0) p.c_scale[static_cast<size_t>(im.ft) * p.row_cap + row] = scv;
+          uint32_t hw[8], lw[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint32_t hp = 0, lp = 0;
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const float v0 = c[4 * j + 2 * h], v1 = c[4 * j + 2 * h + 1];
+              const uint16_t hh = cvt_e4m3x2(v0 * inv, v1 * inv);
+              const float2 hb = e4m3x2_to_float2(hh);
+              const float r0 = fmaf(-hb.x, scv, v0), r1 = fmaf(-hb.y, scv, v1);
+              const uint16_t ll = cvt_e4m3x2(r0 * inv * kLoRatio, r1 * inv * kLoRatio);
+              hp |= static_cast<uint32_t>(hh) << (16 * h);
+              lp |= static_cast<uint32_t>(ll) << (16 * h);
+            }
+            hw[j] = hp;
+            lw[j] = lp;
+          }
+          // c[h * UC ..] are features (128 / H) h + UC grp .. of the tile: H chunks of UC bytes per term
+          constexpr int UC = 32 / H;
+#pragma unroll
+          for (int h = 0; h < H; ++h) {
+            const size_t off = row * kInter + static_cast<size_t>(im.ft) * 128 + h * (128 / H) + grp * UC;
+#pragma unroll
+            for (int v = 0; v < UC / 16; ++v) {
+              const int w0 = (h * UC + v * 16) / 4;
+              *reinterpret_cast<uint4*>(p.c_hi + off + v * 16) = make_uint4(hw[w0], hw[w0 + 1], hw[w0 + 2], hw[w0 + 3]);
+              *reinterpret_cast<uint4*>(p.c_lo + off + v * 16) = make_uint4(lw[w0], lw[w0 + 1], lw[w0 + 2], lw[w0 + 3]);
+            }
+          }
+        }
+        named_bar_sync(1 + q, 128);             // the next item's scales are in place, the amax exchange is free
+        // hand the item to the publisher warp (see grouped_gemm.cu)
+        __threadfence_block();
+        __syncwarp();
+        if (lane == 0) atomicAdd(s_done, 1);
+        ST_END(3);
+      } else {
+        // ===== feature-major: lane = output feature, columns [32 grp, +32) = hi, [n + 32 grp, +32) = lo
+        constexpr int CN = 32;
+        const int c0 = grp * CN;
+        const int n = ok ? im.n : 0;
+        uint64_t acc[CN / 2];
+#pragma unroll
+        for (int j = 0; j < CN / 2; ++j) acc[j] = 0ull;
+        for (int kb = 0; kb < KB && ok; ++kb) {
+          ST_BEGIN();
+          if (!mbar_wait_bounded_tell(&tfull[sl], sph, s_abort, peer_abort, kStatusWaitTimeoutEpilogue, kWaitLimit)) { ok = false; break; }
+          ST_END(0);
+          tc_fence_after();
+          if (!mbar_wait_bounded_tell(&sfull[s], sp, s_abort, peer_abort, kStatusWaitTimeoutEpilogue, kWaitLimit)) { ok = false; break; }
+#ifdef SYFI_PAIR_STATS
+          const long long st_p0 = clock64();
+#endif
+          const float* sc = s_scale + s * SE + c0;
+          const uint32_t t0 = lane_addr + sl * kSlotCols + c0;
+#pragma unroll
+          for (int ch = 0; ch < CN / 16; ++ch) {
+            if (c0 + ch * 16 < n) {
+              const ulonglong2* sp4 = reinterpret_cast<const ulonglong2*>(sc + ch * 16);
               uint32_t r[16], l[16];
               tmem_ld16(t0 + ch * 16, r);                 // hi products
               tmem_ld16(t0 + im.n + ch * 16, l);          // lo products of the same token columns
@@ -536,131 +787,20 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
               }
             }
           }
-        }
-        // the slot and the scale entry go back (the values are in registers)
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-#ifdef PAIR_RELEASE_ARRIVE
-          mbar_arrive_cluster(tempty0[sl]);
-#else
-          mbar_arrive_cluster_relaxed(sl == 0 ? tempty0[0] : tempty0[1]);
-#endif
-          mbar_arrive(&sempty[s]);
-        }
-        if (++sl == kSlots) { sl = 0; sph ^= 1u; }
-        if (++s == kScaleRing) { s = 0; sp ^= 1u; }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive_cluster_relaxed(mapa_tempty + 8u * sl);
+            mbar_arrive(&sempty[s]);
+          }
+          if (++sl == kSlots) { sl = 0; sph ^= 1u; }
+          if (++s == kScaleRing) { s = 0; sp ^= 1u; }
 #ifdef SYFI_PAIR_STATS
-        st_acc[2] += clock64() - st_p0;
+          st_acc[2] += clock64() - st_p0;
 #endif
-      }
-      const int n_out = ok ? n : 0;               // a failed item stores nothing
-      ST_BEGIN();
-
-      if (MODE == 1) {
-        // ---- swap halves with the partner: this CTA keeps columns c0 + 32 rank .. + 31 of every thread's
-        // 64 and sends the other 32; the same thread of the partner CTA does the opposite, so each CTA
-        // ends up with up AND gate of 128 features x (its 128 of the 256 token columns).
-        if (rank == 1) {
-#pragma unroll
-          for (int j = 0; j < 16; ++j) { const uint64_t t = acc[j]; acc[j] = acc[j + 16]; acc[j + 16] = t; }
         }
-        // now acc[0..15] = kept columns, acc[16..31] = columns to send
-        const int keep0 = c0 + 32 * static_cast<int>(rank);      // first kept token column of the item
-        const int send0 = c0 + 32 * static_cast<int>(peer);
-        float mine[32], other[32];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) f32x2_unpack(acc[j], mine[2 * j], mine[2 * j + 1]);
-        if (ok && !mbar_wait_bounded_pair(xfree, xph ^ 1u, s_abort, peer_abort, kStatusWaitTimeoutEpilogue, kWaitLimit)) ok = false;
-        if (ok) {
-          const uint32_t dst = peer_xchg + static_cast<uint32_t>((grp * 32) * 128 + f) * 4u;
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            if (send0 + ((2 * j) & ~15) < n_out) {
-              float a, b;
-              f32x2_unpack(acc[16 + j], a, b);
-              st_cluster_f32(dst + static_cast<uint32_t>(2 * j) * 512u, a);
-              st_cluster_f32(dst + static_cast<uint32_t>(2 * j + 1) * 512u, b);
-            }
-          }
-          fence_acq_rel_cluster();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(peer_xfull);
-          if (!mbar_wait_bounded_pair(xfull, xph, s_abort, peer_abort, kStatusWaitTimeoutEpilogue, kWaitLimit)) ok = false;
-        }
-        const int n_keep = ok ? n_out : 0;
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          other[j] = (keep0 + (j & ~15) < n_keep) ? s_xchg[(grp * 32 + j) * 128 + f] : 0.0f;
-        if (ok) {
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(peer_xfree);
-        }
-        xph ^= 1u;
-
-        // ---- SwiGLU, per-row amax over the 128 features, two-term requantisation (as in grouped_gemm.cu)
-        const int slot0 = grp * 32;               // this thread's columns in the CTA's 128 kept columns
-        const int bar_id = 1 + grp;
-#pragma unroll
-        for (int jb = 0; jb < 32; jb += 16) {
-          if (keep0 + jb < n_keep) {
-            float mx[16];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const float up = rank == 0 ? mine[jb + j] : other[jb + j];
-              const float gt = rank == 0 ? other[jb + j] : mine[jb + j];
-              const float cv = gt * __fdividef(1.0f, 1.0f + __expf(-gt)) * up;
-              mine[jb + j] = cv;
-              mx[j] = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(cv))));
-            }
-            if (lane == 0) {
-              float4* dst = reinterpret_cast<float4*>(s_red + q * 128 + slot0 + jb);
-#pragma unroll
-              for (int j = 0; j < 4; ++j) dst[j] = make_float4(mx[4 * j], mx[4 * j + 1], mx[4 * j + 2], mx[4 * j + 3]);
-            }
-          }
-        }
-        named_bar_sync(bar_id, 128);
-        if (q == 0 && keep0 + lane < n_keep) {
-          const int sl_i = slot0 + lane;
-          const float amax = fmaxf(fmaxf(s_red[sl_i], s_red[128 + sl_i]), fmaxf(s_red[256 + sl_i], s_red[384 + sl_i]));
-          const float scv = fmaxf(amax * (1.0f / 448.0f), 1e-12f);
-          s_cs[sl_i] = scv;
-          s_inv[sl_i] = 1.0f / scv;
-          p.c_scale[static_cast<size_t>(im.ft) * p.row_cap + im.row_start + keep0 + lane] = scv;
-        }
-        named_bar_sync(bar_id, 128);
-        const int qrow = lane & 3;                // which of four rows this lane stores after the transpose
-        const size_t qoff = static_cast<size_t>(im.ft) * 128 + q * 32 + (lane >> 2) * 4;
-#pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          if (keep0 + (j & ~15) < n_keep) {
-            uint32_t hp = 0, lp = 0;
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-              const int c = j + 2 * h;
-              const float sc0 = s_cs[slot0 + c], sc1 = s_cs[slot0 + c + 1];
-              const float in0 = s_inv[slot0 + c], in1 = s_inv[slot0 + c + 1];
-              const float v0 = mine[c], v1 = mine[c + 1];
-              const uint16_t hh = cvt_e4m3x2(v0 * in0, v1 * in1);
-              const float2 hb = e4m3x2_to_float2(hh);
-              const float r0 = fmaf(-hb.x, sc0, v0), r1 = fmaf(-hb.y, sc1, v1);
-              const uint16_t ll = cvt_e4m3x2(r0 * in0 * kLoRatio, r1 * in1 * kLoRatio);
-              hp |= static_cast<uint32_t>(hh) << (16 * h);
-              lp |= static_cast<uint32_t>(ll) << (16 * h);
-            }
-            hp = quad_transpose_bytes(hp, lane);
-            lp = quad_transpose_bytes(lp, lane);
-            const size_t off = static_cast<size_t>(im.row_start + keep0 + j + qrow) * kInter + qoff;
-            *reinterpret_cast<uint32_t*>(p.c_hi + off) = hp;
-            *reinterpret_cast<uint32_t*>(p.c_lo + off) = lp;
-          }
-        }
-        named_bar_sync(bar_id, 128);              // s_red / s_cs of this group are free for the next item
-        __threadfence_block();
-        __syncwarp();
-        if (lane == 0) atomicAdd(s_done, 1);
-      } else {
+        const int n_out = ok ? n : 0;               // a failed item stores nothing
+        ST_BEGIN();
         float out[CN];
 #pragma unroll
         for (int j = 0; j < CN / 2; ++j) f32x2_unpack(acc[j], out[2 * j], out[2 * j + 1]);
@@ -675,8 +815,8 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
             *reinterpret_cast<float4*>(o + static_cast<size_t>(j) * kHidden) = make_float4(a0, a1, a2, a3);
           }
         }
+        ST_END(3);
       }
-      ST_END(3);
     }
     ST_WRITE(8, warp == 4 && lane == 0);
 #ifdef SYFI_PAIR_STATS
@@ -699,7 +839,8 @@ template <int MODE>
 cudaError_t launch_pair(const PairGemmLaunch& g, const PairArgs& a, int num_sms, cudaStream_t st) {
   const int grid = num_sms & ~1;   // whole pairs
   return launch_dependent(pair_gemm_kernel<MODE>, dim3(grid), dim3(kPairThreads),
-                          static_cast<size_t>(PairCfg<MODE>::kSmemBytes), st, g.tm_w, g.tm_b0, g.tm_b1, a);
+                          static_cast<size_t>(PairCfg<MODE>::kSmemBytes), st, g.tm_w, g.tm_b0, g.tm_b1, g.tm_b0w, g.tm_b1w,
+                          a);
 }
 
 }  // namespace

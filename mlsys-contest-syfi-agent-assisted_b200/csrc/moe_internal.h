@@ -96,6 +96,8 @@ struct PairGemmLaunch {
   CUtensorMap tm_w;    // weights, 2-D [E * rows_per_expert, K], box 128 x 128
   CUtensorMap tm_b0;   // GEMM1: a_perm; GEMM2: c_hi; box 32 x 128
   CUtensorMap tm_b1;   // GEMM2: c_lo (unused by GEMM1)
+  CUtensorMap tm_b0w;  // the same tensors with 128-row boxes (tiles of more than 64 rows: one load instead of four)
+  CUtensorMap tm_b1w;
 };
 
 // Programmatic dependent launch: the kernel may be scheduled while its predecessor in the stream is
