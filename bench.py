@@ -1,27 +1,35 @@
 """Benchmark of the fused FP8 block-scale DeepSeek-V3 MoE layer.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--tokens T]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--config 3|4] [--tokens T] [--no-cpu-baseline] [--no-decode] [--no-parity]
 
 One "step" is one call of the layer on one batch of synthetic tokens.
 
-N = 1 (default): the decode-batch configuration — T = 64 tokens, 32 local experts of 256
-(offset 0), seed 0, weights generated on the device.  ``value`` is tokens/s with every
-input already resident in HBM; ``e2e`` is the same call made through ``run_moe_host``
-with the per-step tensors in pinned host memory (H2D of logits / bias / hidden states /
-scales and D2H of the bf16 output inside the timed region; the weights are resident
-parameters).  ``roofline`` is for the dominant kernel (GEMM1 with fused SwiGLU), timed
-with CUDA events recorded by the library around that kernel on the launching stream.
-``cpu_baseline`` times the oracle on the host cores.
+Workloads (seeded synthetic tensors with the definition's shapes and value distributions):
 
-N > 1 (launched by torchrun, one rank per GPU): expert parallelism with weak scaling.
-Every rank brings its own batch of T tokens and owns experts [32 r, 32 r + 32); per step
-the token-side tensors are all-gathered, each rank runs the layer for its experts over
-the N*T gathered tokens (f32 partial sums), and a reduce-scatter sums the partials and
-returns each rank its own T rows, which are rounded to bf16 once.  ``value`` counts the
-N*T tokens of the job.
+* config 3 (default), the largest single-GPU configuration: T = 8192 tokens, the 32 local experts
+  [0, 32) of 256, seed 0.  On N > 1 GPUs (launched by torchrun, one rank per GPU) the SAME layer is
+  sharded by expert: rank r owns experts [32 r / N, 32 (r + 1) / N) (slices of the same seed-0
+  weights), every rank holds all T tokens, computes the f32 partial of its experts, the partials are
+  all-reduced over NCCL and rounded to bf16 once.  Total work is fixed as N grows: "strong" scaling.
+* config 4 (``--config 4``), the full 256-expert layer with load imbalance: T = 4096 tokens shared by
+  all ranks, logits of 16 hot experts raised by 1.5, rank r owns experts [32 r, 32 r + 32) drawn from
+  weight seed r; meant for N = 8 (fewer ranks compute the first 32 N experts only).
+* ``--tokens T`` replaces the token count of config 3 (sweeps; T = 64 is the decode batch).
 
-``--impl reference`` times the CPU restatement of the definition's reference (the oracle)
-on the host cores, on a bounded sample of the same workload, and prints the same line.
+``value`` is tokens/s with every input already resident in HBM, timed with CUDA events on the
+launching stream (max over ranks).  ``e2e`` is the same call made through ``run_moe_host`` with the
+per-step tensors in pinned host memory (H2D of logits / bias / hidden states / scales and D2H of the
+bf16 output inside the timed region; the weights are resident parameters).  ``roofline`` is for the
+dominant kernel (GEMM1 with fused SwiGLU and requantisation), timed with CUDA events the library
+records around that kernel: tensor-bound (TFLOP/s) from 4096 tokens on, HBM-bound (GB/s) below.
+``decode`` repeats the measurement for the decode batch (T = 64) and adds T = 16 and T = 1024: the
+metric is quoted against T.  ``parity`` compares one step's output with the oracle (executed with torch
+on the GPU, summed over ranks in f32) outside the timed region.  ``cpu_baseline`` times the oracle on the
+host cores on a bounded sample of the workload.
+
+``--impl reference`` times the CPU restatement of the definition's reference (the oracle) on the host
+cores, on a bounded sample of the same workload, and prints the same line.
 """
 from __future__ import annotations
 
@@ -41,24 +49,42 @@ PKG = "mlsys-contest-syfi-agent-assisted_b200"
 METRIC = "moe_layer_tokens_per_s"
 UNIT = "tokens/s"
 H, I = 7168, 2048
+GEMM1_FLOP_PER_ROW = 2 * H * 2 * I          # 58,720,256
+NOMINAL_FP8_TFLOPS = 4500.0                 # dense FP8, NVIDIA's B200 figure
 
-# DRAM bytes (read + write) of one GEMM1 launch at the N = 1 workload, from the ncu capture
-# summarised in profiles/gemm_decode_T64.md (dram__bytes_read.sum + dram__bytes_write.sum).
-GEMM1_NCU_TRAFFIC_BYTES = 476318208
+
+def workload_name(config: int, T: int) -> str:
+    if config == 4:
+        return (f"config 4: T={T} tokens shared by all ranks, 256 experts in 8 x 32 (rank r: experts [32r, 32r+32), "
+                "weight seed r), 16 hot experts (logits +1.5, hot seed 1), token seed 0")
+    return f"config 3: T={T} tokens, 32 local experts [0, 32) of 256 global, seed 0, routed_scaling_factor 2.5"
 
 
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
-    return 6650.0, "fallback (earlier measurement on this pool)"
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d["bf16_tflops_sustained"]), "source": "measured (MEASURED_PEAKS.json)"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback (earlier measurement on this pool)"}
+
+
+def ncu_traffic(kernel_key: str):
+    """DRAM bytes per launch from the committed ncu summary (profiles/ncu_traffic.json), or None."""
+    path = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+    try:
+        with open(path) as f:
+            return json.load(f).get(kernel_key)
+    except Exception:
+        return None
 
 
 class ClockSampler(threading.Thread):
     """Samples SM clock and throttle reasons through NVML while the timed region runs."""
 
-    def __init__(self, index: int, period_s: float = 0.02):
+    def __init__(self, index: int, period_s: float = 0.005):
         super().__init__(daemon=True)
         self.index, self.period = index, period_s
         self.samples, self.reasons, self.max_mhz = [], set(), None
@@ -145,6 +171,26 @@ class CpuArm:
                 "sample": sample}
 
 
+def build_inputs(pkg, args, rank, world, dev):
+    """This rank's inputs: (MoeInputs with the rank's expert slice, experts per rank)."""
+    T = args.tokens
+    if args.config == 4:
+        inp = pkg.make_inputs(num_tokens=T, seed=0, e_local=32, local_expert_offset=32 * rank, device=dev,
+                              hot_experts=16, weight_seed=rank)
+        return inp, 32
+    inp = pkg.make_inputs(num_tokens=T, seed=0, e_local=32, local_expert_offset=0, device=dev)
+    if world == 1:
+        return inp, 32
+    per = 32 // world
+    sl = slice(rank * per, (rank + 1) * per)
+    part = pkg.MoeInputs(inp.routing_logits, inp.routing_bias, inp.hidden_states, inp.hidden_states_scale,
+                         inp.gemm1_weights[sl].clone(), inp.gemm1_weights_scale[sl].clone(),
+                         inp.gemm2_weights[sl].clone(), inp.gemm2_weights_scale[sl].clone(), rank * per,
+                         inp.routed_scaling_factor)
+    del inp
+    return part, per
+
+
 def run_reference_arm(args):
     import torch
     rank, local_rank, world = dist_env()
@@ -154,8 +200,10 @@ def run_reference_arm(args):
     oracle = importlib.import_module("oracle.moe_oracle")
     T = args.tokens
     dev = "cuda:0" if torch.cuda.is_available() else "cpu"   # the device only draws the weights faster
-    inp = pkg.make_inputs(num_tokens=T, seed=0, e_local=32, device=dev).to("cpu")
+    inp, _ = build_inputs(pkg, args, 0, 1, dev)
+    inp = inp.to("cpu")
     W, K = max(args.warmup, 0), max(args.steps, 1)
+    W, K = min(W, 1), min(K, 3)               # bounded: every step is tens of seconds of host work
     per_call_budget = max(2.0, min(30.0, 150.0 / (W + K)))
     arm = CpuArm(torch, oracle, inp, per_call_budget)
     times = []
@@ -167,10 +215,11 @@ def run_reference_arm(args):
     value = T / (ms / 1e3)
     base = arm.describe(ms / 1e3)
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-            "steps": K, "warmup": W, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "steps": K, "warmup": W, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong" if args.config == 3 else "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"decode batch T={T}, 32 local experts of 256, offset 0, seed 0 (CPU oracle)",
-                       "tokens": T, "local_experts": 32},
+            "config": {"workload": workload_name(args.config, T), "tokens": T, "local_experts": 32,
+                       "note": "the reference arm is the CPU oracle on rank 0's experts (single-GPU workload)"},
             "cpu_baseline": base,
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -178,16 +227,73 @@ def run_reference_arm(args):
     return 0
 
 
+def time_layer(torch, step, K, barrier, dist, dev):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(K):
+        step()
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1) / K
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
+
+
+def stage_pass(ctx, step, n):
+    ctx.set_stage_timing(True)
+    acc = {}
+    for _ in range(n):
+        step()
+        for k, v in ctx.last_stage_ms().items():
+            acc[k] = acc.get(k, 0.0) + v
+    ctx.set_stage_timing(False)
+    return {k: v / n for k, v in acc.items()}
+
+
+def gemm1_roofline(T, rows, active, stage_ms, peaks, world):
+    """Roofline entry of the dominant kernel for one workload."""
+    t = stage_ms["gemm1"] * 1e-3
+    if T >= 4096:
+        flops = rows * GEMM1_FLOP_PER_ROW
+        achieved = flops / t / 1e12
+        peak = 2.0 * peaks["bf16_tflops_sustained"]
+        key = "pair_gemm_kernel<1>@T8192_E32" if (T == 8192 and world == 1) else None
+        return {"kernel": "pair_gemm_kernel<1> (GEMM1 + SwiGLU + two-term requantisation, CTA pairs, tcgen05 cta_group::2)",
+                "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                "peak_note": "no FP8 figure in MEASURED_PEAKS.json: 2 x bf16_tflops_sustained as the measured proxy "
+                             "(kernel timed inside a long step)",
+                "frac_of_nominal_fp8": achieved / NOMINAL_FP8_TFLOPS, "nominal_fp8_tflops": NOMINAL_FP8_TFLOPS,
+                "traffic": ncu_traffic(key) if key else None, "algorithmic_flops": flops,
+                "launch_ms": stage_ms["gemm1"], "peak_source": peaks["source"]}
+    gemm1_bytes = active * (2 * I * H + 4 * (2 * I // 128) * (H // 128)) + rows * (H + 4 * (H // 128)) \
+        + rows * (2 * I + 4 * (I // 128))
+    achieved = gemm1_bytes / t / 1e9
+    key = "grouped_gemm_kernel<1,32>@T64_E32" if (T == 64 and world == 1) else None
+    return {"kernel": "grouped_gemm_kernel<1> (GEMM1 + SwiGLU + two-term requantisation)", "bound": "hbm",
+            "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+            "traffic": ncu_traffic(key) if key else None, "algorithmic_bytes": gemm1_bytes,
+            "launch_ms": stage_ms["gemm1"], "peak_source": peaks["source"]}
+
+
 # --------------------------------------------------------------------------- GPU arm
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=1000)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--tokens", type=int, default=64)
+    ap.add_argument("--config", type=int, default=3, choices=[3, 4])
+    ap.add_argument("--tokens", type=int, default=None)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--no-parity", action="store_true")
     args = ap.parse_args()
+    if args.tokens is None:
+        args.tokens = 8192 if args.config == 3 else 4096
     if args.impl == "reference":
         return run_reference_arm(args)
 
@@ -197,11 +303,12 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the MoE layer has no CPU path")
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
-    if world > 8:
-        raise SystemExit("at most 8 ranks (8 x 32 experts = the 256 global experts)")
+    if world > 8 or (args.config == 3 and 32 % world != 0):
+        raise SystemExit("1, 2, 4 or 8 ranks")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     pkg = importlib.import_module(PKG)
+    oracle = importlib.import_module("oracle.moe_oracle")
     dist = None
     if world > 1:
         import torch.distributed as dist
@@ -209,32 +316,20 @@ def main():
 
     T = args.tokens
     W, K = max(args.warmup, 3), max(args.steps, 1)
-    # token-side tensors: this rank's own batch; weights: this rank's 32 experts
-    inp = pkg.make_inputs(num_tokens=T, seed=rank, e_local=32, local_expert_offset=32 * rank if world > 1 else 0,
-                          device=dev, weight_seed=rank)
-    ctx = pkg.get_context(local_rank, T * world)
+    inp, e_per_rank = build_inputs(pkg, args, rank, world, dev)
+    ctx = pkg.get_context(local_rank, T)
     out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+    peaks = measured_peaks()
 
-    peer_ok = False
     if world == 1:
         def step():
             pkg.run_moe(*inp.args(), out)
-        n_tok_layer = T
     else:
         ep = pkg.ExpertParallelMoe(inp.gemm1_weights, inp.gemm1_weights_scale, inp.gemm2_weights,
                                    inp.gemm2_weights_scale, inp.local_expert_offset, inp.routed_scaling_factor)
-        # token all-gather and reduce-scatter through the library's own peer-memory kernels when the
-        # ranks can map each other's memory, NCCL collectives otherwise
-        peer_ok = ep.enable_peer_exchange(T, dev)
-        flag = torch.tensor([1 if peer_ok else 0], device=dev)
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        if int(flag.item()) == 0:
-            ep._peer = None
-            peer_ok = False
 
         def step():
-            ep.forward_sharded(inp.routing_logits, inp.routing_bias, inp.hidden_states, inp.hidden_states_scale, out)
-        n_tok_layer = T * world
+            ep.forward_replicated(inp.routing_logits, inp.routing_bias, inp.hidden_states, inp.hidden_states_scale, out)
 
     def barrier():
         if dist is not None:
@@ -248,45 +343,48 @@ def main():
 
     sampler = ClockSampler(local_rank)
     sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    e0.record()
-    for _ in range(K):
-        step()
-    e1.record()
+    ms = time_layer(torch, step, K, barrier, dist, dev)
     sampler.sample()
-    barrier()
     clocks = sampler.finish()
-    ms = e0.elapsed_time(e1) / K
-    if dist is not None:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
     stats = ctx.check()
     launches = ctx.launch_count() * K
-    value = world * T / (ms / 1e3)
+    value = T / (ms / 1e3)
+
+    # ---- parity of one step against the oracle (torch on the GPU, f32 partials summed over ranks); untimed
+    parity = None
+    if not args.no_parity:
+        out.fill_(float("nan"))
+        step()
+        barrier()
+        ref32, ridx, rw = oracle.moe_forward(*inp.args(), return_f32=True)
+        if dist is not None:
+            dist.all_reduce(ref32)
+        ok, ostats = oracle.check_output(out, ref32.to(torch.bfloat16))
+        idx, w = ctx.last_routing(T)
+        cidx, cw = oracle.route(inp.routing_logits.cpu(), inp.routing_bias.cpu(), inp.routed_scaling_factor)
+        rok, rstats = oracle.check_routing(idx, w, cidx, cw)
+        flag = torch.tensor([1 if (ok and rok) else 0], device=dev)
+        if dist is not None:
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        parity = {"ok": bool(int(flag.item())), "output": ostats, "routing": rstats,
+                  "against": "oracle with torch on the GPU, f32 partials summed over ranks, one rounding to bf16; "
+                             "routing against the oracle's CPU route"}
+        del ref32
 
     # ---- per-kernel pass (same steps, events around every kernel) -> roofline of GEMM1
-    ctx.set_stage_timing(True)
-    Ks = min(K, 200)
-    acc = {}
-    for _ in range(Ks):
-        step()
-        for k, v in ctx.last_stage_ms().items():
-            acc[k] = acc.get(k, 0.0) + v
-    ctx.set_stage_timing(False)
-    stage_ms = {k: v / Ks for k, v in acc.items()}
+    Ks = min(K, 100)
+    stage_ms = stage_pass(ctx, step, Ks)
     rows, active = stats["routes"], stats["active_experts"]
-    gemm1_bytes = active * (2 * I * H + 4 * (2 * I // 128) * (H // 128)) + rows * (H + 4 * (H // 128)) \
-        + rows * (2 * I + 4 * (I // 128))
-    peak, peak_src = measured_peaks()
-    achieved = gemm1_bytes / (stage_ms["gemm1"] * 1e-3) / 1e9
-    roofline = {"kernel": "grouped_gemm_kernel<1> (GEMM1 + SwiGLU + requantisation)", "bound": "hbm",
-                "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": (GEMM1_NCU_TRAFFIC_BYTES if (world == 1 and T == 64) else None), "algorithmic_bytes": gemm1_bytes,
-                "launch_ms": stage_ms["gemm1"], "peak_source": peak_src, "timed_steps": Ks,
-                "stage_ms": stage_ms}
-    flops, layer_bytes = pkg.algorithmic_work(rows, active, n_tok_layer)
+    roofline = gemm1_roofline(T, rows, active, stage_ms, peaks, world)
+    roofline["stage_ms"] = stage_ms
+    roofline["timed_steps"] = Ks
+    flops, layer_bytes = pkg.algorithmic_work(rows, active, T)
+    if dist is not None:
+        tot = torch.tensor([float(rows), float(flops)], device=dev, dtype=torch.float64)
+        dist.all_reduce(tot)
+        rows_all, flops_all = int(tot[0].item()), float(tot[1].item())
+    else:
+        rows_all, flops_all = rows, flops
 
     # ---- end to end: per-step tensors in pinned host memory
     h_in = [t.cpu().pin_memory() for t in (inp.routing_logits, inp.routing_bias, inp.hidden_states,
@@ -307,7 +405,7 @@ def main():
             step()
             h_out.copy_(out, non_blocking=True)
             torch.cuda.current_stream().synchronize()
-    Ke = min(K, 300)
+    Ke = min(K, 50)
     for _ in range(3):
         e2e_step()
     barrier()
@@ -322,54 +420,77 @@ def main():
         e2e_ms = float(t.item())
     ctx.check()
 
-    # ---- the same steps on weights re-laid out once by prepack_weights (1 GPU only; an extra, not the headline)
-    prepacked = None
-    if world == 1:
-        packed = pkg.prepack_weights(inp.gemm1_weights, inp.gemm2_weights)
-        out_p = torch.empty_like(out)
+    # ---- the decode batch and two more sizes on the same weights (1 GPU, config 3 only): the metric is quoted vs T
+    decode = None
+    if world == 1 and args.config == 3 and not args.no_decode and T != 64:
+        decode = {}
+        for Td in (16, 64, 1024):
+            tk = pkg.make_inputs(num_tokens=Td, seed=0, e_local=1, device="cpu")
+            small = pkg.MoeInputs(tk.routing_logits.to(dev), tk.routing_bias.to(dev), tk.hidden_states.to(dev),
+                                  tk.hidden_states_scale.to(dev), inp.gemm1_weights, inp.gemm1_weights_scale,
+                                  inp.gemm2_weights, inp.gemm2_weights_scale, 0, inp.routed_scaling_factor)
+            o = torch.empty(Td, H, dtype=torch.bfloat16, device=dev)
 
-        def packed_step():
-            pkg.run_moe_prepacked(inp.routing_logits, inp.routing_bias, inp.hidden_states, inp.hidden_states_scale,
-                                  packed, inp.gemm1_weights_scale, inp.gemm2_weights_scale, inp.local_expert_offset,
-                                  inp.routed_scaling_factor, out_p)
-        for _ in range(max(W, 3)):
-            packed_step()
-        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        p0.record()
-        for _ in range(K):
-            packed_step()
-        p1.record()
-        torch.cuda.synchronize(dev)
-        pms = p0.elapsed_time(p1) / K
-        step()
-        torch.cuda.synchronize(dev)
-        prepacked = {"ms_per_step": pms, "value": T / (pms / 1e3), "unit": UNIT,
-                     "bit_identical_to_unpacked": bool(torch.equal(out, out_p)),
-                     "note": "weights re-laid out once into consumption-order swizzled tiles, fetched with untiled bulk copies"}
-        ctx.check()
-        del packed
+            def dstep():
+                pkg.run_moe(*small.args(), o)
+            for _ in range(5):
+                dstep()
+            torch.cuda.synchronize()
+            dms = time_layer(torch, dstep, 300, torch.cuda.synchronize, None, dev)
+            dstats = ctx.check()
+            dstage = stage_pass(ctx, dstep, 50)
+            fl, by = pkg.algorithmic_work(dstats["routes"], dstats["active_experts"], Td)
+            entry = {"tokens": Td, "ms_per_step": dms, "value": Td / (dms / 1e3), "unit": UNIT,
+                     "routes": dstats["routes"], "active_experts": dstats["active_experts"],
+                     "layer_gbs": by / (dms * 1e-3) / 1e9, "layer_frac_of_hbm_peak": by / (dms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                     "layer_tflops": fl / (dms * 1e-3) / 1e12,
+                     "roofline": gemm1_roofline(Td, dstats["routes"], dstats["active_experts"], dstage, peaks, 1),
+                     "stage_ms": dstage}
+            if Td == 64:
+                hd = [t.cpu().pin_memory() for t in (small.routing_logits, small.routing_bias, small.hidden_states,
+                                                     small.hidden_states_scale)]
+                ho = torch.empty(Td, H, dtype=torch.bfloat16).pin_memory()
+
+                def de2e():
+                    pkg.run_moe_host(*hd, inp.gemm1_weights, inp.gemm1_weights_scale, inp.gemm2_weights,
+                                     inp.gemm2_weights_scale, 0, inp.routed_scaling_factor, ho)
+                for _ in range(5):
+                    de2e()
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                for _ in range(300):
+                    de2e()
+                torch.cuda.synchronize()
+                dems = (time.perf_counter() - t0) * 1e3 / 300
+                entry["e2e"] = {"value": Td / (dems / 1e3), "unit": UNIT, "ms_per_step": dems,
+                                "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in hd),
+                                "d2h_bytes_per_step": ho.numel() * ho.element_size()}
+            decode[f"T{Td}"] = entry
+            ctx.check()
 
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
-            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f8e4m3",
-            "data": "synthetic",
-            "config": {"workload": (f"decode batch T={T} per rank, 32 local experts per rank of 256 global, seed = rank"
-                                    + ("" if world == 1 else f"; expert parallel over {world} ranks: all-gather tokens, "
-                                       "reduce-scatter f32 partials ("
-                                       + ("own kernels over peer memory" if peer_ok else "NCCL") + ")")),
-                       "tokens_per_rank": T, "local_experts": 32, "routes": rows, "active_experts": active,
-                       "l2": f"inputs larger than L2: {active * 44050944 / 1e6:.0f} MB of active-expert weights per step",
-                       "layer_algorithmic_bytes": layer_bytes, "layer_flops": flops,
-                       "layer_gbs": layer_bytes / (ms * 1e-3) / 1e9, "layer_tflops": flops / (ms * 1e-3) / 1e12},
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if args.config == 3 else "weak",
+            "vs_baseline": None, "dtype": "f8e4m3", "data": "synthetic",
+            "config": {"workload": workload_name(args.config, T), "tokens": T, "local_experts_per_rank": e_per_rank,
+                       "parallelism": ("1 GPU" if world == 1 else
+                                       f"expert parallel over {world} ranks, tokens replicated, f32 partials all-reduced (NCCL)"),
+                       "routes": rows_all, "routes_rank0": rows, "active_experts_rank0": active,
+                       "l2": f"inputs larger than L2: {active * 44050944 / 1e6:.0f} MB of active-expert weights per step on rank 0",
+                       "layer_flops": flops_all, "layer_tflops": flops_all / (ms * 1e-3) / 1e12,
+                       "layer_frac_of_nominal_fp8": flops_all / (ms * 1e-3) / 1e12 / (NOMINAL_FP8_TFLOPS * world),
+                       "layer_algorithmic_bytes_rank0": layer_bytes,
+                       "workspace_bytes": ctx.workspace_bytes() if hasattr(ctx, "workspace_bytes") else None},
             "clocks": clocks,
-            "e2e": {"value": world * T / (e2e_ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": h2d,
+            "e2e": {"value": T / (e2e_ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": Ke},
             "gpu_launches": launches, "roofline": roofline}
-    if prepacked is not None:
-        line["prepacked"] = prepacked
+    if parity is not None:
+        line["parity"] = parity
+    if decode is not None:
+        line["decode"] = decode
 
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        oracle = importlib.import_module("oracle.moe_oracle")
-        arm = CpuArm(torch, oracle, inp.to("cpu"), budget_s=25.0)
+        arm = CpuArm(torch, oracle, inp.to("cpu"), budget_s=20.0)
         line["cpu_baseline"] = arm.describe(arm.step())
     if rank == 0:
         print(json.dumps(line), flush=True)

@@ -134,21 +134,115 @@ def test_odd_shapes_match_oracle(T, E, off, seed, pkg, oracle):
     assert ok, (ostats, stats)
 
 
-def test_every_token_tile_gives_the_same_bits(pkg, oracle, monkeypatch):
-    """The GEMM kernels exist for token tiles of 32, 64 and 128 rows (the library picks by batch size, the
-    environment variable forces one).  The tile changes the work split, never the arithmetic of an output
-    element, so all three must agree bit for bit, and with the oracle within tolerance; 600 tokens over 8
-    experts give every expert several full tiles and a ragged last one."""
-    inp = pkg.make_inputs(num_tokens=600, seed=11, e_local=8, local_expert_offset=16, device=DEV)
+def _check_against_gpu_oracle(pkg, oracle, inp):
+    """Whole layer against the oracle executed with torch on the GPU (large cases), routing against the
+    oracle's CPU route (the one the golden vectors pin)."""
+    T = inp.num_tokens
+    out, stats = _run(pkg, inp)
+    ref, _, _ = oracle.moe_forward(*inp.args())
+    cidx, cw = oracle.route(inp.routing_logits.cpu(), inp.routing_bias.cpu(), inp.routed_scaling_factor)
+    idx, w = pkg.get_context(0).last_routing(T)
+    ok, rstats = oracle.check_routing(idx, w, cidx, cw)
+    assert ok, rstats
+    ok, ostats = oracle.check_output(out, ref)
+    assert ok, (ostats, stats)
+    return out, stats
+
+
+def test_full_prefill_configuration_matches_oracle(pkg, oracle):
+    """The largest single-GPU configuration: T = 8192 tokens, all 32 local experts, seed 0, offset 0
+    (8951 routed rows over 30 active experts, 0 .. 1316 rows per expert).  Runs the CTA-pair kernels."""
+    inp = pkg.make_inputs(num_tokens=8192, seed=0, e_local=32, device=DEV)
+    _, stats = _check_against_gpu_oracle(pkg, oracle, inp)
+    assert stats["routes"] == 8951 and stats["active_experts"] == 30
+
+
+@pytest.mark.parametrize("rank", [0, 5])
+def test_skewed_full_layer_rank_matches_oracle(rank, pkg, oracle):
+    """One rank of the 256-expert, 8-rank configuration with load imbalance: T = 4096 tokens shared by all
+    ranks, logits of 16 hot experts raised by 1.5 (chosen with seed 1), this rank's 32 experts drawn from
+    weight seed = rank, offset 32 * rank."""
+    inp = pkg.make_inputs(num_tokens=4096, seed=0, e_local=32, local_expert_offset=32 * rank, device=DEV,
+                          hot_experts=16, weight_seed=rank)
+    _, stats = _check_against_gpu_oracle(pkg, oracle, inp)
+    assert stats["routes"] > 2000
+
+
+@pytest.mark.parametrize("T,E,off,tile", [(300, 8, 0, None), (129, 4, 36, None), (1500, 4, 8, 256)])
+def test_intermediate_stages_match_oracle(T, E, off, tile, pkg, oracle, monkeypatch):
+    """Stage by stage through the workspace: the gathered activation bytes and scales are exact copies of the
+    routed tokens' rows; the two-term e4m3 SwiGLU output s * (hi + lo / 28) reproduces the oracle's f32
+    silu(X2) * X1 to ~8 bits (a single e4m3 term would be ~4: this is what the second term buys); the per-route
+    GEMM2 rows match the oracle's C W2^T."""
+    if tile is not None:
+        monkeypatch.setenv("SYFI_MOE_TOKEN_TILE", str(tile))
+    inp = pkg.make_inputs(num_tokens=T, seed=5, e_local=E, local_expert_offset=off, device=DEV)
+    _run(pkg, inp)
+    ctx = pkg.get_context(0)
+    meta, cap = ctx.debug_read("meta", torch.int32)
+    R = int(meta[1])
+    row_token, _ = ctx.debug_read("row_token", torch.int32)
+    row_token = row_token[:R].long()
+    valid = row_token >= 0
+    a_perm, _ = ctx.debug_read("a_perm", torch.uint8, max_bytes=R * 7168)
+    a_scale, _ = ctx.debug_read("a_scale", torch.float32)
+    hs = inp.hidden_states.cpu().view(torch.uint8)
+    assert torch.equal(a_perm.view(R, 7168)[valid], hs[row_token[valid]])
+    assert bool((a_perm.view(R, 7168)[~valid] == 0).all())
+    assert torch.equal(a_scale.view(56, cap)[:, :R][:, valid], inp.hidden_states_scale.cpu()[:, row_token[valid]])
+    c_hi, _ = ctx.debug_read("c_hi", torch.uint8, max_bytes=R * 2048)
+    c_lo, _ = ctx.debug_read("c_lo", torch.uint8, max_bytes=R * 2048)
+    c_scale, _ = ctx.debug_read("c_scale", torch.float32)
+    o_rows, _ = ctx.debug_read("o_rows", torch.float32, max_bytes=R * 7168 * 4)
+    c_scale = c_scale.view(16, cap)[:, :R].t().contiguous()
+    hi = c_hi.view(R, 2048).view(torch.float8_e4m3fn).float().view(R, 16, 128)
+    lo = c_lo.view(R, 2048).view(torch.float8_e4m3fn).float().view(R, 16, 128)
+    c_two = ((hi + lo / 28.0) * c_scale.unsqueeze(-1)).view(R, 2048).to(DEV)
+    c_one = (hi * c_scale.unsqueeze(-1)).view(R, 2048).to(DEV)
+    o_rows = o_rows.view(R, 7168).to(DEV)
+    counts, _ = ctx.debug_read("counts", torch.int32)
+    A = oracle.dequant_act(inp.hidden_states, inp.hidden_states_scale)
+    start, worst_two, worst_one, worst_o = 0, 0.0, 0.0, 0.0
+    for e in range(E):
+        c = int(counts[e])
+        if c:
+            tok = row_token[start:start + c].to(DEV)
+            W13 = oracle.dequant_weight(inp.gemm1_weights[e], inp.gemm1_weights_scale[e])
+            W2 = oracle.dequant_weight(inp.gemm2_weights[e], inp.gemm2_weights_scale[e])
+            G1 = A[tok] @ W13.t()
+            C = (G1[:, 2048:] / (1.0 + torch.exp(-G1[:, 2048:]))) * G1[:, :2048]
+            # per 1x128 block, relative to the block's amax (the quantity the block scale is made from)
+            amax = C.view(c, 16, 128).abs().amax(-1, keepdim=True).clamp_min(1e-30)
+            worst_two = max(worst_two, float(((c_two[start:start + c] - C).view(c, 16, 128).abs() / amax).max()))
+            worst_one = max(worst_one, float(((c_one[start:start + c] - C).view(c, 16, 128).abs() / amax).max()))
+            O = C @ W2.t()
+            worst_o = max(worst_o, float((o_rows[start:start + c] - O).abs().max() / O.abs().max()))
+        start += (c + 15) // 16 * 16
+    assert worst_two <= 2.0 ** -8, worst_two      # two terms: error below 2^-8 of the block's amax
+    assert worst_one >= 2.0 ** -6, worst_one      # one term alone is an order of magnitude coarser
+    assert worst_o <= 4e-3, worst_o
+
+
+@pytest.mark.parametrize("T,E,off,seed", [(600, 8, 16, 11), (3000, 4, 100, 12)])
+def test_every_token_tile_gives_the_same_bits(T, E, off, seed, pkg, oracle, monkeypatch):
+    """The GEMM kernels exist for token tiles of 32, 64 and 128 rows and as the CTA-pair configuration
+    (256: token-major GEMM1 on 256-row tiles, GEMM2 on 128-row tiles); the library picks by batch size, the
+    environment variable forces one.  The tile changes the work split and the operand orientation, never
+    the arithmetic of an output element (same products, same K-block order, same promotion), so all four
+    must agree bit for bit, and with the oracle within tolerance.  600 tokens over 8 experts give every
+    expert several small tiles and a ragged last one; 3000 tokens over 4 experts give the pair kernels
+    experts with more than 256 rows (several 256-row tiles, the second CTA of a pair partly filled)."""
+    inp = pkg.make_inputs(num_tokens=T, seed=seed, e_local=E, local_expert_offset=off, device=DEV)
     ref, _, _ = oracle.moe_forward(*inp.args())
     outs = []
-    for tile in (32, 64, 128):
+    for tile in (32, 64, 128, 256):
         monkeypatch.setenv("SYFI_MOE_TOKEN_TILE", str(tile))
         out, stats = _run(pkg, inp)
         ok, ostats = oracle.check_output(out, ref)
         assert ok, (tile, ostats, stats)
         outs.append(out)
-    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    for o in outs[1:]:
+        assert torch.equal(outs[0], o)
 
 
 def _swizzled_tiles(x):
