@@ -10,8 +10,11 @@ Workloads (seeded synthetic tensors with the definition's shapes and value distr
 * config 3 (default), the largest single-GPU configuration: T = 8192 tokens, the 32 local experts
   [0, 32) of 256, seed 0.  On N > 1 GPUs (launched by torchrun, one rank per GPU) the SAME layer is
   sharded by expert: rank r owns experts [32 r / N, 32 (r + 1) / N) (slices of the same seed-0
-  weights), every rank holds all T tokens, computes the f32 partial of its experts, the partials are
-  all-reduced over NCCL and rounded to bf16 once.  Total work is fixed as N grows: "strong" scaling.
+  weights), every rank holds all T tokens and computes the f32 partial of its experts; the partial rows
+  are summed over the ranks and each rank ends with the bf16 rows of its own T / N tokens (a
+  reduce-scatter by rows, fused into the layer's combine kernel over NVLink peer memory; NCCL's
+  reduce-scatter when the ranks cannot map each other).  Total work is fixed as N grows: "strong"
+  scaling.
 * config 4 (``--config 4``), the full 256-expert layer with load imbalance: T = 4096 tokens shared by
   all ranks, logits of 16 hot experts raised by 1.5, rank r owns experts [32 r, 32 r + 32) drawn from
   weight seed r; meant for N = 8 (fewer ranks compute the first 32 N experts only).
@@ -303,8 +306,8 @@ def main():
         raise SystemExit("bench.py needs a CUDA device: the MoE layer has no CPU path")
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
-    if world > 8 or (args.config == 3 and 32 % world != 0):
-        raise SystemExit("1, 2, 4 or 8 ranks")
+    if world > 8 or 32 % world != 0 or args.tokens % world != 0:
+        raise SystemExit("1, 2, 4 or 8 ranks, and a token count they divide")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     pkg = importlib.import_module(PKG)
@@ -320,6 +323,7 @@ def main():
     ctx = pkg.get_context(local_rank, T)
     out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
     peaks = measured_peaks()
+    peer_ok = False
 
     if world == 1:
         def step():
@@ -328,8 +332,19 @@ def main():
         ep = pkg.ExpertParallelMoe(inp.gemm1_weights, inp.gemm1_weights_scale, inp.gemm2_weights,
                                    inp.gemm2_weights_scale, inp.local_expert_offset, inp.routed_scaling_factor)
 
+        # every rank ends with the rows of its own T / N tokens (reduce-scatter by rows): fused into the
+        # layer's combine kernel over peer memory when the ranks can map each other, NCCL otherwise
+        peer_ok = ep.enable_peer_exchange(T // world, dev)
+        flag = torch.tensor([1 if peer_ok else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            ep._peer = None
+            peer_ok = False
+        out = torch.empty(T // world, H, dtype=torch.bfloat16, device=dev)
+
         def step():
-            ep.forward_replicated(inp.routing_logits, inp.routing_bias, inp.hidden_states, inp.hidden_states_scale, out)
+            ep.forward_replicated(inp.routing_logits, inp.routing_bias, inp.hidden_states, inp.hidden_states_scale, out,
+                                  scatter_rows=True)
 
     def barrier():
         if dist is not None:
@@ -359,7 +374,8 @@ def main():
         ref32, ridx, rw = oracle.moe_forward(*inp.args(), return_f32=True)
         if dist is not None:
             dist.all_reduce(ref32)
-        ok, ostats = oracle.check_output(out, ref32.to(torch.bfloat16))
+        mine = slice(rank * (T // world), (rank + 1) * (T // world))
+        ok, ostats = oracle.check_output(out, ref32[mine].to(torch.bfloat16))
         idx, w = ctx.last_routing(T)
         cidx, cw = oracle.route(inp.routing_logits.cpu(), inp.routing_bias.cpu(), inp.routed_scaling_factor)
         rok, rstats = oracle.check_routing(idx, w, cidx, cw)
@@ -389,7 +405,7 @@ def main():
     # ---- end to end: per-step tensors in pinned host memory
     h_in = [t.cpu().pin_memory() for t in (inp.routing_logits, inp.routing_bias, inp.hidden_states,
                                             inp.hidden_states_scale)]
-    h_out = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
+    h_out = torch.empty(out.shape[0], H, dtype=torch.bfloat16).pin_memory()
     h2d = sum(t.numel() * t.element_size() for t in h_in)
     d2h = h_out.numel() * h_out.element_size()
     if world == 1:
@@ -473,7 +489,9 @@ def main():
             "vs_baseline": None, "dtype": "f8e4m3", "data": "synthetic",
             "config": {"workload": workload_name(args.config, T), "tokens": T, "local_experts_per_rank": e_per_rank,
                        "parallelism": ("1 GPU" if world == 1 else
-                                       f"expert parallel over {world} ranks, tokens replicated, f32 partials all-reduced (NCCL)"),
+                                       f"expert parallel over {world} ranks, tokens replicated, every rank ends with its T/{world} rows: "
+                                       + ("reduce-scatter fused into the combine kernel over peer memory" if peer_ok
+                                          else "f32 partials reduce-scattered by NCCL")),
                        "routes": rows_all, "routes_rank0": rows, "active_experts_rank0": active,
                        "l2": f"inputs larger than L2: {active * 44050944 / 1e6:.0f} MB of active-expert weights per step on rank 0",
                        "layer_flops": flops_all, "layer_tflops": flops_all / (ms * 1e-3) / 1e12,

@@ -132,21 +132,50 @@ int syfi_moe_route(syfi_moe_ctx* ctx, const void* routing_logits, const void* ro
  *               no barrier.
  * Inputs are this rank's OWN token-side tensors (device pointers, shapes as in syfi_moe_forward with
  * T = tokens_per_rank) and its expert weights; output is bf16 [tokens_per_rank, 7168]: this rank's tokens
- * summed over all ranks' experts, rounded once.  Waits on other ranks are bounded (about a second);
- * syfi_moe_check then reports status 105. */
+ * summed over all ranks' experts, rounded once.
+ * Waits on other ranks are bounded: wait_limit_cycles SM clocks per wait (0 = the default, 2^35, about
+ * 17 s: a serving process may stall for seconds in an allocation or a module load; tests use short
+ * limits).  A rank whose wait runs out records status 105 and marks the step as failed for everybody:
+ * it sends a failure mark instead of rows, and every output row that depends on a failed rank is
+ * written as NaN, so a stalled peer can never turn into plausible numbers.  The status word is only read
+ * by syfi_moe_check (which synchronises): poll it at some cadence, e.g. once per model step.
+ * Call syfi_moe_ep_prepare on every rank and put a barrier of your own behind it before step 1, so that no
+ * rank allocates (and stalls) inside its first step. */
 #define SYFI_MOE_EP_MAX_RANKS 8
 typedef struct syfi_moe_ep_desc {
   int32_t world_size;
   int32_t rank;
   int64_t tokens_per_rank;
   void* region[SYFI_MOE_EP_MAX_RANKS];
+  int64_t wait_limit_cycles;
 } syfi_moe_ep_desc;
 int64_t syfi_moe_ep_region_bytes(int32_t world_size, int64_t tokens_per_rank);
+/* Allocates everything the expert-parallel entry points below need for this descriptor (workspace for
+ * world_size * tokens_per_rank tokens, the gathered-token buffers), so that the steps themselves do not
+ * allocate.  No counterpart in the reference. */
+int syfi_moe_ep_prepare(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep);
 int syfi_moe_ep_forward(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep, int64_t step, const void* routing_logits,
                         const void* routing_bias, const void* hidden_states, const void* hidden_states_scale,
                         const void* gemm1_weights, const void* gemm1_weights_scale, const void* gemm2_weights,
                         const void* gemm2_weights_scale, int32_t num_local_experts, int64_t local_expert_offset,
                         double routed_scaling_factor, void* output, void* stream);
+/* The same exchange for REPLICATED tokens (the large-prefill layout: every rank holds the same
+ * world_size * tokens_per_rank tokens and owns a slice of the experts; the reference's
+ * local_expert_offset hook, moe.cu:182-185, used as expert parallelism).  No token gather: each rank runs
+ * the layer for its experts on all tokens, and the weighted combine writes every token's f32 partial row
+ * straight into the receive slot of the rank that owns the token (rank t / tokens_per_rank) — the
+ * reduce-scatter is fused into the combine kernel; tokens without a local route send one presence word.
+ * Inputs: token-side tensors of ALL world_size * tokens_per_rank tokens (identical on every rank);
+ * output: bf16 [tokens_per_rank, 7168], the rows of this rank's tokens summed over all ranks in rank
+ * order, rounded once.  Same step / region / wait rules as syfi_moe_ep_forward; the two may share a
+ * region as long as every rank makes the same sequence of calls. */
+int syfi_moe_ep_forward_replicated(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep, int64_t step,
+                                   const void* routing_logits, const void* routing_bias, const void* hidden_states,
+                                   const void* hidden_states_scale, const void* gemm1_weights,
+                                   const void* gemm1_weights_scale, const void* gemm2_weights,
+                                   const void* gemm2_weights_scale, int32_t num_local_experts,
+                                   int64_t local_expert_offset, double routed_scaling_factor, void* output,
+                                   void* stream);
 
 /* Router for callers that cannot allocate device memory (no counterpart in the reference, which
  * allocates its workspace with cudaMalloc on first use, moe.cu:2863-2926).  Same result as

@@ -5,11 +5,11 @@ Public surface: :func:`run_moe` (the reference's entry point, same argument orde
 generator in :mod:`workloads`.
 """
 from .moe import (ABI, EpDesc, MoeContext, MoeError, get_context, library_path, load_library, release_contexts, route,
-                  run_moe, run_moe_ep, run_moe_host, ep_region_bytes, PackedWeights, prepack_weights,
+                  run_moe, run_moe_ep, run_moe_ep_replicated, ep_prepare, run_moe_host, ep_region_bytes, PackedWeights, prepack_weights,
                   run_moe_prepacked)
 from .parallel import ExpertParallelMoe, expert_slice
 from .workloads import MoeInputs, algorithmic_work, make_inputs
 
 __all__ = ["ABI", "ExpertParallelMoe", "expert_slice", "MoeContext", "MoeError", "MoeInputs", "algorithmic_work", "get_context", "library_path",
-           "load_library", "make_inputs", "release_contexts", "route", "run_moe", "run_moe_ep", "run_moe_host",
+           "load_library", "make_inputs", "release_contexts", "route", "run_moe", "run_moe_ep", "run_moe_ep_replicated", "ep_prepare", "run_moe_host",
            "EpDesc", "ep_region_bytes", "PackedWeights", "prepack_weights", "run_moe_prepacked"]

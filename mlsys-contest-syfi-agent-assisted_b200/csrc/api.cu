@@ -562,11 +562,8 @@ int64_t syfi_moe_ep_region_bytes(int32_t world_size, int64_t tokens_per_rank) {
   return (int64_t)ep_region_bytes(world_size, tokens_per_rank);
 }
 
-int syfi_moe_ep_forward(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep, int64_t step, const void* routing_logits,
-                        const void* routing_bias, const void* hidden_states, const void* hidden_states_scale,
-                        const void* gemm1_weights, const void* gemm1_weights_scale, const void* gemm2_weights,
-                        const void* gemm2_weights_scale, int32_t num_local_experts, int64_t local_expert_offset,
-                        double routed_scaling_factor, void* output, void* stream) {
+namespace {
+int validate_ep(const syfi_moe_ep_desc* ep, int64_t step) {
   if (!ep) return fail(SYFI_MOE_ERR_INVALID, "ep descriptor is null");
   const int W = ep->world_size;
   const int64_t T = ep->tokens_per_rank;
@@ -574,29 +571,60 @@ int syfi_moe_ep_forward(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep, int64_t s
   if (ep->rank < 0 || ep->rank >= W) return fail(SYFI_MOE_ERR_INVALID, "rank %d outside the world of %d", ep->rank, W);
   if (T < 1 || T * W > (1 << 24)) return fail(SYFI_MOE_ERR_INVALID, "tokens_per_rank %lld out of range", (long long)T);
   if (step < 1 || step > 0x7fffffff) return fail(SYFI_MOE_ERR_INVALID, "step must count up from 1");
+  if (ep->wait_limit_cycles < 0) return fail(SYFI_MOE_ERR_INVALID, "wait_limit_cycles must not be negative");
   for (int r = 0; r < W; ++r)
     if (!ep->region[r] || !aligned16(ep->region[r])) return fail(SYFI_MOE_ERR_INVALID, "region[%d] is null or misaligned", r);
+  return SYFI_MOE_OK;
+}
+
+// gathered token-side tensors of the sharded layout: logits [W*T, 256] f32 | hidden [W*T, 7168] e4m3 | scales [56, W*T] f32
+int ensure_ep_gather(syfi_moe_ctx* ctx, size_t need) {
+  if (need <= ctx->ep_gather_bytes) return SYFI_MOE_OK;
+  CU_TRY(cudaDeviceSynchronize());
+  if (ctx->ep_gather) cudaFree(ctx->ep_gather);
+  ctx->ep_gather = nullptr;
+  ctx->ep_gather_bytes = 0;
+  CU_TRY(cudaMalloc(&ctx->ep_gather, need));
+  ctx->ep_gather_bytes = need;
+  return SYFI_MOE_OK;
+}
+size_t up256(size_t v) { return (v + 255) / 256 * 256; }
+}  // namespace
+
+int syfi_moe_ep_prepare(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep) {
+  if (!ctx) return fail(SYFI_MOE_ERR_INVALID, "context is null");
+  int rc = validate_ep(ep, 1);
+  if (rc) return rc;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard guard(ctx->ws.device);
+  if (!guard.ok) return fail(SYFI_MOE_ERR_CUDA, "cannot select device %d", ctx->ws.device);
+  const size_t NT = (size_t)ep->tokens_per_rank * ep->world_size;
+  if ((rc = ensure_capacity(ctx, (int64_t)NT))) return rc;
+  const size_t need = up256(NT * kExpertsGlobal * 4) + up256(NT * kHidden) + up256(NT * kHBlocks * 4);
+  return ensure_ep_gather(ctx, need);
+}
+
+int syfi_moe_ep_forward(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep, int64_t step, const void* routing_logits,
+                        const void* routing_bias, const void* hidden_states, const void* hidden_states_scale,
+                        const void* gemm1_weights, const void* gemm1_weights_scale, const void* gemm2_weights,
+                        const void* gemm2_weights_scale, int32_t num_local_experts, int64_t local_expert_offset,
+                        double routed_scaling_factor, void* output, void* stream) {
+  int rc = validate_ep(ep, step);
+  if (rc) return rc;
+  const int W = ep->world_size;
+  const int64_t T = ep->tokens_per_rank;
   const void* ptrs[] = {routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
                         gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, output};
-  int rc = validate(ctx, ptrs, 9, T * W, num_local_experts, local_expert_offset, routed_scaling_factor);
+  rc = validate(ctx, ptrs, 9, T * W, num_local_experts, local_expert_offset, routed_scaling_factor);
   if (rc) return rc;
   std::lock_guard<std::mutex> lock(ctx->mu);
   DeviceGuard guard(ctx->ws.device);
   if (!guard.ok) return fail(SYFI_MOE_ERR_CUDA, "cannot select device %d", ctx->ws.device);
   if ((rc = ensure_capacity(ctx, T * W))) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // local gathered tensors: logits [W*T, 256] f32 | hidden [W*T, 7168] e4m3 | scales [56, W*T] f32
-  auto up = [](size_t v) { return (v + 255) / 256 * 256; };
   const size_t NT = (size_t)T * W;
-  const size_t o_hs = up(NT * kExpertsGlobal * 4), o_sc = o_hs + up(NT * kHidden), need = o_sc + up(NT * kHBlocks * 4);
-  if (need > ctx->ep_gather_bytes) {
-    CU_TRY(cudaDeviceSynchronize());
-    if (ctx->ep_gather) cudaFree(ctx->ep_gather);
-    ctx->ep_gather = nullptr;
-    ctx->ep_gather_bytes = 0;
-    CU_TRY(cudaMalloc(&ctx->ep_gather, need));
-    ctx->ep_gather_bytes = need;
-  }
+  const size_t o_hs = up256(NT * kExpertsGlobal * 4), o_sc = o_hs + up256(NT * kHidden), need = o_sc + up256(NT * kHBlocks * 4);
+  if ((rc = ensure_ep_gather(ctx, need))) return rc;
   char* g = static_cast<char*>(ctx->ep_gather);
   const uint32_t seq = (uint32_t)step;
   CU_TRY(launch_ep_publish_gather(*ep, seq, routing_logits, hidden_states, hidden_states_scale, g, g + o_hs, g + o_sc,
@@ -607,6 +635,36 @@ int syfi_moe_ep_forward(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep, int64_t s
   if (rc) return rc;
   CU_TRY(launch_ep_push_final(*ep, seq, ctx->ws, output, ctx->ws.ep_ticket, st));
   ctx->launches += 4;
+  return SYFI_MOE_OK;
+}
+
+int syfi_moe_ep_forward_replicated(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep, int64_t step,
+                                   const void* routing_logits, const void* routing_bias, const void* hidden_states,
+                                   const void* hidden_states_scale, const void* gemm1_weights,
+                                   const void* gemm1_weights_scale, const void* gemm2_weights,
+                                   const void* gemm2_weights_scale, int32_t num_local_experts,
+                                   int64_t local_expert_offset, double routed_scaling_factor, void* output,
+                                   void* stream) {
+  int rc = validate_ep(ep, step);
+  if (rc) return rc;
+  const int64_t NT = ep->tokens_per_rank * ep->world_size;
+  const void* ptrs[] = {routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                        gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, output};
+  rc = validate(ctx, ptrs, 9, NT, num_local_experts, local_expert_offset, routed_scaling_factor);
+  if (rc) return rc;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard guard(ctx->ws.device);
+  if (!guard.ok) return fail(SYFI_MOE_ERR_CUDA, "cannot select device %d", ctx->ws.device);
+  if ((rc = ensure_capacity(ctx, NT))) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // every rank already holds all tokens: the layer for this rank's experts, then the combine that pushes each
+  // token's partial row to the token's owner and the final sum of the owners
+  rc = run_layer(ctx, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                 gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, NT, num_local_experts, local_expert_offset,
+                 routed_scaling_factor, nullptr, 0, st);
+  if (rc) return rc;
+  CU_TRY(launch_ep_push_final(*ep, (uint32_t)step, ctx->ws, output, ctx->ws.ep_ticket, st));
+  ctx->launches += 2;
   return SYFI_MOE_OK;
 }
 
@@ -667,7 +725,8 @@ int syfi_moe_check(syfi_moe_ctx* ctx, int32_t* stats4, void* stream) {
     cudaMemsetAsync(ctx->ws.status, 0, sizeof(status), st);
     cudaMemsetAsync(ctx->ws.counts, 0, kMaxLocalExperts * sizeof(int), st);
     return fail(SYFI_MOE_ERR_DEVICE, "a kernel reported status %d (101/102/103: bounded wait expired in the TMA / MMA / "
-                "epilogue role of a grouped GEMM; 104: row or tile table overflow; 105: a peer rank's flag did not arrive)", status[0]);
+                "epilogue role of a grouped GEMM; 104: row or tile table overflow; 105: a peer rank's flag did not arrive; "
+                "106: GEMM2 waited in vain for GEMM1 to finish an expert)", status[0]);
   }
   return SYFI_MOE_OK;
 }

@@ -17,8 +17,11 @@
 //   final   : wait for all out flags, add the present slots in rank order, round to bf16 once
 // Flags carry the caller's monotonically increasing step number, buffers are double buffered by its
 // parity, so no barrier is needed between steps: a rank can only be one step ahead of a peer because
-// its own next final depends on that peer's push.  Every flag wait is bounded; on expiry the kernel
-// records status 105 and returns.
+// its own next final depends on that peer's push.  Every flag wait is bounded (the descriptor carries the
+// limit); on expiry the kernel records status 105, the rank sends failure marks instead of rows, and every
+// output row that depends on a failed rank is written as NaN.
+// With replicated tokens (every rank holds all W*T tokens, syfi_moe_ep_forward_replicated) only push and
+// final run: the reduce-scatter is the combine kernel itself.
 #include <cuda_bf16.h>
 
 #include "../../include/syfi_moe.h"
@@ -30,11 +33,13 @@ namespace syfi {
 namespace {
 
 constexpr int kMaxRanks = SYFI_MOE_EP_MAX_RANKS;
-constexpr long long kFlagWaitCycles = 1ll << 31;     // about a second
+constexpr long long kDefaultFlagWaitCycles = 1ll << 35;   // about 17 s: a serving process may stall for seconds
+constexpr uint32_t kHasRow = 1u, kHasNothing = 0u, kHasFailed = 2u;   // presence words of a (source rank, token) slot
 
 struct EpView {
   uint8_t* base[kMaxRanks];   // every rank's region, as mapped into this process
   int world, rank, T;
+  long long wait_cycles;
   size_t in_off[2], recv_off[2], has_off[2], flag_off;
 };
 
@@ -49,10 +54,10 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   return v;
 }
 // true once *flag >= seq (step numbers only grow); false after the cycle budget
-__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t seq) {
+__device__ __forceinline__ bool wait_flag(const uint32_t* flag, uint32_t seq, long long limit) {
   const long long t0 = clock64();
   while (static_cast<int>(ld_acquire_sys(flag) - seq) < 0) {
-    if (clock64() - t0 > kFlagWaitCycles) return false;
+    if (clock64() - t0 > limit) return false;
     __nanosleep(100);
   }
   return true;
@@ -99,7 +104,7 @@ ep_gather_kernel(EpView v, uint32_t seq, uint4* __restrict__ g_logits, uint4* __
   __shared__ int s_ok;
   const int src = blockIdx.y, T = v.T, W = v.world;
   if (threadIdx.x == 0) {
-    s_ok = wait_flag(in_flag(v, v.rank, src), seq) ? 1 : 0;
+    s_ok = wait_flag(in_flag(v, v.rank, src), seq, v.wait_cycles) ? 1 : 0;
     if (!s_ok) atomicExch(status, kStatusPeerTimeout);
   }
   __syncthreads();
@@ -125,10 +130,14 @@ constexpr int kVec = kHidden / (kPushThreads * 4);   // 7 float4 per thread
 
 __global__ void __launch_bounds__(kPushThreads)
 ep_combine_push_kernel(EpView v, uint32_t seq, const int* __restrict__ route_row, const float* __restrict__ topk_w,
-                       const float* __restrict__ o_rows, int row_cap, int* __restrict__ ticket) {
-  const int t = blockIdx.x;                      // gathered token index, 0 .. W*T-1
+                       const float* __restrict__ o_rows, int row_cap, int* __restrict__ ticket,
+                       const int* __restrict__ status) {
+  const int t = blockIdx.x;                      // token index over all ranks' tokens, 0 .. W*T-1
   const int owner = t / v.T, tl = t % v.T;
   const int tid = threadIdx.x;
+  // a step that already failed on this rank (a gather wait ran out: the layer worked on stale tokens; a GEMM
+  // wait ran out) sends a failure mark instead of rows, so the owners write NaN rather than plausible numbers
+  const bool failed = *reinterpret_cast<const volatile int*>(status) != 0;
   int rows[kTopK];
   float w[kTopK];
   bool any = false;
@@ -140,7 +149,7 @@ ep_combine_push_kernel(EpView v, uint32_t seq, const int* __restrict__ route_row
     any = any || rows[k] >= 0;
   }
   uint32_t* has = reinterpret_cast<uint32_t*>(v.base[owner] + v.has_off[seq & 1]) + v.rank * v.T + tl;
-  if (any) {
+  if (any && !failed) {
     float4 acc[kVec];
 #pragma unroll
     for (int i = 0; i < kVec; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -162,7 +171,7 @@ ep_combine_push_kernel(EpView v, uint32_t seq, const int* __restrict__ route_row
 #pragma unroll
     for (int i = 0; i < kVec; ++i) dst[i * kPushThreads + tid] = acc[i];
   }
-  if (tid == 0) *has = any ? 1u : 0u;
+  if (tid == 0) *has = failed ? kHasFailed : (any ? kHasRow : kHasNothing);
   __threadfence_system();
   __syncthreads();
   if (tid == 0) {
@@ -181,25 +190,32 @@ ep_final_kernel(EpView v, uint32_t seq, __nv_bfloat16* __restrict__ out, int* __
   const int tl = blockIdx.x, tid = threadIdx.x;
   if (tid == 0) {
     int ok = 1;
-    for (int q = 0; q < v.world && ok; ++q) ok = wait_flag(out_flag(v, v.rank, q), seq) ? 1 : 0;
+    for (int q = 0; q < v.world && ok; ++q) ok = wait_flag(out_flag(v, v.rank, q), seq, v.wait_cycles) ? 1 : 0;
     if (!ok) atomicExch(status, kStatusPeerTimeout);
     s_ok = ok;
   }
   __syncthreads();
-  if (!s_ok) return;
   const uint32_t* has = reinterpret_cast<const uint32_t*>(v.base[v.rank] + v.has_off[seq & 1]);
   const float4* recv = reinterpret_cast<const float4*>(v.base[v.rank] + v.recv_off[seq & 1]);
+  bool poisoned = !s_ok;
   float4 acc[kVec];
 #pragma unroll
   for (int i = 0; i < kVec; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-  for (int q = 0; q < v.world; ++q) {
-    if (__ldcg(has + q * v.T + tl) == 0) continue;
+  for (int q = 0; q < v.world && !poisoned; ++q) {
+    const uint32_t h = __ldcg(has + q * v.T + tl);
+    if (h == kHasFailed) { poisoned = true; break; }
+    if (h == kHasNothing) continue;
     const float4* src = recv + (static_cast<size_t>(q) * v.T + tl) * (kHidden / 4);
 #pragma unroll
     for (int i = 0; i < kVec; ++i) {
       const float4 x = __ldcg(src + i * kPushThreads + tid);
       acc[i].x += x.x; acc[i].y += x.y; acc[i].z += x.z; acc[i].w += x.w;
     }
+  }
+  if (poisoned) {   // a peer never answered, or told us its step failed: no number is better than a wrong one
+    const float nan = __int_as_float(0x7fc00000);
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) acc[i] = make_float4(nan, nan, nan, nan);
   }
   uint2* dst = reinterpret_cast<uint2*>(out + static_cast<size_t>(tl) * kHidden);
 #pragma unroll
@@ -219,6 +235,7 @@ EpView make_view(const syfi_moe_ep_desc& d) {
   v.world = d.world_size;
   v.rank = d.rank;
   v.T = static_cast<int>(d.tokens_per_rank);
+  v.wait_cycles = d.wait_limit_cycles > 0 ? d.wait_limit_cycles : kDefaultFlagWaitCycles;
   const size_t T = v.T, W = v.world;
   size_t off = 0;
   for (int b = 0; b < 2; ++b) { v.in_off[b] = off; off += align256(T * (kExpertsGlobal * 4 + kHidden + kHBlocks * 4)); }
@@ -256,7 +273,7 @@ cudaError_t launch_ep_push_final(const syfi_moe_ep_desc& d, uint32_t seq, const 
   const EpView v = make_view(d);
   const int tokens = d.world_size * static_cast<int>(d.tokens_per_rank);
   ep_combine_push_kernel<<<tokens, kPushThreads, 0, st>>>(v, seq, ws.route_row, ws.topk_w, ws.o_rows, ws.row_cap,
-                                                         ticket);
+                                                         ticket, ws.status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
   ep_final_kernel<<<static_cast<int>(d.tokens_per_rank), kPushThreads, 0, st>>>(

@@ -41,6 +41,8 @@ ABI = {
     "syfi_moe_route": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i32, _i64, _f64, _vp, _vp, _vp]),
     "syfi_moe_ep_region_bytes": (_i64, [_i32, _i64]),
     "syfi_moe_ep_forward": (ctypes.c_int, [_vp, _vp, _i64] + [_vp] * 8 + [_i32, _i64, _f64, _vp, _vp]),
+    "syfi_moe_ep_forward_replicated": (ctypes.c_int, [_vp, _vp, _i64] + [_vp] * 8 + [_i32, _i64, _f64, _vp, _vp]),
+    "syfi_moe_ep_prepare": (ctypes.c_int, [_vp, _vp]),
     "syfi_moe_route_noalloc": (ctypes.c_int, [_vp, _vp, _i64, _i32, _i64, _f64, _vp, _vp, _vp]),
     "syfi_moe_last_routing": (ctypes.c_int, [_vp, _i64, _vp, _vp, _vp]),
     "syfi_moe_check": (ctypes.c_int, [_vp, ctypes.POINTER(_i32), _vp]),
@@ -63,7 +65,8 @@ EP_MAX_RANKS = 8
 
 class EpDesc(ctypes.Structure):
     """Mirror of ``syfi_moe_ep_desc`` (include/syfi_moe.h)."""
-    _fields_ = [("world_size", _i32), ("rank", _i32), ("tokens_per_rank", _i64), ("region", _vp * EP_MAX_RANKS)]
+    _fields_ = [("world_size", _i32), ("rank", _i32), ("tokens_per_rank", _i64), ("region", _vp * EP_MAX_RANKS),
+                ("wait_limit_cycles", _i64)]
 
 
 def library_path() -> str:
@@ -235,7 +238,8 @@ def _validate(routing_logits, routing_bias, hidden_states, hidden_states_scale, 
     _expect(gemm1_weights_scale, "gemm1_weights_scale", torch.float32, (E, 2 * INTER // 128, HIDDEN // 128), wdev)
     _expect(gemm2_weights, "gemm2_weights", f8, (E, HIDDEN, INTER), wdev)
     _expect(gemm2_weights_scale, "gemm2_weights_scale", torch.float32, (E, HIDDEN // 128, INTER // 128), wdev)
-    _expect(output, "output", out_dtype, (T, HIDDEN), tdev)
+    if output is not None:
+        _expect(output, "output", out_dtype, (T, HIDDEN), tdev)
     return T, E, off, wdev
 
 
@@ -366,6 +370,37 @@ def run_moe_ep(desc: EpDesc, step: int, routing_logits, routing_bias, hidden_sta
         raise ValueError(f"descriptor is for {desc.tokens_per_rank} tokens per rank, got {T}")
     ctx = get_context(dev.index, T * desc.world_size)
     _check(ctx.lib.syfi_moe_ep_forward(
+        ctx.handle, ctypes.byref(desc), int(step), routing_logits.data_ptr(), routing_bias.data_ptr(),
+        hidden_states.data_ptr(), hidden_states_scale.data_ptr(), gemm1_weights.data_ptr(),
+        gemm1_weights_scale.data_ptr(), gemm2_weights.data_ptr(), gemm2_weights_scale.data_ptr(), E, off,
+        float(routed_scaling_factor), output.data_ptr(), _stream_ptr(stream, ctx.device)))
+    return output
+
+
+def ep_prepare(desc: EpDesc, device: int):
+    """Allocate everything the expert-parallel steps for ``desc`` need (see ``syfi_moe_ep_prepare``); put a
+    barrier of your own behind it on every rank before step 1."""
+    ctx = get_context(device, int(desc.tokens_per_rank) * int(desc.world_size))
+    _check(ctx.lib.syfi_moe_ep_prepare(ctx.handle, ctypes.byref(desc)))
+
+
+def run_moe_ep_replicated(desc: EpDesc, step: int, routing_logits, routing_bias, hidden_states, hidden_states_scale,
+                          gemm1_weights, gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
+                          routed_scaling_factor, output, *, stream=None):
+    """One expert-parallel step with REPLICATED tokens through peer memory (``syfi_moe_ep_forward_replicated``):
+    every rank passes all ``world_size * tokens_per_rank`` tokens and its expert slice; ``output`` receives the
+    bf16 rows of this rank's tokens [rank * tokens_per_rank, ...) summed over all ranks, rounded once."""
+    T_all = int(desc.tokens_per_rank) * int(desc.world_size)
+    if not isinstance(output, torch.Tensor) or tuple(output.shape) != (int(desc.tokens_per_rank), HIDDEN):
+        raise ValueError(f"output must have shape ({int(desc.tokens_per_rank)}, {HIDDEN})")
+    T, E, off, dev = _validate(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                               gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
+                               None, torch.bfloat16, None)
+    if T != T_all:
+        raise ValueError(f"descriptor is for {T_all} tokens in all, got {T}")
+    _expect(output, "output", torch.bfloat16, (int(desc.tokens_per_rank), HIDDEN), dev)
+    ctx = get_context(dev.index, T_all)
+    _check(ctx.lib.syfi_moe_ep_forward_replicated(
         ctx.handle, ctypes.byref(desc), int(step), routing_logits.data_ptr(), routing_bias.data_ptr(),
         hidden_states.data_ptr(), hidden_states_scale.data_ptr(), gemm1_weights.data_ptr(),
         gemm1_weights_scale.data_ptr(), gemm2_weights.data_ptr(), gemm2_weights_scale.data_ptr(), E, off,

@@ -106,8 +106,20 @@ class ExpertParallelMoe:
 
     def forward_replicated(self, logits, bias, hs, hs_scale, out_bf16=None, scatter_rows: bool = False):
         """Tokens replicated on every rank.  Returns bf16 [T, 7168] on every rank, or with
-        ``scatter_rows`` this rank's T/W rows of it (T must divide by the world size)."""
+        ``scatter_rows`` this rank's T/W rows of it (T must divide by the world size).  With
+        ``scatter_rows`` and the peer-memory path enabled for T/W tokens per rank
+        (:meth:`enable_peer_exchange`), the reduce-scatter is fused into the layer's combine kernel
+        (``syfi_moe_ep_forward_replicated``); otherwise NCCL sums the f32 partials."""
         T = logits.shape[0]
+        peer = getattr(self, "_peer", None)
+        if (scatter_rows and self.world > 1 and peer is not None and T % self.world == 0
+                and peer[2].tokens_per_rank == T // self.world):
+            from . import moe as _moe
+            if out_bf16 is None:
+                out_bf16 = torch.empty(T // self.world, hs.shape[1], dtype=torch.bfloat16, device=logits.device)
+            self._peer_step += 1
+            return _moe.run_moe_ep_replicated(peer[2], self._peer_step, logits, bias, hs, hs_scale, self.w13,
+                                              self.w13_s, self.w2, self.w2_s, self.offset, self.scaling, out_bf16)
         part = self.partial(logits, bias, hs, hs_scale)
         if self.world == 1:
             res = part
@@ -124,7 +136,7 @@ class ExpertParallelMoe:
         out_bf16.copy_(res)
         return out_bf16
 
-    def enable_peer_exchange(self, tokens_per_rank: int, device) -> bool:
+    def enable_peer_exchange(self, tokens_per_rank: int, device, wait_limit_cycles: int = 0) -> bool:
         """Set up the peer-memory path for ``forward_sharded``: a symmetric region on every rank, mapped
         into every other rank (torch's symmetric memory does the allocation and the exchange of
         mappings; the data path is this library's own kernels).  Returns False when symmetric memory is
@@ -143,8 +155,14 @@ class ExpertParallelMoe:
             torch.cuda.synchronize(device)
             desc = _moe.EpDesc()
             desc.world_size, desc.rank, desc.tokens_per_rank = self.world, self.rank, int(tokens_per_rank)
+            desc.wait_limit_cycles = int(wait_limit_cycles)      # 0: the library's serving default
             for r, ptr in enumerate(handle.buffer_ptrs):
                 desc.region[r] = ptr
+            # allocate the workspace and the gathered-token buffers now, then meet the other ranks: no rank
+            # may stall in an allocation inside its first step while its peers are already waiting for it
+            _moe.ep_prepare(desc, device.index if isinstance(device, torch.device) else torch.device(device).index)
+            torch.cuda.synchronize(device)
+            handle.barrier()
         except Exception as exc:  # no symmetric memory on this system / backend
             self._peer_error = repr(exc)
             return False

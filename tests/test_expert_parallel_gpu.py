@@ -55,16 +55,46 @@ def _worker(rank, world, port, q):
                                         mine.hidden_states_scale.to(dev), fd.gemm1_weights, fd.gemm1_weights_scale,
                                         fd.gemm2_weights, fd.gemm2_weights_scale, 0, 2.5)
         ok3, s3 = oracle.check_output(o3, ref3)
-        # the same step through the library's peer-memory exchange instead of NCCL, three steps in a row
+        # The same layouts through the library's peer-memory exchange instead of NCCL.  Six steps in a row, every
+        # step on different tokens, no host synchronisation in between, and rank 1 dawdling on the host before
+        # some steps so that the ranks run a step apart: a wrong buffer parity, an early flag or a reused receive
+        # slot would hand a rank another step's rows.  Every step must equal the NCCL path bit for bit (two
+        # ranks: the f32 sum of two partials does not depend on the order).
         ok4, s4 = True, "peer exchange unavailable"
+        steps = []
+        for i in range(6):
+            m = pkg.make_inputs(num_tokens=32, seed=100 + 10 * i + rank, e_local=1, device="cpu")
+            steps.append([t.to(dev) for t in (m.routing_logits, m.hidden_states, m.hidden_states_scale)])
+        nccl_out = [ep.forward_sharded(lg, tok[1], hs, sc).clone() for lg, hs, sc in steps]
+        rep_tok = []
+        for i in range(6):
+            m = pkg.make_inputs(num_tokens=256, seed=200 + i, e_local=1, device="cpu")
+            rep_tok.append([t.to(dev) for t in (m.routing_logits, m.hidden_states, m.hidden_states_scale)])
+        nccl_rows = [ep.forward_replicated(lg, tok[1], hs, sc, scatter_rows=True).clone() for lg, hs, sc in rep_tok]
+        torch.cuda.synchronize()
+        import time
         if ep.enable_peer_exchange(32, dev):
-            for _ in range(3):
-                o4 = ep.forward_sharded(mine.routing_logits.to(dev), tok[1], mine.hidden_states.to(dev),
-                                        mine.hidden_states_scale.to(dev))
-                torch.cuda.synchronize()
-                pkg.get_context(rank).check()
-                ok4, s4 = oracle.check_output(o4, ref3)
-                ok4 = ok4 and float((o4.float() - o3.float()).abs().max()) <= 2.0 ** -5
+            outs = [torch.empty(32, 7168, dtype=torch.bfloat16, device=dev) for _ in range(6)]
+            for i, (lg, hs, sc) in enumerate(steps):
+                if rank == 1 and i in (1, 4):
+                    time.sleep(0.05)
+                ep.forward_sharded(lg, tok[1], hs, sc, outs[i])
+            torch.cuda.synchronize()
+            pkg.get_context(rank).check()
+            ok4 = all(torch.equal(a, b) for a, b in zip(outs, nccl_out))
+            s4 = [float((a.float() - b.float()).abs().max()) for a, b in zip(outs, nccl_out)]
+        # replicated tokens: the reduce-scatter fused into the combine kernel, against NCCL's reduce-scatter
+        ep6 = pkg.ExpertParallelMoe(ep.w13, ep.w13_s, ep.w2, ep.w2_s, off, 2.5)
+        if ep6.enable_peer_exchange(256 // world, dev):
+            outs = [torch.empty(256 // world, 7168, dtype=torch.bfloat16, device=dev) for _ in range(6)]
+            for i, (lg, hs, sc) in enumerate(rep_tok):
+                if rank == 1 and i in (2, 3):
+                    time.sleep(0.05)
+                ep6.forward_replicated(lg, tok[1], hs, sc, outs[i], scatter_rows=True)
+            torch.cuda.synchronize()
+            pkg.get_context(rank).check()
+            ok4 = ok4 and all(torch.equal(a, b) for a, b in zip(outs, nccl_rows))
+            s4 = (s4, [float((a.float() - b.float()).abs().max()) for a, b in zip(outs, nccl_rows)])
         # load-imbalance configuration in miniature: skewed logits (hot experts), per-rank weights,
         # expert offset 32 * rank, replicated tokens, partial outputs summed over the ranks
         skew = pkg.make_inputs(num_tokens=192, seed=0, e_local=32, local_expert_offset=32 * rank, device=dev,

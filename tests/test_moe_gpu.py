@@ -433,8 +433,9 @@ def test_argument_validation(pkg):
 
 def test_peer_wait_runs_out_without_hanging(pkg):
     """Failure detection without a GPU fault: an expert-parallel step whose 'peer' never publishes
-    (a second local buffer stands in for rank 1).  The flag waits give up after about a second each,
-    the kernels return, the status word reports it, and the context keeps working."""
+    (a second local buffer stands in for rank 1).  The flag waits give up after their limit (set short
+    here), the kernels return, the status word reports it, the output rows are NaN rather than sums over
+    stale data, and the context keeps working."""
     import ctypes
     moe = __import__("importlib").import_module(pkg.__name__ + ".moe")
     T = 8
@@ -445,10 +446,13 @@ def test_peer_wait_runs_out_without_hanging(pkg):
     desc = pkg.EpDesc()
     desc.world_size, desc.rank, desc.tokens_per_rank = 2, 0, T
     desc.region[0], desc.region[1] = mine.data_ptr(), silent_peer.data_ptr()
+    desc.wait_limit_cycles = 1 << 27          # ~70 ms per wait instead of the serving default of many seconds
     out = torch.zeros(T, 7168, dtype=torch.bfloat16, device=DEV)
     pkg.run_moe_ep(desc, 1, *inp.args()[:8], 0, 2.5, out)
     with pytest.raises(pkg.MoeError, match="105"):
         pkg.get_context(0).check()
+    # a step whose peer never answered must not leave plausible numbers behind: every row is NaN
+    assert bool(torch.isnan(out.float()).all())
     # the context is usable afterwards
     good = torch.empty(T, 7168, dtype=torch.bfloat16, device=DEV)
     pkg.run_moe(*inp.args(), good)
