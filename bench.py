@@ -31,6 +31,9 @@ metric is quoted against T.  ``parity`` compares one step's output with the orac
 on the GPU, summed over ranks in f32) outside the timed region.  ``cpu_baseline`` times the oracle on the
 host cores on a bounded sample of the workload.
 
+``gpu_reference`` is the reference's own CUDA kernel (``moe/solution/cuda/moe.cu`` compiled unmodified for
+sm_100a into ``baseline/_ref``), timed on the same GPU and workloads by ``baseline/gpu_reference.py``.
+
 ``--impl reference`` times the CPU restatement of the definition's reference (the oracle) on the host
 cores, on a bounded sample of the same workload, and prints the same line.
 """
@@ -230,6 +233,29 @@ def run_reference_arm(args):
     return 0
 
 
+def run_gpu_reference(T: int):
+    """The reference's own sm_100a kernel (moe/solution/cuda/moe.cu, compiled unmodified) timed on this GPU
+    on the same workloads, by baseline/gpu_reference.py in a child process."""
+    import subprocess
+    lib = os.path.join(ROOT, "baseline", "_ref", "libref_moe.so")
+    if not os.path.exists(lib):
+        return {"unavailable": "baseline/_ref/libref_moe.so has not been built (the reference source was not at hand)"}
+    tokens = sorted({64, 1024, T})
+    try:
+        proc = subprocess.run([sys.executable, os.path.join(ROOT, "baseline", "gpu_reference.py"), "--tokens",
+                               ",".join(str(t) for t in tokens), "--iters", "50"], capture_output=True, text=True,
+                              timeout=240)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": "the reference kernel did not finish within 240 s"}
+    for ln in reversed(proc.stdout.strip().splitlines()):
+        if ln.startswith("{"):
+            try:
+                return json.loads(ln)
+            except ValueError:
+                break
+    return {"unavailable": "no result line", "stderr_tail": proc.stderr[-300:]}
+
+
 def time_layer(torch, step, K, barrier, dist, dev):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
@@ -294,6 +320,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
+    ap.add_argument("--no-gpu-reference", action="store_true")
     args = ap.parse_args()
     if args.tokens is None:
         args.tokens = 8192 if args.config == 3 else 4096
@@ -506,6 +533,11 @@ def main():
         line["parity"] = parity
     if decode is not None:
         line["decode"] = decode
+
+    # ---- the reference's own CUDA kernel on this GPU (compiled unmodified into baseline/_ref), as a child process
+    # with a time limit: its device-side waits are unbounded
+    if rank == 0 and world == 1 and args.config == 3 and not args.no_gpu_reference:
+        line["gpu_reference"] = run_gpu_reference(T)
 
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         arm = CpuArm(torch, oracle, inp.to("cpu"), budget_s=20.0)

@@ -217,6 +217,17 @@ int syfi_moe_check(syfi_moe_ctx* ctx, int32_t* stats4, void* stream);
 int syfi_moe_debug_read(syfi_moe_ctx* ctx, const char* name, void* dst_host, int64_t max_bytes, int64_t* bytes,
                         int32_t* row_cap);
 
+/* Test hook for the bounded device-side waits (the reference's waits spin for ever, moe.cu:1298-1305, so it
+ * has nothing to test).  Applies to the NEXT forward on this context only, then clears itself:
+ *   wait_limit_cycles  SM clocks any wait inside the GEMM kernels may take (0 = the normal limit, 2^32);
+ *   mask               1 = GEMM1's TMA producer issues nothing (its MMA / epilogue waits run out: status
+ *                      102 / 103), 2 = GEMM1 is not launched (GEMM2's wait for GEMM1's experts runs out:
+ *                      106), 4 = GEMM2 is not launched, 8 = GEMM2's TMA producer issues nothing.
+ * Nothing faults, traps or spins without limit: the roles give up, the kernel frees its tensor memory and
+ * returns, syfi_moe_check reports the status, and the context stays usable.  The output of such a call is
+ * undefined. */
+int syfi_moe_debug_fault(syfi_moe_ctx* ctx, int32_t mask, int64_t wait_limit_cycles);
+
 /* Per-kernel timing.  When enabled, every forward brackets each of its six kernels (router,
  * row lists, gather, GEMM1, GEMM2, combine — in that order) with CUDA events on the stream it is
  * enqueued on; syfi_moe_last_stage_ms() synchronises on the last event and writes the six

@@ -75,6 +75,41 @@ def build_tvm_ffi_binding(force: bool = False) -> str | None:
     return TVMFFI_LIB
 
 
+REPO_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF_GPU_LIB = os.path.join(REPO_ROOT, "baseline", "_ref", "libref_moe.so")
+
+
+def build_reference_gpu(force: bool = False) -> str | None:
+    """Compiles the reference's own ``moe/solution/cuda/moe.cu`` — unmodified, straight from where it lies —
+    for sm_100a into ``baseline/_ref/libref_moe.so`` (git-ignored; a measured baseline, never part of the
+    product, see ``baseline/gpu_reference.py``).  The reference has no build file (its harness compiles
+    the source with the tvm-ffi binding), so this is that one nvcc command.  The source is looked up in
+    ``$SYFI_MOE_REFERENCE_SOURCE`` or in a ``reference`` checkout next to this repository; returns None
+    when there is none (then an already built library is used as it is) or tvm-ffi is not installed."""
+    src = os.environ.get("SYFI_MOE_REFERENCE_SOURCE") or os.path.join(
+        os.path.dirname(REPO_ROOT), "reference", "moe", "solution", "cuda", "moe.cu")
+    if not os.path.exists(src):
+        return REF_GPU_LIB if os.path.exists(REF_GPU_LIB) else None
+    try:
+        import tvm_ffi
+    except Exception:
+        return None
+    if not force and os.path.exists(REF_GPU_LIB) and os.path.getmtime(REF_GPU_LIB) >= os.path.getmtime(src):
+        return REF_GPU_LIB
+    root = os.path.dirname(tvm_ffi.__file__)
+    os.makedirs(os.path.dirname(REF_GPU_LIB), exist_ok=True)
+    cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-w", "-Xcompiler", "-fPIC",
+           "-shared", "-I" + os.path.join(root, "include"), "-I" + os.path.join(root, "3rdparty", "dlpack", "include"),
+           src, "-o", REF_GPU_LIB, "-L" + os.path.join(root, "lib"), "-ltvm_ffi", "-lcuda",
+           "-Xlinker", "-rpath", "-Xlinker", os.path.join(root, "lib")]
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    if proc.returncode != 0:
+        sys.stderr.write(proc.stdout + proc.stderr)
+        raise RuntimeError("nvcc failed building " + REF_GPU_LIB)
+    return REF_GPU_LIB
+
+
 if __name__ == "__main__":
     print(build_library(force="--force" in sys.argv, verbose=True))
     print(build_tvm_ffi_binding(force="--force" in sys.argv))
+    print(build_reference_gpu(force="--force" in sys.argv))

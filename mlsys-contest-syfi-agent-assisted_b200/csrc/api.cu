@@ -48,6 +48,9 @@ struct syfi_moe_ctx {
   // gathered token-side tensors of the peer-memory expert-parallel path
   void* ep_gather = nullptr;
   size_t ep_gather_bytes = 0;
+  // one-shot test hook (syfi_moe_debug_fault): applies to the next forward, then clears itself
+  int fault_mask = 0;
+  long long fault_wait_limit = 0;
   // optional per-kernel timing
   bool timing = false;
   bool timing_valid = false;
@@ -330,16 +333,28 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
     CU_TRY(cudaStreamWaitEvent(st, ctx->wait_before_gather, 0));
     ctx->wait_before_gather = nullptr;
   }
-  CU_TRY(launch_gather(static_cast<const uint8_t*>(hs), static_cast<const float*>(hs_scale), T, ws, st));
+  CU_TRY(launch_gather(static_cast<const uint8_t*>(hs), static_cast<const float*>(hs_scale), T, ws, ctx->num_sms, st));
   ctx->launches += 1;
   STAGE_MARK(3);
-  if (pair) CU_TRY(launch_pair_gemm1(ctx->p1, static_cast<const float*>(w13_scale), e_local, ws, grid, st));
-  else CU_TRY(launch_gemm1(g1, static_cast<const float*>(w13_scale), e_local, ws, grid, st));
-  ctx->launches += 1;
+  // test hook: short wait limit and roles / kernels left out for this one call (see syfi_moe_debug_fault)
+  const int fault = ctx->fault_mask;
+  const long long wl = ctx->fault_wait_limit > 0 ? ctx->fault_wait_limit : (1ll << 32);
+  ctx->fault_mask = 0;
+  ctx->fault_wait_limit = 0;
+  g1.wait_limit = g2.wait_limit = ctx->p1.wait_limit = ctx->p2.wait_limit = wl;
+  g1.silent_producer = ctx->p1.silent_producer = (fault & 1) ? 1 : 0;
+  g2.silent_producer = ctx->p2.silent_producer = (fault & 8) ? 1 : 0;
+  if (!(fault & 2)) {
+    if (pair) CU_TRY(launch_pair_gemm1(ctx->p1, static_cast<const float*>(w13_scale), e_local, ws, grid, st));
+    else CU_TRY(launch_gemm1(g1, static_cast<const float*>(w13_scale), e_local, ws, grid, st));
+    ctx->launches += 1;
+  }
   STAGE_MARK(4);
-  if (pair) CU_TRY(launch_pair_gemm2(ctx->p2, static_cast<const float*>(w2_scale), e_local, ws, grid, st));
-  else CU_TRY(launch_gemm2(g2, static_cast<const float*>(w2_scale), e_local, ws, grid, st));
-  ctx->launches += 1;
+  if (!(fault & 4)) {
+    if (pair) CU_TRY(launch_pair_gemm2(ctx->p2, static_cast<const float*>(w2_scale), e_local, ws, grid, st));
+    else CU_TRY(launch_gemm2(g2, static_cast<const float*>(w2_scale), e_local, ws, grid, st));
+    ctx->launches += 1;
+  }
   STAGE_MARK(5);
   if (out != nullptr) {   // the expert-parallel path combines straight into the owners' memory instead
     CU_TRY(launch_combine(T, ws, out, out_is_f32, st));
@@ -455,7 +470,7 @@ int syfi_moe_prepack_weights(syfi_moe_ctx* ctx, const void* gemm1_weights, const
   if (!guard.ok) return fail(SYFI_MOE_ERR_CUDA, "cannot select device %d", ctx->ws.device);
   CU_TRY(launch_prepack(static_cast<const uint8_t*>(gemm1_weights), static_cast<const uint8_t*>(gemm2_weights),
                         num_local_experts, static_cast<uint8_t*>(gemm1_packed), static_cast<uint8_t*>(gemm2_packed),
-                        static_cast<cudaStream_t>(stream)));
+                        ctx->num_sms, static_cast<cudaStream_t>(stream)));
   return SYFI_MOE_OK;
 }
 
@@ -760,6 +775,16 @@ int syfi_moe_debug_read(syfi_moe_ctx* ctx, const char* name, void* dst_host, int
     }
   }
   return fail(SYFI_MOE_ERR_INVALID, "unknown workspace buffer '%s'", name);
+}
+
+int syfi_moe_debug_fault(syfi_moe_ctx* ctx, int32_t mask, int64_t wait_limit_cycles) {
+  if (!ctx) return fail(SYFI_MOE_ERR_INVALID, "context is null");
+  if (mask < 0 || mask > 15) return fail(SYFI_MOE_ERR_INVALID, "mask must be a combination of 1, 2, 4 and 8");
+  if (wait_limit_cycles < 0) return fail(SYFI_MOE_ERR_INVALID, "wait_limit_cycles must not be negative");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  ctx->fault_mask = mask;
+  ctx->fault_wait_limit = wait_limit_cycles;
+  return SYFI_MOE_OK;
 }
 
 int syfi_moe_set_stage_timing(syfi_moe_ctx* ctx, int32_t enable) {

@@ -104,6 +104,8 @@ struct GemmArgs {
   int* status;
   long long* trace;         // [3][4096] timeline of CTA 0 when built with SYFI_TRACE, else unused
   long long* trace_cta;     // [grid][5] per-CTA start/end (globaltimer, clock64) and SM id, SYFI_TRACE only
+  long long wait_limit;     // SM clocks a wait may take before the CTA gives up (tests make it short)
+  int silent_producer;      // test hook: the TMA producer issues nothing, so that the other roles' waits run out
 };
 
 // Optional timeline trace of CTA 0 (compile with -DSYFI_TRACE): role r appends (tag, clock) pairs.
@@ -265,7 +267,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (one thread)
-    if (lane == 0) {
+    if (lane == 0 && !p.silent_producer) {
       // a weight tile is re-read by the other token tiles of its expert (from L2) only when the
       // expert has several tiles; with a single tile per expert it is streamed exactly once
       const uint64_t pol_w = s_meta[0] > s_meta[1] ? l2_policy_evict_last() : l2_policy_evict_first();
@@ -292,7 +294,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             const long long t0 = clock64();
             while (*reinterpret_cast<volatile int*>(s_done) <= static_cast<int>(n_items)) {
               if (*s_abort != 0) { alive = false; break; }
-              if (clock64() - t0 > (1ll << 32)) { *s_abort = kStatusDependencyTimeout; alive = false; break; }
+              if (clock64() - t0 > p.wait_limit) { *s_abort = kStatusDependencyTimeout; alive = false; break; }
             }
             if (!alive) break;
           }
@@ -300,7 +302,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           // scales of the item: [16 K blocks x NT rows] activation scales through a tensor map and the
           // 16 weight scales as a 64-byte bulk copy, into the buffer the epilogue released three items ago
           const uint32_t sb = n_items % 3u, sp = (n_items / 3u) & 1u;
-          if (!mbar_wait_bounded(&sempty[sb], sp ^ 1u, s_abort, kStatusWaitTimeoutProducer)) { alive = false; break; }
+          if (!mbar_wait_bounded(&sempty[sb], sp ^ 1u, s_abort, kStatusWaitTimeoutProducer, p.wait_limit)) { alive = false; break; }
           float* d_act = s_scales + sb * kScaleStride;
           mbar_arrive_expect_tx(&sfull[sb], (KB * NT + KB) * 4);
           tma_load_2d(d_act, &tm_sc, &sfull[sb], im.row_start, 0, pol_b);
@@ -309,7 +311,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           ++n_items;
         }
         for (int step = 0; step < STEPS; ++step) {
-          if (!mbar_wait_bounded(&empty[g], ph ^ 1u, s_abort, kStatusWaitTimeoutProducer)) { alive = false; break; }
+          if (!mbar_wait_bounded(&empty[g], ph ^ 1u, s_abort, kStatusWaitTimeoutProducer, p.wait_limit)) { alive = false; break; }
           TRACE(0, step);
           mbar_arrive_expect_tx(&full[g], group_tx);
           // The boxes that continue each other along K (same rows, next 128 bytes) are issued back to
@@ -365,11 +367,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         // instead of one per term; mode 1 needs two because up and gate are different A tiles.
         const uint32_t idesc = umma_idesc_e4m3_m128(MODE == 1 ? static_cast<uint32_t>(im.n) : 2u * NT);
         for (int step = 0; step < STEPS; ++step) {
-          if (!mbar_wait_bounded(&full[g], ph, s_abort, kStatusWaitTimeoutMma)) { alive = false; break; }
+          if (!mbar_wait_bounded(&full[g], ph, s_abort, kStatusWaitTimeoutMma, p.wait_limit)) { alive = false; break; }
           TRACE(1, step);
 #pragma unroll
           for (int tk = 0; tk < KPS / TKPS && alive; ++tk) {
-            if (!mbar_wait_bounded(&tempty[pr], pph ^ 1u, s_abort, kStatusWaitTimeoutMma)) { alive = false; break; }
+            if (!mbar_wait_bounded(&tempty[pr], pph ^ 1u, s_abort, kStatusWaitTimeoutMma, p.wait_limit)) { alive = false; break; }
             tc_fence_after();
 #pragma unroll
             for (int k2 = 0; k2 < TKPS; ++k2) {
@@ -440,7 +442,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           bool seen = true;
           while (ld_acquire_gpu(p.ready + im.expert) < need) {
             if (*s_abort != 0) { seen = false; break; }
-            if (clock64() - t0 > (1ll << 31)) { *s_abort = kStatusDependencyTimeout; seen = false; break; }
+            if (clock64() - t0 > (p.wait_limit >> 1)) { *s_abort = kStatusDependencyTimeout; seen = false; break; }   // half the other roles' limit: this wait reports first
             __nanosleep(100);
           }
           if (!seen) break;
@@ -511,7 +513,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         // rows' scales and are never read.
         s_act = s_scales + sbuf * kScaleStride;
         s_ws = s_act + KB * NT;
-        if (ok && !mbar_wait_bounded(&sfull[sbuf], (sph >> sbuf) & 1u, s_abort, kStatusWaitTimeoutEpilogue)) ok = false;
+        if (ok && !mbar_wait_bounded(&sfull[sbuf], (sph >> sbuf) & 1u, s_abort, kStatusWaitTimeoutEpilogue, p.wait_limit)) ok = false;
         sph ^= 1u << sbuf;
       }
       if (et == 0) TRACE(2, 1001);
@@ -551,7 +553,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         }
       };
       for (int ts = 0; ts < STEPS * (KPS / TKPS) && ok; ++ts) {
-        if (!mbar_wait_bounded(&tfull[pr], pph, s_abort, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
+        if (!mbar_wait_bounded(&tfull[pr], pph, s_abort, kStatusWaitTimeoutEpilogue, p.wait_limit)) { ok = false; break; }
         tc_fence_after();
         if (et == 0) TRACE(2, ts);
 #pragma unroll
@@ -763,7 +765,7 @@ cudaError_t gemm_set_attributes() {
 cudaError_t launch_gemm1(const GemmLaunch& g, const float* w13_scale, int e_local, const Workspace& ws, int num_sms,
                          cudaStream_t st) {
   GemmArgs a{g.w_packed, ws.work, ws.meta, ws.a_scale, w13_scale, ws.c_hi, ws.c_lo, ws.c_scale, nullptr, ws.row_cap, e_local,
-             ws.ready, ws.status, ws.trace, ws.trace + 6 * 4096};
+             ws.ready, ws.status, ws.trace, ws.trace + 6 * 4096, g.wait_limit, g.silent_producer};
   if (g.token_tile == 128) return launch_gemm<1, 128>(g, a, num_sms, st);
   return g.token_tile == 32 ? launch_gemm<1, 32>(g, a, num_sms, st) : launch_gemm<1, 64>(g, a, num_sms, st);
 }
@@ -771,7 +773,7 @@ cudaError_t launch_gemm1(const GemmLaunch& g, const float* w13_scale, int e_loca
 cudaError_t launch_gemm2(const GemmLaunch& g, const float* w2_scale, int e_local, const Workspace& ws, int num_sms,
                          cudaStream_t st) {
   GemmArgs a{g.w_packed, ws.work, ws.meta, ws.c_scale, w2_scale, nullptr, nullptr, nullptr, ws.o_rows, ws.row_cap, e_local,
-             ws.ready, ws.status, ws.trace + 3 * 4096, ws.trace + 7 * 4096};
+             ws.ready, ws.status, ws.trace + 3 * 4096, ws.trace + 7 * 4096, g.wait_limit, g.silent_producer};
   if (g.token_tile == 128) return launch_gemm<2, 128>(g, a, num_sms, st);
   return g.token_tile == 32 ? launch_gemm<2, 32>(g, a, num_sms, st) : launch_gemm<2, 64>(g, a, num_sms, st);
 }

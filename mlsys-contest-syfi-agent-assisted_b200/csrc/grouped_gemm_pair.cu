@@ -55,7 +55,6 @@ constexpr int kEpiThreads = 32 * kEpiWarps;
 constexpr int kPairThreads = 128 + kEpiThreads;
 constexpr int kMaxSlots = 4;
 constexpr int kPairTmemCols = 512;
-constexpr long long kWaitLimit = 1ll << 31;  // cycles before a wait gives up (about a second)
 
 template <int MODE> struct PairCfg {
   static constexpr int kKBlocks = MODE == 1 ? kHBlocks : kIBlocks;              // 56 / 16
@@ -96,6 +95,8 @@ struct PairArgs {
   int* ready;               // [32] GEMM1 (CTA, item) completions per expert: mode 1 increments, mode 2 waits
   int* status;
   long long* stats;         // [grid][16] cycle counters per CTA (only written by SYFI_PAIR_STATS builds)
+  long long wait_limit;     // SM clocks a wait may take before the CTA gives up (tests make it short)
+  int silent_producer;      // test hook: the TMA producer issues nothing, so that the other roles' waits run out
 };
 
 // Optional per-CTA cycle accounting (compile with -DSYFI_PAIR_STATS): where each role spends its time.
@@ -275,7 +276,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
       const uint32_t idesc = umma_idesc_e4m3_m256(MODE == 1 ? 256u / H : 2u * im.n);
       for (int kb = static_cast<int>(par); kb < KB; kb += kIssuers) {
         ST_BEGIN();
-        if (!mbar_wait_bounded_tell(&full[g], ph, s_abort, peer_abort, kStatusWaitTimeoutMma, kWaitLimit)) { alive = false; break; }
+        if (!mbar_wait_bounded_tell(&full[g], ph, s_abort, peer_abort, kStatusWaitTimeoutMma, p.wait_limit)) { alive = false; break; }
         ST_END(0);
         const uint32_t sb = smem_u32(smem + g * kStageBytes);
         const uint64_t a0 = umma_smem_desc_sw128(sb);
@@ -283,7 +284,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         for (int h = 0; h < H; ++h) {
           const uint32_t sl = slot + h;
           ST_BEGIN();
-          if (!mbar_wait_bounded_tell(&tempty[sl], sph ^ 1u, s_abort, peer_abort, kStatusWaitTimeoutMma, kWaitLimit)) { alive = false; break; }
+          if (!mbar_wait_bounded_tell(&tempty[sl], sph ^ 1u, s_abort, peer_abort, kStatusWaitTimeoutMma, p.wait_limit)) { alive = false; break; }
           ST_END(1);
           if (MODE == 1 && par == 0) TR(0, 1);       // operands and slot are there
           tc_fence_after();
@@ -319,7 +320,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   if (warp < 4) {
     if (warp == 0) {
       // ------------------------------------------------------------ TMA producer (one thread per CTA)
-      if (lane == 0) {
+      if (lane == 0 && !p.silent_producer) {
         const uint64_t pol_w = s_meta[0] > s_meta[1] ? l2_policy_evict_last() : l2_policy_evict_first();
         const uint64_t pol_b = l2_policy_evict_last();
         uint32_t full0[G];                     // the first CTA's full barriers as cluster addresses
@@ -364,7 +365,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
             // epilogue released two items ago
             const int par = i & 1;
             if (!mbar_wait_bounded_tell(&wempty[par], ((wp >> par) & 1u) ^ 1u, s_abort, peer_abort,
-                                        kStatusWaitTimeoutProducer, kWaitLimit)) { alive = false; break; }
+                                        kStatusWaitTimeoutProducer, p.wait_limit)) { alive = false; break; }
             wp ^= 1u << par;
             mbar_arrive_expect_tx(&wfull[par], 2u * kHBlocks * 4u);
             bulk_load(s_ws + par * 128, p.w_scale + (static_cast<size_t>(im.expert) * 32 + im.ft) * kHBlocks,
@@ -381,7 +382,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
               const long long t0 = clock64();
               while (*reinterpret_cast<volatile int*>(s_done) <= static_cast<int>(n_items)) {
                 if (*s_abort != 0) { alive = false; break; }
-                if (clock64() - t0 > kWaitLimit) {
+                if (clock64() - t0 > p.wait_limit) {
                   *s_abort = kStatusDependencyTimeout;
                   st_cluster_u32(peer_abort, kStatusDependencyTimeout);
                   alive = false;
@@ -396,7 +397,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
           for (int kb = 0; kb < KB; kb += 2) {
             ST_BEGIN();
             if (!mbar_wait_bounded_tell(&empty[g >> 1], ph ^ 1u, s_abort, peer_abort, kStatusWaitTimeoutProducer,
-                                        kWaitLimit)) { alive = false; break; }
+                                        p.wait_limit)) { alive = false; break; }
             ST_END(0);
 #ifdef PAIR_NO_LOAD
             if (rank == 0) { mbar_arrive(&full[g]); mbar_arrive(&full[g + 1]); }
@@ -467,7 +468,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
           if (*reinterpret_cast<volatile int*>(s_done) <= static_cast<int>(n_items)) {
             const long long t0 = clock64();
             while (*reinterpret_cast<volatile int*>(s_done) <= static_cast<int>(n_items)) {
-              if (*s_abort != 0 || clock64() - t0 > kWaitLimit) { alive = false; break; }
+              if (*s_abort != 0 || clock64() - t0 > p.wait_limit) { alive = false; break; }
             }
           }
           alive = __all_sync(0xffffffffu, alive);
@@ -489,7 +490,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
 #pragma unroll
             for (int k = 0; k < kBatch; ++k) {
               const float ws = __shfl_sync(0xffffffffu, ws_a, kb0 + k);
-              bool ok = mbar_wait_bounded_tell(&sempty[s], sp ^ 1u, s_abort, peer_abort, kStatusWaitTimeoutProducer, kWaitLimit);
+              bool ok = mbar_wait_bounded_tell(&sempty[s], sp ^ 1u, s_abort, peer_abort, kStatusWaitTimeoutProducer, p.wait_limit);
               ok = __all_sync(0xffffffffu, ok);
               if (!ok) { alive = false; break; }
               *reinterpret_cast<float4*>(s_scale + s * SE + col) =
@@ -533,7 +534,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
             bool seen = true;
             while (ld_acquire_gpu(p.ready + im.expert) < need) {
               if (*s_abort != 0) { seen = false; break; }
-              if (clock64() - t0 > kWaitLimit) {
+              if (clock64() - t0 > (p.wait_limit >> 1)) {   // half the other roles' limit: this wait reports first
                 *s_abort = kStatusDependencyTimeout;
                 st_cluster_u32(peer_abort, kStatusDependencyTimeout);
                 seen = false;
@@ -589,7 +590,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         const int par = i & 1;
         const float* ws = s_ws + par * 128;
         if (ok && !mbar_wait_bounded_tell(&wfull[par], (wp >> par) & 1u, s_abort, peer_abort,
-                                          kStatusWaitTimeoutEpilogue, kWaitLimit)) ok = false;
+                                          kStatusWaitTimeoutEpilogue, p.wait_limit)) ok = false;
         wp ^= 1u << par;
         float up[32], gt[32];
 #pragma unroll
@@ -608,7 +609,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
 #pragma unroll
           for (int h = 0; h < H; ++h) {
             ST_BEGIN();
-            if (!mbar_wait_bounded_tell(&tfull[sl], sph, s_abort, peer_abort, kStatusWaitTimeoutEpilogue, kWaitLimit)) { ok = false; break; }
+            if (!mbar_wait_bounded_tell(&tfull[sl], sph, s_abort, peer_abort, kStatusWaitTimeoutEpilogue, p.wait_limit)) { ok = false; break; }
             ST_END(0);
             if (warp == 4 && lane == 0) TR(1, 1);     // accumulator complete
             tc_fence_after();
@@ -760,10 +761,10 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         for (int j = 0; j < CN / 2; ++j) acc[j] = 0ull;
         for (int kb = 0; kb < KB && ok; ++kb) {
           ST_BEGIN();
-          if (!mbar_wait_bounded_tell(&tfull[sl], sph, s_abort, peer_abort, kStatusWaitTimeoutEpilogue, kWaitLimit)) { ok = false; break; }
+          if (!mbar_wait_bounded_tell(&tfull[sl], sph, s_abort, peer_abort, kStatusWaitTimeoutEpilogue, p.wait_limit)) { ok = false; break; }
           ST_END(0);
           tc_fence_after();
-          if (!mbar_wait_bounded_tell(&sfull[s], sp, s_abort, peer_abort, kStatusWaitTimeoutEpilogue, kWaitLimit)) { ok = false; break; }
+          if (!mbar_wait_bounded_tell(&sfull[s], sp, s_abort, peer_abort, kStatusWaitTimeoutEpilogue, p.wait_limit)) { ok = false; break; }
 #ifdef SYFI_PAIR_STATS
           const long long st_p0 = clock64();
 #endif
@@ -856,14 +857,14 @@ cudaError_t pair_gemm_set_attributes() {
 cudaError_t launch_pair_gemm1(const PairGemmLaunch& g, const float* w13_scale, int e_local, const Workspace& ws,
                               int num_sms, cudaStream_t st) {
   PairArgs a{ws.work, ws.meta, ws.a_scale, w13_scale, ws.c_hi, ws.c_lo, ws.c_scale, nullptr, ws.row_cap, e_local,
-             ws.ready, ws.status, ws.trace};
+             ws.ready, ws.status, ws.trace, g.wait_limit, g.silent_producer};
   return launch_pair<1>(g, a, num_sms, st);
 }
 
 cudaError_t launch_pair_gemm2(const PairGemmLaunch& g, const float* w2_scale, int e_local, const Workspace& ws,
                               int num_sms, cudaStream_t st) {
   PairArgs a{ws.work, ws.meta, ws.c_scale, w2_scale, nullptr, nullptr, nullptr, ws.o_rows, ws.row_cap, e_local,
-             ws.ready, ws.status, ws.trace + 4096};
+             ws.ready, ws.status, ws.trace + 4096, g.wait_limit, g.silent_producer};
   return launch_pair<2>(g, a, num_sms, st);
 }
 

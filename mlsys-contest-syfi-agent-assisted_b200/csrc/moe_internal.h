@@ -89,6 +89,8 @@ struct GemmLaunch {
   CUtensorMap tm_sc;   // GEMM2: c_scale as f32 [16, row_cap], box 16 x token_tile (one load per work item)
   const uint8_t* w_packed = nullptr;   // pre-packed weights (tm_w unused) or nullptr
   int token_tile;      // 32, 64 or 128: token rows per work item, must match the row-list kernel's
+  long long wait_limit = 1ll << 32;   // SM clocks a device-side wait may take (about two seconds)
+  int silent_producer = 0;            // test hook, see syfi_moe_debug_fault
 };
 
 // Tensor maps of the CTA-pair GEMM kernels (grouped_gemm_pair.cu): token-side operands use 32-row boxes.
@@ -98,6 +100,8 @@ struct PairGemmLaunch {
   CUtensorMap tm_b1;   // GEMM2: c_lo (unused by GEMM1)
   CUtensorMap tm_b0w;  // the same tensors with 128-row boxes (tiles of more than 64 rows: one load instead of four)
   CUtensorMap tm_b1w;
+  long long wait_limit = 1ll << 32;   // SM clocks a device-side wait may take (about two seconds)
+  int silent_producer = 0;            // test hook, see syfi_moe_debug_fault
 };
 
 // Programmatic dependent launch: the kernel may be scheduled while its predecessor in the stream is
@@ -125,7 +129,7 @@ cudaError_t launch_router(const float* logits, const void* bias_bf16, int T, int
                           float scaling, const Workspace& ws, bool counters_are_zero, cudaStream_t st);
 cudaError_t launch_build_rows(int T, int e_local, int expert_offset, int token_tile, const Workspace& ws,
                               cudaStream_t st);
-cudaError_t launch_gather(const uint8_t* hidden, const float* hidden_scale, int T, const Workspace& ws,
+cudaError_t launch_gather(const uint8_t* hidden, const float* hidden_scale, int T, const Workspace& ws, int num_sms,
                           cudaStream_t st);
 cudaError_t launch_gemm1(const GemmLaunch& g, const float* w13_scale, int e_local, const Workspace& ws, int num_sms,
                          cudaStream_t st);
@@ -142,7 +146,7 @@ cudaError_t launch_pair_gemm2(const PairGemmLaunch& g, const float* w2_scale, in
 // block) one 16 KB tile holding the rows' 128 bytes with the 128-byte shared-memory swizzle already applied;
 // GEMM1's up and gate tiles of the same features interleave per K block.
 cudaError_t launch_prepack(const uint8_t* w13, const uint8_t* w2, int e_local, uint8_t* w13_packed,
-                           uint8_t* w2_packed, cudaStream_t st);
+                           uint8_t* w2_packed, int num_sms, cudaStream_t st);
 cudaError_t launch_combine(int T, const Workspace& ws, void* out, int out_is_f32, cudaStream_t st);
 cudaError_t gemm_set_attributes();
 

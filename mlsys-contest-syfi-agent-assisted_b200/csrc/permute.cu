@@ -153,10 +153,10 @@ cudaError_t launch_build_rows(int T, int e_local, int expert_offset, int token_t
                           ws.row_cap, token_tile, ws.status, ws.ready, ws.counts_last);
 }
 
-cudaError_t launch_gather(const uint8_t* hidden, const float* hidden_scale, int T, const Workspace& ws,
+cudaError_t launch_gather(const uint8_t* hidden, const float* hidden_scale, int T, const Workspace& ws, int num_sms,
                           cudaStream_t st) {
   const int max_rows = 8 * T + kRowPad * kMaxLocalExperts;
-  const int grid = max_rows < 148 * 8 ? max_rows : 148 * 8;
+  const int grid = max_rows < num_sms * 8 ? max_rows : num_sms * 8;
   return launch_dependent(gather_rows_kernel, dim3(grid), dim3(kGatherThreads), 0, st, hidden, hidden_scale, T,
                           ws.row_token, ws.meta, ws.a_perm, ws.a_scale, ws.row_cap, ws.counts);
 }

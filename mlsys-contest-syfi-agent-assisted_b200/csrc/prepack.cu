@@ -49,10 +49,10 @@ prepack_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, long long
 }  // namespace
 
 cudaError_t launch_prepack(const uint8_t* w13, const uint8_t* w2, int e_local, uint8_t* w13_packed,
-                           uint8_t* w2_packed, cudaStream_t st) {
+                           uint8_t* w2_packed, int num_sms, cudaStream_t st) {
   const long long c13 = static_cast<long long>(e_local) * 2 * kInter * (kHidden / 16);
   const long long c2 = static_cast<long long>(e_local) * kHidden * (kInter / 16);
-  const int grid = 148 * 16;
+  const int grid = num_sms * 16;
   prepack_kernel<2 * kInter, kHidden, true><<<grid, kPackThreads, 0, st>>>(
       reinterpret_cast<const uint4*>(w13), reinterpret_cast<uint4*>(w13_packed), c13);
   prepack_kernel<kHidden, kInter, false><<<grid, kPackThreads, 0, st>>>(

@@ -478,3 +478,60 @@ def test_tvm_ffi_entry_point(pkg, oracle):
     ref, _, _ = oracle.moe_forward(*inp.to("cpu").args())
     ok, stats = oracle.check_output(out, ref)
     assert ok, stats
+
+
+def test_tvm_ffi_entry_point_rejects_mismatched_tensors(pkg):
+    """The symbol the reference's harness loads validates dtype, rank, every dimension, device and
+    contiguity of all nine tensors (the reference checks nothing, moe.cu:3045-3053): a hidden-state tensor one
+    row short would make the gather read out of bounds, so it must raise instead, and name the argument."""
+    tvm_ffi = pytest.importorskip("tvm_ffi")
+    build = __import__("importlib").import_module(pkg.__name__ + ".build")
+    pkg.load_library()
+    mod = tvm_ffi.load_module(build.build_tvm_ffi_binding())
+    T = 24
+    inp = pkg.make_inputs(num_tokens=T, seed=29, e_local=4, device=DEV)
+    out = torch.zeros(T, 7168, dtype=torch.bfloat16, device=DEV)
+    u8 = lambda t: t.view(torch.uint8)
+    good = [inp.routing_logits, inp.routing_bias, u8(inp.hidden_states), inp.hidden_states_scale,
+            u8(inp.gemm1_weights), inp.gemm1_weights_scale, u8(inp.gemm2_weights), inp.gemm2_weights_scale, 0, 2.5, out]
+
+    def expect_error(pos, value, word):
+        args = list(good)
+        args[pos] = value
+        with pytest.raises(Exception, match=word):
+            mod.run_moe(*args)
+
+    expect_error(2, u8(inp.hidden_states)[:T - 1], "hidden_states")                 # one row short
+    expect_error(3, inp.hidden_states_scale[:, :T - 1].contiguous(), "hidden_states_scale")
+    expect_error(0, inp.routing_logits.double(), "routing_logits")                  # wrong dtype
+    expect_error(3, inp.hidden_states_scale.t().contiguous().t(), "contiguous")     # right shape, wrong strides
+    expect_error(5, inp.gemm1_weights_scale[:3].contiguous(), "gemm1_weights_scale")  # expert count mismatch
+    expect_error(10, out[:T - 1], "output")
+    expect_error(8, 254, "outside")                                                 # expert range
+    mod.run_moe(*good)                                                              # still works afterwards
+    torch.cuda.synchronize()
+    assert bool(torch.isfinite(out.float()).all())
+
+
+@pytest.mark.parametrize("T,E,tile", [(200, 8, None), (700, 4, 256)])
+@pytest.mark.parametrize("mask,expected", [(1 | 4, {102, 103}), (2, {106}), (8, {102, 103})])
+def test_bounded_waits_run_out_and_the_context_recovers(T, E, tile, mask, expected, pkg, monkeypatch):
+    """Failure detection without a GPU fault: one forward is made with a short wait limit (2^22 clocks, about
+    two milliseconds) and a role or kernel left out, so that a bounded wait inside the GEMM kernels runs
+    out — a silent TMA producer starves the MMA and epilogue roles (status 102 / 103), a GEMM1 that never ran
+    starves GEMM2's wait for its experts (106).  The roles give up, the kernels free tensor memory and return,
+    the status word names the wait, and the next normal call reproduces the earlier result bit for bit.
+    Both kernel families: the single-CTA GEMMs and (tile 256) the CTA-pair GEMMs."""
+    if tile is not None:
+        monkeypatch.setenv("SYFI_MOE_TOKEN_TILE", str(tile))
+    inp = pkg.make_inputs(num_tokens=T, seed=41, e_local=E, device=DEV)
+    before, _ = _run(pkg, inp)
+    ctx = pkg.get_context(0)
+    ctx.debug_fault(mask, 1 << 22)
+    junk = torch.empty_like(before)
+    pkg.run_moe(*inp.args(), junk)
+    with pytest.raises(pkg.MoeError) as err:
+        ctx.check()
+    assert any(f"status {c}" in str(err.value) for c in expected), str(err.value)
+    after, _ = _run(pkg, inp)                    # the hook was one-shot; the context works as before
+    assert torch.equal(before, after)

@@ -70,3 +70,30 @@ def test_rejects_batches_beyond_its_fixed_scratch(pkg):
     assert rc == 0, lib.syfi_moe_last_error()
     torch.cuda.synchronize()
     assert int(idx.min()) >= 0 and bool(torch.isfinite(w).all())
+
+
+def test_warmed_calls_leave_device_memory_untouched(pkg):
+    """The point of the entry point: once the first call on the device has looked up the scratch array, a call
+    allocates nothing — the free device memory reported by the driver is the same before and after two calls
+    (torch's caching allocator is kept out of the picture: the output tensors exist before the measurement)."""
+    torch.cuda.set_device(0)
+    lib = pkg.load_library()
+    T = 257
+    inp = pkg.make_inputs(num_tokens=T, seed=23, e_local=1, device="cpu")
+    logits, bias = inp.routing_logits.to(DEV), inp.routing_bias.to(DEV)
+    idx = torch.empty(T, 8, dtype=torch.int32, device=DEV)
+    w = torch.empty(T, 8, dtype=torch.float32, device=DEV)
+    stream = torch.cuda.current_stream(logits.device).cuda_stream
+
+    def call():
+        return lib.syfi_moe_route_noalloc(logits.data_ptr(), bias.data_ptr(), T, 32, 0, 2.5, idx.data_ptr(),
+                                          w.data_ptr(), stream)
+    assert call() == 0, lib.syfi_moe_last_error()        # first call: set-up
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info(0)
+    assert call() == 0 and call() == 0
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info(0)
+    assert free_after == free_before
+    ref_idx, ref_w = pkg.route(logits, bias, 0, 2.5)
+    assert torch.equal(idx, ref_idx) and torch.equal(w.view(torch.int32), ref_w.view(torch.int32))
