@@ -41,6 +41,16 @@ enum {
  * ensure_singletons / ensure_per_token / ensure_schedule (moe.cu:2832-2926). */
 int syfi_moe_create(int device, int64_t max_tokens, syfi_moe_ctx** out_ctx);
 
+/* Sizes the workspace explicitly: for calls of up to max_tokens tokens that route up to max_rows (token, local
+ * expert) pairs to this rank's experts (0 = the worst case, 8 * max_tokens).  Without it the workspace holds
+ * 8 rows per token up to 2048 tokens and 3 rows per token beyond (a token sends about one of its 8 routes to 32
+ * of 256 experts; the per-route f32 output rows are 28 KB each, so the worst case costs 2.5 GB at 8192 tokens
+ * against 1 GB for three rows per token).  A call that routes more rows than the workspace holds writes nothing
+ * out of bounds: syfi_moe_check reports status 104 and the output of that call is undefined.  Synchronises the
+ * device.  The reference sizes for 8 T rows always (moe.cu:2896-2926) but bounds its small-batch grids by
+ * min(8 T, 2 T + 4) rows (moe.cu:3069). */
+int syfi_moe_reserve(syfi_moe_ctx* ctx, int64_t max_tokens, int64_t max_rows);
+
 /* Frees the workspace (the reference never frees, moe.cu:2896-2926). */
 int syfi_moe_destroy(syfi_moe_ctx* ctx);
 
@@ -203,7 +213,7 @@ int syfi_moe_last_routing(syfi_moe_ctx* ctx, int64_t num_tokens, int32_t* topk_i
  * rows, [3] = active local experts (stats may be null).  Returns SYFI_MOE_ERR_DEVICE when a
  * kernel gave up on a bounded wait (the reference's mbarrier waits spin for ever, moe.cu:1298-1305);
  * the message names the status word: 101/102/103 = a GEMM kernel's producer/MMA/epilogue wait expired,
- * 104 = row table overflow, 105 = a peer rank's flag did not arrive, 106 = GEMM2 waited in vain for
+ * 104 = more routed rows than the workspace holds (syfi_moe_reserve), 105 = a peer rank's flag did not arrive, 106 = GEMM2 waited in vain for
  * GEMM1 to finish an expert. */
 int syfi_moe_check(syfi_moe_ctx* ctx, int32_t* stats4, void* stream);
 

@@ -49,6 +49,7 @@ struct syfi_moe_ctx {
   void* ep_gather = nullptr;
   size_t ep_gather_bytes = 0;
   // one-shot test hook (syfi_moe_debug_fault): applies to the next forward, then clears itself
+  int64_t reserved_rows = 0;          // syfi_moe_reserve: row capacity the caller asked for (0 = the default rule)
   int fault_mask = 0;
   long long fault_wait_limit = 0;
   // optional per-kernel timing
@@ -139,12 +140,21 @@ cudaError_t dev_alloc(T** p, size_t count, size_t* total) {
   return cudaMalloc(reinterpret_cast<void**>(p), bytes);
 }
 
-int alloc_workspace(Workspace& ws, int64_t max_tokens) {
+// Rows of the permuted row space (one per (token, local expert) route, plus per-expert padding) the workspace is
+// sized for.  A token can in theory send all 8 of its routes to the local experts (8 T rows), but with at most
+// 32 of 256 experts local it sends about one; the f32 per-route output rows are 28 KB each, so sizing for the
+// worst case costs 2.5 GB at 8192 tokens.  Up to 2048 tokens the worst case is kept (it is small); beyond,
+// 3 rows per token unless the caller reserved more (syfi_moe_reserve).  A call that needs more rows than there
+// are writes nothing out of bounds: the row-list kernel reports status 104 and the call's output is undefined.
+int64_t default_rows(int64_t T) { return T <= 2048 ? 8 * T : (3 * T > 16384 ? 3 * T : 16384); }
+
+int alloc_workspace(Workspace& ws, int64_t max_tokens, int64_t max_rows = 0) {
   if (max_tokens < 1) max_tokens = 1;
   free_workspace(ws);
   const int64_t T = max_tokens;
-  // worst case: every one of the 8 routes of every token is local, plus per-expert padding
-  const int64_t row_cap = (8 * T + kRowPad * kMaxLocalExperts + kMaxTokenTile - 1) / kMaxTokenTile * kMaxTokenTile;
+  int64_t rows = max_rows > 0 ? max_rows : default_rows(T);
+  if (rows > 8 * T) rows = 8 * T;
+  const int64_t row_cap = (rows + kRowPad * kMaxLocalExperts + 256 + kMaxTokenTile - 1) / kMaxTokenTile * kMaxTokenTile;
   if (row_cap * (int64_t)kHidden > (int64_t)1 << 40) return fail(SYFI_MOE_ERR_INVALID, "max_tokens too large");
   size_t total = 0;
   CU_TRY(dev_alloc(&ws.topk_idx, T * kTopK, &total));
@@ -160,6 +170,7 @@ int alloc_workspace(Workspace& ws, int64_t max_tokens) {
   CU_TRY(dev_alloc(&ws.row_token, row_cap, &total));
   CU_TRY(dev_alloc(&ws.route_row, T * kTopK, &total));
   CU_TRY(dev_alloc(&ws.work, kMaxLocalExperts, &total));
+  CU_TRY(cudaMemset(ws.work, 0, kMaxLocalExperts * sizeof(ExpertWork)));
   CU_TRY(dev_alloc(&ws.a_perm, row_cap * kHidden, &total));
   CU_TRY(dev_alloc(&ws.a_scale, row_cap * kHBlocks, &total));
   CU_TRY(dev_alloc(&ws.c_hi, row_cap * kInter, &total));
@@ -230,12 +241,12 @@ int validate(syfi_moe_ctx* ctx, const void* const* ptrs, int nptrs, int64_t T, i
 }
 
 int ensure_capacity(syfi_moe_ctx* ctx, int64_t T) {
-  if (T <= ctx->ws.max_tokens) return SYFI_MOE_OK;
+  if (T <= ctx->ws.max_tokens && (ctx->reserved_rows > 0 || ctx->ws.row_cap >= default_rows(T))) return SYFI_MOE_OK;
   // growing frees buffers that earlier calls may still be using
   CU_TRY(cudaDeviceSynchronize());
   ctx->map_w13 = nullptr;   // cached tensor maps point into the old workspace
   ctx->counters_clean = false;
-  return alloc_workspace(ctx->ws, T);
+  return alloc_workspace(ctx->ws, T > ctx->ws.max_tokens ? T : ctx->ws.max_tokens, ctx->reserved_rows);
 }
 
 int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const void* hs, const void* hs_scale,
@@ -424,6 +435,20 @@ int syfi_moe_create(int device, int64_t max_tokens, syfi_moe_ctx** out_ctx) {
   }
   *out_ctx = ctx;
   return SYFI_MOE_OK;
+}
+
+int syfi_moe_reserve(syfi_moe_ctx* ctx, int64_t max_tokens, int64_t max_rows) {
+  if (!ctx) return fail(SYFI_MOE_ERR_INVALID, "context is null");
+  if (max_tokens < 1 || max_tokens > (1 << 24)) return fail(SYFI_MOE_ERR_INVALID, "max_tokens out of range");
+  if (max_rows < 0 || max_rows > 8 * max_tokens) return fail(SYFI_MOE_ERR_INVALID, "max_rows must be in [0, 8 * max_tokens]");
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard guard(ctx->ws.device);
+  if (!guard.ok) return fail(SYFI_MOE_ERR_CUDA, "cannot select device %d", ctx->ws.device);
+  CU_TRY(cudaDeviceSynchronize());       // earlier calls may still be using the buffers that are replaced
+  ctx->map_w13 = nullptr;
+  ctx->counters_clean = false;
+  ctx->reserved_rows = max_rows;
+  return alloc_workspace(ctx->ws, max_tokens, max_rows);
 }
 
 int syfi_moe_destroy(syfi_moe_ctx* ctx) {
@@ -740,7 +765,7 @@ int syfi_moe_check(syfi_moe_ctx* ctx, int32_t* stats4, void* stream) {
     cudaMemsetAsync(ctx->ws.status, 0, sizeof(status), st);
     cudaMemsetAsync(ctx->ws.counts, 0, kMaxLocalExperts * sizeof(int), st);
     return fail(SYFI_MOE_ERR_DEVICE, "a kernel reported status %d (101/102/103: bounded wait expired in the TMA / MMA / "
-                "epilogue role of a grouped GEMM; 104: row or tile table overflow; 105: a peer rank's flag did not arrive; "
+                "epilogue role of a grouped GEMM; 104: more routed rows than the workspace holds, reserve more with syfi_moe_reserve; 105: a peer rank's flag did not arrive; "
                 "106: GEMM2 waited in vain for GEMM1 to finish an expert)", status[0]);
   }
   return SYFI_MOE_OK;

@@ -231,7 +231,8 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   pdl_trigger();
   if (warp == 3) {
     // this kernel's own tile table: token tiles of NT rows per expert and their prefix sums
-    ExpertWork ew = (lane < p.e_local) ? p.work[lane] : ExpertWork{0, 0, 0, 0};
+    // (meta[1] = 0: the row-list kernel refused the call, its work table is stale)
+    ExpertWork ew = (lane < p.e_local && p.meta[1] > 0) ? p.work[lane] : ExpertWork{0, 0, 0, 0};
     const int tiles = (ew.rows_pad + NT - 1) / NT;
     int incl = tiles;
 #pragma unroll

@@ -44,6 +44,7 @@ ABI = {
     "syfi_moe_ep_forward_replicated": (ctypes.c_int, [_vp, _vp, _i64] + [_vp] * 8 + [_i32, _i64, _f64, _vp, _vp]),
     "syfi_moe_ep_prepare": (ctypes.c_int, [_vp, _vp]),
     "syfi_moe_debug_fault": (ctypes.c_int, [_vp, _i32, _i64]),
+    "syfi_moe_reserve": (ctypes.c_int, [_vp, _i64, _i64]),
     "syfi_moe_route_noalloc": (ctypes.c_int, [_vp, _vp, _i64, _i32, _i64, _f64, _vp, _vp, _vp]),
     "syfi_moe_last_routing": (ctypes.c_int, [_vp, _i64, _vp, _vp, _vp]),
     "syfi_moe_check": (ctypes.c_int, [_vp, ctypes.POINTER(_i32), _vp]),
@@ -144,6 +145,11 @@ class MoeContext:
         ms = (ctypes.c_float * 6)()
         _check(self.lib.syfi_moe_last_stage_ms(self.handle, ms))
         return dict(zip(self.STAGES, [float(x) for x in ms]))
+
+    def reserve(self, max_tokens: int, max_rows: int = 0):
+        """Size the workspace for ``max_tokens`` tokens routing up to ``max_rows`` rows to this rank's experts
+        (0 = the worst case of 8 per token); see ``syfi_moe_reserve``."""
+        _check(self.lib.syfi_moe_reserve(self.handle, int(max_tokens), int(max_rows)))
 
     def debug_fault(self, mask: int, wait_limit_cycles: int):
         """Test hook (``syfi_moe_debug_fault``): the next forward runs with a short wait limit and the given

@@ -535,3 +535,26 @@ def test_bounded_waits_run_out_and_the_context_recovers(T, E, tile, mask, expect
     assert any(f"status {c}" in str(err.value) for c in expected), str(err.value)
     after, _ = _run(pkg, inp)                    # the hook was one-shot; the context works as before
     assert torch.equal(before, after)
+
+
+def test_row_capacity_overflow_is_reported_not_written(pkg):
+    """The workspace holds 3 rows per token beyond 2048 tokens (a token sends about one of its 8 routes to 32 of
+    256 experts).  Every local expert made hot sends far more: the row-list kernel refuses to write past the
+    capacity and the call reports status 104; after reserving the worst case the same call succeeds."""
+    T = 2304
+    inp = pkg.make_inputs(num_tokens=T, seed=43, e_local=32, device=DEV)
+    # raise the logits of the 32 local experts so that most of every token's 8 routes stay local
+    logits = inp.routing_logits.clone()
+    logits[:, :32] += 6.0
+    hot = pkg.MoeInputs(logits, *inp.args()[1:])
+    ctx = pkg.get_context(0, T)
+    ctx.reserve(T, 3 * T)                       # the default rule, made explicit
+    out = torch.empty(T, 7168, dtype=torch.bfloat16, device=DEV)
+    pkg.run_moe(*hot.args(), out)
+    with pytest.raises(pkg.MoeError, match="status 104"):
+        ctx.check()
+    ctx.reserve(T, 0)                           # worst case: 8 rows per token
+    out2, stats = _run(pkg, hot)
+    assert stats["routes"] > 3 * T
+    assert bool(torch.isfinite(out2.float()).all())
+    ctx.reserve(64, 0)                          # back to a small workspace for whatever runs next
