@@ -184,9 +184,9 @@ def build_inputs(pkg, args, rank, world, dev):
         inp = pkg.make_inputs(num_tokens=T, seed=0, e_local=32, local_expert_offset=32 * rank, device=dev,
                               hot_experts=16, weight_seed=rank)
         return inp, 32
-    inp = pkg.make_inputs(num_tokens=T, seed=0, e_local=32, local_expert_offset=0, device=dev)
+    inp = pkg.make_inputs(num_tokens=T, seed=0, e_local=args.experts if world == 1 else 32, local_expert_offset=0, device=dev)
     if world == 1:
-        return inp, 32
+        return inp, args.experts
     per = 32 // world
     sl = slice(rank * per, (rank + 1) * per)
     part = pkg.MoeInputs(inp.routing_logits, inp.routing_bias, inp.hidden_states, inp.hidden_states_scale,
@@ -290,7 +290,7 @@ def gemm1_roofline(T, rows, active, stage_ms, peaks, world):
         flops = rows * GEMM1_FLOP_PER_ROW
         achieved = flops / t / 1e12
         peak = 2.0 * peaks["bf16_tflops_sustained"]
-        key = "pair_gemm_kernel<1>@T8192_E32" if (T == 8192 and world == 1) else None
+        key = "pair_gemm_kernel<1>@T8192_E32" if (T == 8192 and world == 1 and active >= 24) else None
         return {"kernel": "pair_gemm_kernel<1> (GEMM1 + SwiGLU + two-term requantisation, CTA pairs, tcgen05 cta_group::2)",
                 "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                 "peak_note": "no FP8 figure in MEASURED_PEAKS.json: 2 x bf16_tflops_sustained as the measured proxy "
@@ -317,6 +317,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", type=int, default=3, choices=[3, 4])
     ap.add_argument("--tokens", type=int, default=None)
+    ap.add_argument("--experts", type=int, default=32, help="1 GPU, config 3: only the first E local experts (profiling on a small case)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
@@ -465,7 +466,7 @@ def main():
 
     # ---- the decode batch and two more sizes on the same weights (1 GPU, config 3 only): the metric is quoted vs T
     decode = None
-    if world == 1 and args.config == 3 and not args.no_decode and T != 64:
+    if world == 1 and args.config == 3 and not args.no_decode and T != 64 and args.experts == 32:
         decode = {}
         for Td in (16, 64, 1024):
             tk = pkg.make_inputs(num_tokens=Td, seed=0, e_local=1, device="cpu")
@@ -533,6 +534,8 @@ def main():
         line["parity"] = parity
     if decode is not None:
         line["decode"] = decode
+    if args.experts != 32:
+        line["config"]["workload"] += f" (first {args.experts} experts only: a profiling case, not the headline)"
 
     # ---- the reference's own CUDA kernel on this GPU (compiled unmodified into baseline/_ref), as a child process
     # with a time limit: its device-side waits are unbounded
