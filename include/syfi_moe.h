@@ -194,7 +194,9 @@ int syfi_moe_ep_forward_replicated(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep
  * memory on every GPU that loads the library, held until the process exits), which limits a call to
  * SYFI_MOE_NOALLOC_MAX_TOKENS tokens; larger batches are rejected with SYFI_MOE_ERR_INVALID.
  * It works on the CURRENT device.  The first call on a device looks up the array's device address
- * (one cudaGetSymbolAddress); make that first call before any stream capture begins.  All calls on a
+ * (one cudaGetSymbolAddress) and keeps it for the life of the process: after cudaDeviceReset on that
+ * device the kept address is stale, so a process that resets a device must not call this again for it.
+ * Make that first call during start-up, outside any stream capture.  All calls on a
  * device share the array, so calls that overlap on the GPU (different streams, no dependency) race;
  * keep them on one stream or order them with events.  Outputs are caller-supplied DEVICE buffers:
  * topk_idx int32 [T, 8], topk_weights f32 [T, 8]. */

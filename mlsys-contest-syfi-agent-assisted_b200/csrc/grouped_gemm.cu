@@ -411,6 +411,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     // An item counts when every epilogue warp has issued its stores (s_done) and a gpu-scope fence has
     // made them visible; that fence waits for the stores to be acknowledged (microseconds while HBM is
     // saturated), which is why it runs here and not in an epilogue warp.
+    //
+    // The ordering chain from GEMM1's stores to GEMM2's TMA loads, link by link:
+    //   1. epilogue threads: generic-proxy stores of c_hi / c_lo / c_scale, then __threadfence_block(),
+    //      then one atomicAdd on s_done per warp (CTA scope: stores before the count);
+    //   2. this lane: volatile read of s_done (observes the counts, hence the stores, by causality at
+    //      CTA scope), __threadfence() (cumulative: lifts what it observed to gpu scope),
+    //      fence.proxy.async (generic-proxy writes ordered before later async-proxy accesses),
+    //      red.release.gpu on ready[expert];
+    //   3. GEMM2's helper lane: ld.acquire.gpu of ready[expert] (synchronises with every release of 2),
+    //      fence.proxy.async, __threadfence_block(), volatile store of the cleared-item count to s_done;
+    //   4. GEMM2's producer lane: volatile read of that count, __threadfence_block(), then the TMA loads.
+    // Links 2 and 3 put a proxy fence on both sides of the release/acquire pair; links 1 and 4 are plain
+    // CTA-scope causality, which the fences of 2 and 3 extend because fences are cumulative.  The fences
+    // are executed by the publishing / acquiring lanes, not by the threads that store or that issue the
+    // loads; the back-to-back bit-identity test exercises exactly this hand-off.
     if (MODE == 1 && lane == 0) {
       int done_target = 0, e_hint = 0;
       for (int i = 0; i < my_items; ++i) {

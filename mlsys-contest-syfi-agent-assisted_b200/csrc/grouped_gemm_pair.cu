@@ -519,6 +519,8 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
             __nanosleep(200);
           }
           if (!seen || *s_abort != 0) break;          // a failed item is never published
+          // same ordering chain as the single-CTA kernel's publisher (grouped_gemm.cu): stores -> CTA-scope
+          // count -> gpu-scope fence + proxy fence + release here; acquire + proxy fence in GEMM2's helper
           __threadfence();
           fence_proxy_async_all();
           red_release_gpu_add(p.ready + im.expert, 1);
