@@ -415,6 +415,40 @@ def main():
                              "routing against the oracle's CPU route"}
         del ref32
 
+    # ---- the serving layout on the same tokens: every rank brings only its own T/N tokens (token dispatch: routed
+    # rows pulled over NVLink; beside it the all-gather of every token).  Same rows in the same order reach every
+    # expert as with replicated tokens, so the outputs must equal the replicated step's bit for bit.
+    sharded = None
+    if world > 1 and peer_ok:
+        mine = slice(rank * (T // world), (rank + 1) * (T // world))
+        s_in = (inp.routing_logits[mine].contiguous(), inp.hidden_states[mine].contiguous(),
+                inp.hidden_states_scale[:, mine].contiguous())
+        o_d, o_g = torch.empty_like(out), torch.empty_like(out)
+
+        def dstep():
+            ep.forward_sharded(s_in[0], inp.routing_bias, s_in[1], s_in[2], o_d, dispatch=True)
+
+        def gstep():
+            ep.forward_sharded(s_in[0], inp.routing_bias, s_in[1], s_in[2], o_g, dispatch=False)
+        for _ in range(3):
+            dstep()
+            gstep()
+        barrier()
+        ms_d = time_layer(torch, dstep, K, barrier, dist, dev)
+        ms_g = time_layer(torch, gstep, K, barrier, dist, dev)
+        step()
+        barrier()
+        same = torch.tensor([1 if (torch.equal(o_d, out) and torch.equal(o_g, out)) else 0], device=dev)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        ctx.check()
+        sharded = {"tokens_per_rank": T // world, "unit": UNIT,
+                   "token_dispatch": {"ms_per_step": ms_d, "value": T / (ms_d / 1e3)},
+                   "all_gather": {"ms_per_step": ms_g, "value": T / (ms_g / 1e3)},
+                   "bit_identical_to_replicated_step": bool(int(same.item())),
+                   "note": "each rank passes its own T/N tokens; dispatch = route own tokens, peers pull only the rows "
+                           "routed to their experts; all_gather = every token to every rank; both return partial rows "
+                           "to the owners through the fused combine + push"}
+
     # ---- per-kernel pass (same steps, events around every kernel) -> roofline of GEMM1
     Ks = min(K, 100)
     stage_ms = stage_pass(ctx, step, Ks)
@@ -534,6 +568,8 @@ def main():
         line["parity"] = parity
     if decode is not None:
         line["decode"] = decode
+    if sharded is not None:
+        line["sharded"] = sharded
     if args.experts != 32:
         line["config"]["workload"] += f" (first {args.experts} experts only: a profiling case, not the headline)"
 

@@ -169,6 +169,24 @@ int syfi_moe_ep_forward(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep, int64_t s
                         const void* gemm1_weights, const void* gemm1_weights_scale, const void* gemm2_weights,
                         const void* gemm2_weights_scale, int32_t num_local_experts, int64_t local_expert_offset,
                         double routed_scaling_factor, void* output, void* stream);
+/* Token dispatch: same inputs, output, region and step rules as syfi_moe_ep_forward, and bit-identical
+ * results, but the tokens are not all-gathered.  Each rank routes only its OWN tokens and publishes their
+ * eight (expert, weight) pairs, hidden rows and scales; each rank then pulls from every rank only the rows
+ * that selected one of its experts (with DeepSeek's group-limited routing a token reaches at most four of
+ * the eight expert groups, so at most half of the rows travel to a rank that owns one group), derives the
+ * masks and row counts of its experts from the received routes, and runs the layer from the row lists on.
+ * Against the all-gather layout: the router runs on tokens_per_rank instead of world_size * tokens_per_rank
+ * tokens, no logits cross the link, and only routed rows do.  The return leg (partial rows pushed to the
+ * tokens' owners, summed in rank order) is the same.  The two layouts may share a region as long as every
+ * rank makes the same sequence of calls.  No counterpart in the reference (moe.cu:182-185 is its only
+ * multi-GPU hook). */
+int syfi_moe_ep_forward_dispatch(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep, int64_t step,
+                                 const void* routing_logits, const void* routing_bias, const void* hidden_states,
+                                 const void* hidden_states_scale, const void* gemm1_weights,
+                                 const void* gemm1_weights_scale, const void* gemm2_weights,
+                                 const void* gemm2_weights_scale, int32_t num_local_experts,
+                                 int64_t local_expert_offset, double routed_scaling_factor, void* output,
+                                 void* stream);
 /* The same exchange for REPLICATED tokens (the large-prefill layout: every rank holds the same
  * world_size * tokens_per_rank tokens and owns a slice of the experts; the reference's
  * local_expert_offset hook, moe.cu:182-185, used as expert parallelism).  No token gather: each rank runs

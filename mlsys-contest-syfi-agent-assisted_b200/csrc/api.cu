@@ -202,6 +202,7 @@ const void* mapped_alias(const void* host) {
 constexpr int64_t kPairMinTokens = 6144;   // batches from this size on use the CTA-pair GEMM kernels (measured: even at 4096, 8 % faster at 8192, 17 % at 16384)
 constexpr int kFlagOutF32 = 1;      // run_layer flags
 constexpr int kFlagPrepacked = 2;
+constexpr int kFlagRoutingGiven = 4;   // the workspace already holds routes, masks and row counters of all tokens (token dispatch)
 
 // f32 matrix [rows, cols] (cols contiguous), box [rows, box_cols], no swizzle: the per-K-block scales of a
 // token tile, fetched with one load.
@@ -326,8 +327,10 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
   // has left (or will have left, in stream order) the row counters at zero
   const bool clean = ctx->counters_clean;
   ctx->counters_clean = false;
-  CU_TRY(launch_router(static_cast<const float*>(logits), bias, T, e_local, (int)offset, (float)scaling, ws, clean, st));
-  ctx->launches += 1;
+  if (!(flags & kFlagRoutingGiven)) {
+    CU_TRY(launch_router(static_cast<const float*>(logits), bias, T, e_local, (int)offset, (float)scaling, ws, clean, st));
+    ctx->launches += 1;
+  }
   STAGE_MARK(1);
   if (ctx->n_pending > 0) {         // forward_host: the hidden states travel while the router runs
     for (int i = 0; i < ctx->n_pending; ++i)
@@ -675,6 +678,52 @@ int syfi_moe_ep_forward(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep, int64_t s
   if (rc) return rc;
   CU_TRY(launch_ep_push_final(*ep, seq, ctx->ws, output, ctx->ws.ep_ticket, st));
   ctx->launches += 4;
+  return SYFI_MOE_OK;
+}
+
+int syfi_moe_ep_forward_dispatch(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep, int64_t step,
+                                 const void* routing_logits, const void* routing_bias, const void* hidden_states,
+                                 const void* hidden_states_scale, const void* gemm1_weights,
+                                 const void* gemm1_weights_scale, const void* gemm2_weights,
+                                 const void* gemm2_weights_scale, int32_t num_local_experts,
+                                 int64_t local_expert_offset, double routed_scaling_factor, void* output,
+                                 void* stream) {
+  int rc = validate_ep(ep, step);
+  if (rc) return rc;
+  const int W = ep->world_size;
+  const int64_t T = ep->tokens_per_rank;
+  const void* ptrs[] = {routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                        gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, output};
+  rc = validate(ctx, ptrs, 9, T * W, num_local_experts, local_expert_offset, routed_scaling_factor);
+  if (rc) return rc;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  DeviceGuard guard(ctx->ws.device);
+  if (!guard.ok) return fail(SYFI_MOE_ERR_CUDA, "cannot select device %d", ctx->ws.device);
+  if ((rc = ensure_capacity(ctx, T * W))) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t NT = (size_t)T * W;
+  const size_t o_hs = up256(NT * kExpertsGlobal * 4), o_sc = o_hs + up256(NT * kHidden), need = o_sc + up256(NT * kHBlocks * 4);
+  if ((rc = ensure_ep_gather(ctx, need))) return rc;
+  char* g = static_cast<char*>(ctx->ep_gather);
+  const uint32_t seq = (uint32_t)step;
+  // 1. route this rank's own tokens; ids and weights go straight into the step's in-buffer of the region
+  //    (no expert counts as local here: masks and row counters are made by the pull, per destination)
+  Workspace own = ctx->ws;
+  ep_dispatch_route_targets(*ep, seq, &own.topk_idx, &own.topk_w);
+  if (!ctx->counters_clean) CU_TRY(cudaMemsetAsync(ctx->ws.counts, 0, sizeof(int) * 2 * kMaxLocalExperts, st));
+  ctx->counters_clean = false;
+  CU_TRY(launch_router(static_cast<const float*>(routing_logits), routing_bias, (int)T, 0, 0,
+                       (float)routed_scaling_factor, own, true, st));
+  // 2. publish rows and scales, pull the rows routed to this rank's experts from every rank
+  CU_TRY(launch_ep_dispatch(*ep, seq, hidden_states, hidden_states_scale, num_local_experts, (int)local_expert_offset,
+                            ctx->ws, g + o_hs, g + o_sc, ctx->num_sms, st));
+  // 3. the layer from the row lists on, 4. partial rows back to the tokens' owners, summed there
+  rc = run_layer(ctx, nullptr, routing_bias, g + o_hs, g + o_sc, gemm1_weights, gemm1_weights_scale, gemm2_weights,
+                 gemm2_weights_scale, (int64_t)NT, num_local_experts, local_expert_offset, routed_scaling_factor,
+                 nullptr, kFlagRoutingGiven, st);
+  if (rc) return rc;
+  CU_TRY(launch_ep_push_final(*ep, seq, ctx->ws, output, ctx->ws.ep_ticket, st));
+  ctx->launches += 5;
   return SYFI_MOE_OK;
 }
 

@@ -22,6 +22,12 @@
 // output row that depends on a failed rank is written as NaN.
 // With replicated tokens (every rank holds all W*T tokens, syfi_moe_ep_forward_replicated) only push and
 // final run: the reduce-scatter is the combine kernel itself.
+// Token dispatch (syfi_moe_ep_forward_dispatch) replaces publish + gather by
+//   route   : the router runs on this rank's own T tokens and writes ids and weights into the in-buffer
+//   publish : hidden rows and token-major scales beside them, then the same in_flag
+//   pull    : per source rank, wait for its flag, read the routes of its tokens (64 bytes each), keep the
+//             ones that name a local expert (mask, row counters), and pull only those tokens' rows
+// so the layer starts at the row lists; push and final are shared with the other layouts.
 #include <cuda_bf16.h>
 
 #include "../../include/syfi_moe.h"
@@ -121,6 +127,133 @@ ep_gather_kernel(EpView v, uint32_t seq, uint4* __restrict__ g_logits, uint4* __
   for (size_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n_sc; i += stride) {
     const int kb = static_cast<int>(i / T), t = static_cast<int>(i % T);
     g_scale[static_cast<size_t>(kb) * (static_cast<size_t>(W) * T) + static_cast<size_t>(src) * T + t] = sc[i];
+  }
+}
+
+// ------------------------------------------------------------------- token dispatch: publish
+// Token dispatch: a rank routes its OWN tokens (the router writes the eight expert ids and weights of every
+// token straight into this rank's in-buffer), publishes hidden rows and token-major scales beside them, and
+// every rank then pulls only the rows that selected one of its experts.  In-buffer of a step:
+//   topk_idx int32 [T, 8] | topk_w f32 [T, 8] | hidden e4m3 [T, 7168] | scales f32 [T, 56]
+// (7456 bytes per token: fits the in-buffer of the all-gather layout, so both layouts share one region).
+__host__ __device__ inline size_t disp_w_off(size_t T) { return T * 32; }
+__host__ __device__ inline size_t disp_hs_off(size_t T) { return T * 64; }
+__host__ __device__ inline size_t disp_sc_off(size_t T) { return T * 64 + T * kHidden; }
+
+__global__ void __launch_bounds__(256)
+ep_publish_tokens_kernel(EpView v, uint32_t seq, const uint4* __restrict__ hs, const float* __restrict__ scale,
+                         int* __restrict__ ticket) {
+  const size_t T = v.T;
+  uint8_t* in = v.base[v.rank] + v.in_off[seq & 1];
+  uint4* dst_hs = reinterpret_cast<uint4*>(in + disp_hs_off(T));
+  float* dst_sc = reinterpret_cast<float*>(in + disp_sc_off(T));
+  const size_t n_hs = T * (kHidden / 16), n_sc = T * kHBlocks;
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  for (size_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n_hs; i += stride) dst_hs[i] = __ldg(hs + i);
+  // scales arrive [56, T]; a puller wants the 56 scales of a token side by side (one 224-byte read)
+  for (size_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n_sc; i += stride) {
+    const size_t kb = i / T, t = i % T;
+    dst_sc[t * kHBlocks + kb] = __ldg(scale + i);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (atomicAdd(ticket, 1) == static_cast<int>(gridDim.x) - 1) {   // last CTA: everything is written
+      *ticket = 0;
+      __threadfence_system();
+      for (int r = 0; r < v.world; ++r) st_release_sys(in_flag(v, r, v.rank), seq);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------- token dispatch: pull
+// grid = (chunks, world): blockIdx.y is the source rank; a CTA takes 32 tokens of that rank at a time.
+// Warp 0 reads the tokens' routes from the source, keeps a copy for the row-list and combine kernels,
+// derives the mask of this rank's experts and counts rows per expert; then the eight warps pull the rows
+// of the tokens whose mask is not empty (7168 + 224 bytes each) into the slot [source rank][token] of the
+// gathered tensors.  Rows nobody here needs never cross the link.
+constexpr int kPullTokens = 32;
+constexpr int kPullThreads = 256;
+
+__global__ void __launch_bounds__(kPullThreads)
+ep_dispatch_pull_kernel(EpView v, uint32_t seq, int e_local, int expert_offset, int* __restrict__ topk_idx,
+                        float* __restrict__ topk_w, uint32_t* __restrict__ local_mask, int* __restrict__ route_row,
+                        int* __restrict__ counts, uint4* __restrict__ g_hs, float* __restrict__ g_scale,
+                        int* __restrict__ status) {
+  __shared__ int s_ok, s_n;
+  __shared__ int s_list[kPullTokens];
+  __shared__ int s_cnt[kMaxLocalExperts];
+  const int src = blockIdx.y, T = v.T, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const size_t NT = static_cast<size_t>(v.world) * T;
+  if (tid == 0) {
+    s_ok = wait_flag(in_flag(v, v.rank, src), seq, v.wait_cycles) ? 1 : 0;
+    if (!s_ok) atomicExch(status, kStatusPeerTimeout);
+  }
+  __syncthreads();
+  const bool ok = s_ok != 0;
+  const uint8_t* in = v.base[src] + v.in_off[seq & 1];
+  const int4* r_idx = reinterpret_cast<const int4*>(in);
+  const float4* r_w = reinterpret_cast<const float4*>(in + disp_w_off(T));
+  const uint4* r_hs = reinterpret_cast<const uint4*>(in + disp_hs_off(T));
+  const float4* r_sc = reinterpret_cast<const float4*>(in + disp_sc_off(T));
+  const int chunks = (T + kPullTokens - 1) / kPullTokens;
+  for (int c = blockIdx.x; c < chunks; c += gridDim.x) {
+    if (tid < kMaxLocalExperts) s_cnt[tid] = 0;
+    if (tid == 0) s_n = 0;
+    __syncthreads();
+    if (warp == 0) {
+      const int t = c * kPullTokens + lane;
+      uint32_t mask = 0;
+      if (t < T) {
+        const size_t g = static_cast<size_t>(src) * T + t;
+        int4 i0 = make_int4(-1, -1, -1, -1), i1 = i0;
+        float4 w0 = make_float4(0.f, 0.f, 0.f, 0.f), w1 = w0;
+        if (ok) {   // a source that never published contributes no rows (and the step is marked failed)
+          i0 = r_idx[2 * t]; i1 = r_idx[2 * t + 1];
+          w0 = r_w[2 * t]; w1 = r_w[2 * t + 1];
+        }
+        reinterpret_cast<int4*>(topk_idx)[2 * g] = i0;
+        reinterpret_cast<int4*>(topk_idx)[2 * g + 1] = i1;
+        reinterpret_cast<float4*>(topk_w)[2 * g] = w0;
+        reinterpret_cast<float4*>(topk_w)[2 * g + 1] = w1;
+        const int4 none = make_int4(-1, -1, -1, -1);
+        reinterpret_cast<int4*>(route_row)[2 * g] = none;
+        reinterpret_cast<int4*>(route_row)[2 * g + 1] = none;
+        const int ids[kTopK] = {i0.x, i0.y, i0.z, i0.w, i1.x, i1.y, i1.z, i1.w};
+#pragma unroll
+        for (int k = 0; k < kTopK; ++k) {
+          const int le = ids[k] - expert_offset;
+          if (ids[k] >= 0 && le >= 0 && le < e_local) { mask |= 1u << le; atomicAdd(&s_cnt[le], 1); }
+        }
+        local_mask[g] = mask;
+      }
+      const unsigned hit = __ballot_sync(0xffffffffu, mask != 0);
+      if (mask != 0) s_list[__popc(hit & ((1u << lane) - 1u))] = t;
+      if (lane == 0) s_n = __popc(hit);
+    }
+    __syncthreads();
+    if (tid < e_local && s_cnt[tid] != 0) atomicAdd(&counts[tid], s_cnt[tid]);
+    const int n = s_n;
+    for (int j = warp; j < n; j += kPullThreads / 32) {
+      const int t = s_list[j];
+      const size_t g = static_cast<size_t>(src) * T + t;
+      const uint4* rs = r_hs + static_cast<size_t>(t) * (kHidden / 16);
+      uint4* rd = g_hs + g * (kHidden / 16);
+      uint4 x[14];                       // 448 x 16 bytes per row: all of a lane's loads in flight together
+#pragma unroll
+      for (int i = 0; i < 14; ++i) x[i] = rs[i * 32 + lane];
+      float4 sc = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (lane < kHBlocks / 4) sc = r_sc[static_cast<size_t>(t) * (kHBlocks / 4) + lane];
+#pragma unroll
+      for (int i = 0; i < 14; ++i) rd[i * 32 + lane] = x[i];
+      if (lane < kHBlocks / 4) {         // the layer wants scales k-block-major: [56, W*T]
+        g_scale[(4 * lane + 0) * NT + g] = sc.x;
+        g_scale[(4 * lane + 1) * NT + g] = sc.y;
+        g_scale[(4 * lane + 2) * NT + g] = sc.z;
+        g_scale[(4 * lane + 3) * NT + g] = sc.w;
+      }
+    }
+    __syncthreads();
   }
 }
 
@@ -265,6 +398,31 @@ cudaError_t launch_ep_publish_gather(const syfi_moe_ep_desc& d, uint32_t seq, co
   ep_gather_kernel<<<dim3(16, d.world_size), 256, 0, st>>>(v, seq, static_cast<uint4*>(g_logits),
                                                            static_cast<uint4*>(g_hs), static_cast<float*>(g_scale),
                                                            status);
+  return cudaGetLastError();
+}
+
+void ep_dispatch_route_targets(const syfi_moe_ep_desc& d, uint32_t seq, int** topk_idx, float** topk_w) {
+  const EpView v = make_view(d);
+  uint8_t* in = v.base[v.rank] + v.in_off[seq & 1];
+  *topk_idx = reinterpret_cast<int*>(in);
+  *topk_w = reinterpret_cast<float*>(in + disp_w_off(v.T));
+}
+
+cudaError_t launch_ep_dispatch(const syfi_moe_ep_desc& d, uint32_t seq, const void* hs, const void* hs_scale,
+                               int e_local, int expert_offset, const Workspace& ws, void* g_hs, void* g_scale,
+                               int num_sms, cudaStream_t st) {
+  const EpView v = make_view(d);
+  ep_publish_tokens_kernel<<<64, 256, 0, st>>>(v, seq, static_cast<const uint4*>(hs),
+                                               static_cast<const float*>(hs_scale), ws.ep_ticket);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  const int chunks = (v.T + kPullTokens - 1) / kPullTokens;
+  int per_src = (num_sms * 8 + d.world_size - 1) / d.world_size;   // about eight CTAs per SM over all sources
+  if (per_src > chunks) per_src = chunks;
+  if (per_src < 1) per_src = 1;
+  ep_dispatch_pull_kernel<<<dim3(per_src, d.world_size), kPullThreads, 0, st>>>(
+      v, seq, e_local, expert_offset, ws.topk_idx, ws.topk_w, ws.local_mask, ws.route_row, ws.counts,
+      static_cast<uint4*>(g_hs), static_cast<float*>(g_scale), ws.status);
   return cudaGetLastError();
 }
 

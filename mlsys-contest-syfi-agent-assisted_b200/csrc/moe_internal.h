@@ -158,6 +158,12 @@ size_t ep_region_bytes(int world, int64_t tokens_per_rank);
 cudaError_t launch_ep_publish_gather(const syfi_moe_ep_desc& d, uint32_t seq, const void* logits, const void* hs,
                                      const void* hs_scale, void* g_logits, void* g_hs, void* g_scale, int* ticket,
                                      int* status, cudaStream_t st);
+// token dispatch: where the router of this rank's own tokens must write (inside the step's in-buffer), and the
+// publish + sparse pull that fills ws.topk_idx / topk_w / local_mask / route_row / counts for all W*T tokens
+void ep_dispatch_route_targets(const syfi_moe_ep_desc& d, uint32_t seq, int** topk_idx, float** topk_w);
+cudaError_t launch_ep_dispatch(const syfi_moe_ep_desc& d, uint32_t seq, const void* hs, const void* hs_scale,
+                               int e_local, int expert_offset, const Workspace& ws, void* g_hs, void* g_scale,
+                               int num_sms, cudaStream_t st);
 cudaError_t launch_ep_push_final(const syfi_moe_ep_desc& d, uint32_t seq, const Workspace& ws, void* out_bf16,
                                  int* ticket, cudaStream_t st);
 

@@ -41,6 +41,7 @@ ABI = {
     "syfi_moe_route": (ctypes.c_int, [_vp, _vp, _vp, _i64, _i32, _i64, _f64, _vp, _vp, _vp]),
     "syfi_moe_ep_region_bytes": (_i64, [_i32, _i64]),
     "syfi_moe_ep_forward": (ctypes.c_int, [_vp, _vp, _i64] + [_vp] * 8 + [_i32, _i64, _f64, _vp, _vp]),
+    "syfi_moe_ep_forward_dispatch": (ctypes.c_int, [_vp, _vp, _i64] + [_vp] * 8 + [_i32, _i64, _f64, _vp, _vp]),
     "syfi_moe_ep_forward_replicated": (ctypes.c_int, [_vp, _vp, _i64] + [_vp] * 8 + [_i32, _i64, _f64, _vp, _vp]),
     "syfi_moe_ep_prepare": (ctypes.c_int, [_vp, _vp]),
     "syfi_moe_debug_fault": (ctypes.c_int, [_vp, _i32, _i64]),
@@ -371,17 +372,20 @@ def ep_region_bytes(world_size: int, tokens_per_rank: int) -> int:
 
 def run_moe_ep(desc: EpDesc, step: int, routing_logits, routing_bias, hidden_states, hidden_states_scale,
                gemm1_weights, gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
-               routed_scaling_factor, output, *, stream=None):
+               routed_scaling_factor, output, *, stream=None, dispatch: bool = False):
     """One expert-parallel step through peer memory (see ``syfi_moe_ep_forward``): this rank's own
     tokens in, their bf16 outputs summed over all ranks' experts out.  ``step`` counts 1, 2, 3, ...
-    identically on every rank."""
+    identically on every rank.  ``dispatch`` selects token dispatch (``syfi_moe_ep_forward_dispatch``: only
+    routed rows travel, each rank routes only its own tokens) instead of the all-gather of every token;
+    the results are bit-identical."""
     T, E, off, dev = _validate(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
                                gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
                                output, torch.bfloat16, None)
     if T != desc.tokens_per_rank:
         raise ValueError(f"descriptor is for {desc.tokens_per_rank} tokens per rank, got {T}")
     ctx = get_context(dev.index, T * desc.world_size)
-    _check(ctx.lib.syfi_moe_ep_forward(
+    fn = ctx.lib.syfi_moe_ep_forward_dispatch if dispatch else ctx.lib.syfi_moe_ep_forward
+    _check(fn(
         ctx.handle, ctypes.byref(desc), int(step), routing_logits.data_ptr(), routing_bias.data_ptr(),
         hidden_states.data_ptr(), hidden_states_scale.data_ptr(), gemm1_weights.data_ptr(),
         gemm1_weights_scale.data_ptr(), gemm2_weights.data_ptr(), gemm2_weights_scale.data_ptr(), E, off,

@@ -9,7 +9,9 @@ expert with one exchange step, the sum of the ranks' partial outputs:
   configuration): each rank computes an f32 partial [T, 7168] for its experts, the
   partials are all-reduced (or reduce-scattered by rows) and rounded to bf16 once.
 * ``forward_sharded`` — every rank brings its own T tokens (the serving layout:
-  data-parallel attention, expert-parallel MoE): token-side tensors are all-gathered,
+  data-parallel attention, expert-parallel MoE).  Peer-memory path: token dispatch (each rank
+  routes its own tokens, every rank pulls only the rows routed to its experts) and a sparse
+  push of partial rows back to the owners.  NCCL path: token-side tensors are all-gathered,
   each rank runs its experts over the W*T gathered tokens, and a reduce-scatter returns
   to each rank the summed rows of its own tokens.
 
@@ -170,9 +172,11 @@ class ExpertParallelMoe:
         self._peer_step = 0
         return True
 
-    def forward_sharded(self, logits, bias, hs, hs_scale, out_bf16=None):
+    def forward_sharded(self, logits, bias, hs, hs_scale, out_bf16=None, dispatch: bool = True):
         """Each rank passes its OWN T tokens (same T on every rank); returns their bf16 outputs
-        summed over all ranks' experts."""
+        summed over all ranks' experts.  On the peer-memory path ``dispatch`` (default) sends only the
+        rows a rank's experts were selected for (token dispatch); ``dispatch=False`` all-gathers every
+        token to every rank.  Both give the same bits."""
         T = logits.shape[0]
         W = self.world
         if W == 1:
@@ -185,7 +189,7 @@ class ExpertParallelMoe:
                 out_bf16 = torch.empty(T, hs.shape[1], dtype=torch.bfloat16, device=dev)
             self._peer_step += 1
             return _moe.run_moe_ep(peer[2], self._peer_step, logits, bias, hs, hs_scale, self.w13, self.w13_s,
-                                   self.w2, self.w2_s, self.offset, self.scaling, out_bf16)
+                                   self.w2, self.w2_s, self.offset, self.scaling, out_bf16, dispatch=dispatch)
         g_logits = self._buffer("g_logits", (W * T, logits.shape[1]), logits.dtype, dev)
         g_hs = self._buffer("g_hs", (W * T, hs.shape[1]), torch.uint8, dev)
         g_sc = self._buffer("g_sc", (W * hs_scale.shape[0], T), hs_scale.dtype, dev)

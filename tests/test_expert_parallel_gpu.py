@@ -83,6 +83,16 @@ def _worker(rank, world, port, q):
             pkg.get_context(rank).check()
             ok4 = all(torch.equal(a, b) for a, b in zip(outs, nccl_out))
             s4 = [float((a.float() - b.float()).abs().max()) for a, b in zip(outs, nccl_out)]
+            # forward_sharded dispatches tokens by default (only routed rows travel); the all-gather layout
+            # shares the region with it: alternate the two, again without host synchronisation
+            outs2 = [torch.empty(32, 7168, dtype=torch.bfloat16, device=dev) for _ in range(6)]
+            for i, (lg, hs, sc) in enumerate(steps):
+                if rank == 0 and i == 3:
+                    time.sleep(0.05)
+                ep.forward_sharded(lg, tok[1], hs, sc, outs2[i], dispatch=(i % 2 == 1))
+            torch.cuda.synchronize()
+            pkg.get_context(rank).check()
+            ok4 = ok4 and all(torch.equal(a, b) for a, b in zip(outs2, nccl_out))
         # replicated tokens: the reduce-scatter fused into the combine kernel, against NCCL's reduce-scatter
         ep6 = pkg.ExpertParallelMoe(ep.w13, ep.w13_s, ep.w2, ep.w2_s, off, 2.5)
         if ep6.enable_peer_exchange(256 // world, dev):

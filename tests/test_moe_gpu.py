@@ -431,6 +431,33 @@ def test_argument_validation(pkg):
     pkg.get_context(0).check()
 
 
+@pytest.mark.parametrize("T,E,seed", [(8, 2, 3), (77, 8, 4), (1500, 32, 5)])
+def test_token_dispatch_on_one_rank_equals_the_plain_layer(T, E, seed, pkg):
+    """The token-dispatch entry point with a world of one rank: route, publish, pull the routed rows from
+    the rank's own region, the layer from the row lists on, push and final sum.  Everything but the link is
+    exercised, and the result must equal the plain layer bit for bit — over several steps on different
+    tokens (alternating buffer sets) and interleaved with the all-gather layout on the same region."""
+    nbytes = pkg.ep_region_bytes(1, T)
+    region = torch.zeros(nbytes, dtype=torch.uint8, device=DEV)
+    desc = pkg.EpDesc()
+    desc.world_size, desc.rank, desc.tokens_per_rank = 1, 0, T
+    desc.region[0] = region.data_ptr()
+    desc.wait_limit_cycles = 1 << 27
+    base = pkg.make_inputs(num_tokens=T, seed=seed, e_local=E, local_expert_offset=32 if E < 32 else 0, device=DEV)
+    w = base.args()[4:8]
+    for step in range(1, 6):
+        tok = pkg.make_inputs(num_tokens=T, seed=100 * seed + step, e_local=1, device="cpu")
+        lg, hs, sc = (t.to(DEV) for t in (tok.routing_logits, tok.hidden_states, tok.hidden_states_scale))
+        want = torch.empty(T, 7168, dtype=torch.bfloat16, device=DEV)
+        pkg.run_moe(lg, base.routing_bias, hs, sc, *w, base.local_expert_offset, 2.5, want)
+        got = torch.full((T, 7168), float("nan"), dtype=torch.bfloat16, device=DEV)
+        pkg.run_moe_ep(desc, step, lg, base.routing_bias, hs, sc, *w, base.local_expert_offset, 2.5, got,
+                       dispatch=(step != 3))
+        stats = pkg.get_context(0).check()
+        assert torch.equal(got, want), (step, float((got.float() - want.float()).abs().max()))
+    assert stats["routes"] > 0      # the cases route rows to the local experts
+
+
 def test_peer_wait_runs_out_without_hanging(pkg):
     """Failure detection without a GPU fault: an expert-parallel step whose 'peer' never publishes
     (a second local buffer stands in for rank 1).  The flag waits give up after their limit (set short
@@ -448,11 +475,13 @@ def test_peer_wait_runs_out_without_hanging(pkg):
     desc.region[0], desc.region[1] = mine.data_ptr(), silent_peer.data_ptr()
     desc.wait_limit_cycles = 1 << 27          # ~70 ms per wait instead of the serving default of many seconds
     out = torch.zeros(T, 7168, dtype=torch.bfloat16, device=DEV)
-    pkg.run_moe_ep(desc, 1, *inp.args()[:8], 0, 2.5, out)
-    with pytest.raises(pkg.MoeError, match="105"):
-        pkg.get_context(0).check()
-    # a step whose peer never answered must not leave plausible numbers behind: every row is NaN
-    assert bool(torch.isnan(out.float()).all())
+    for step, dispatch in ((1, False), (2, True)):     # the all-gather layout, then token dispatch
+        out.zero_()
+        pkg.run_moe_ep(desc, step, *inp.args()[:8], 0, 2.5, out, dispatch=dispatch)
+        with pytest.raises(pkg.MoeError, match="105"):
+            pkg.get_context(0).check()
+        # a step whose peer never answered must not leave plausible numbers behind: every row is NaN
+        assert bool(torch.isnan(out.float()).all())
     # the context is usable afterwards
     good = torch.empty(T, 7168, dtype=torch.bfloat16, device=DEV)
     pkg.run_moe(*inp.args(), good)
