@@ -391,11 +391,12 @@ cudaError_t launch_ep_publish_gather(const syfi_moe_ep_desc& d, uint32_t seq, co
                                      const void* hs_scale, void* g_logits, void* g_hs, void* g_scale, int* ticket,
                                      int* status, cudaStream_t st) {
   const EpView v = make_view(d);
-  ep_publish_kernel<<<64, 256, 0, st>>>(v, seq, static_cast<const uint4*>(logits), static_cast<const uint4*>(hs),
+  // grids sized for large batches (tens of MB per rank); the grid-stride loops make small ones cheap
+  ep_publish_kernel<<<256, 256, 0, st>>>(v, seq, static_cast<const uint4*>(logits), static_cast<const uint4*>(hs),
                                         static_cast<const uint4*>(hs_scale), ticket);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
-  ep_gather_kernel<<<dim3(16, d.world_size), 256, 0, st>>>(v, seq, static_cast<uint4*>(g_logits),
+  ep_gather_kernel<<<dim3(1024 / d.world_size, d.world_size), 256, 0, st>>>(v, seq, static_cast<uint4*>(g_logits),
                                                            static_cast<uint4*>(g_hs), static_cast<float*>(g_scale),
                                                            status);
   return cudaGetLastError();
@@ -412,7 +413,11 @@ cudaError_t launch_ep_dispatch(const syfi_moe_ep_desc& d, uint32_t seq, const vo
                                int e_local, int expert_offset, const Workspace& ws, void* g_hs, void* g_scale,
                                int num_sms, cudaStream_t st) {
   const EpView v = make_view(d);
-  ep_publish_tokens_kernel<<<64, 256, 0, st>>>(v, seq, static_cast<const uint4*>(hs),
+  const long long vecs = static_cast<long long>(v.T) * (kHidden / 16);
+  int pub = static_cast<int>((vecs + 256 * 4 - 1) / (256 * 4));       // about four 16-byte vectors per thread
+  if (pub > num_sms * 8) pub = num_sms * 8;
+  if (pub < 1) pub = 1;
+  ep_publish_tokens_kernel<<<pub, 256, 0, st>>>(v, seq, static_cast<const uint4*>(hs),
                                                static_cast<const float*>(hs_scale), ws.ep_ticket);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
