@@ -415,6 +415,22 @@ def main():
                              "routing against the oracle's CPU route"}
         del ref32
 
+    # ---- the return leg both ways: GEMM2 storing its rows straight into the owners' memory (the default, timed
+    # above) against rows kept local + a combine kernel that pushes partial rows after GEMM2
+    return_leg = None
+    if world > 1 and peer_ok:
+        barrier()
+        os.environ["SYFI_MOE_EP_RETURN"] = "push"
+        for _ in range(3):
+            step()
+        ms_push = time_layer(torch, step, K, barrier, dist, dev)
+        del os.environ["SYFI_MOE_EP_RETURN"]
+        barrier()
+        step()
+        barrier()
+        ctx.check()
+        return_leg = {"rows_stored_by_gemm2_into_owner_memory_ms": ms, "combine_kernel_pushes_partial_rows_ms": ms_push}
+
     # ---- the serving layout on the same tokens: every rank brings only its own T/N tokens (token dispatch: routed
     # rows pulled over NVLink; beside it the all-gather of every token).  Same rows in the same order reach every
     # expert as with replicated tokens, so the outputs must equal the replicated step's bit for bit.
@@ -552,7 +568,7 @@ def main():
             "config": {"workload": workload_name(args.config, T), "tokens": T, "local_experts_per_rank": e_per_rank,
                        "parallelism": ("1 GPU" if world == 1 else
                                        f"expert parallel over {world} ranks, tokens replicated, every rank ends with its T/{world} rows: "
-                                       + ("reduce-scatter fused into the combine kernel over peer memory" if peer_ok
+                                       + ("reduce-scatter fused into GEMM2: its epilogue stores every expert row into the token owner's memory over NVLink, the owner sums in route order" if peer_ok
                                           else "f32 partials reduce-scattered by NCCL")),
                        "routes": rows_all, "routes_rank0": rows, "active_experts_rank0": active,
                        "l2": f"inputs larger than L2: {active * 44050944 / 1e6:.0f} MB of active-expert weights per step on rank 0",
@@ -570,6 +586,8 @@ def main():
         line["decode"] = decode
     if sharded is not None:
         line["sharded"] = sharded
+    if return_leg is not None:
+        line["return_leg"] = return_leg
     if args.experts != 32:
         line["config"]["workload"] += f" (first {args.experts} experts only: a profiling case, not the headline)"
 

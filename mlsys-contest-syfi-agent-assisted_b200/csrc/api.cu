@@ -48,6 +48,10 @@ struct syfi_moe_ctx {
   // gathered token-side tensors of the peer-memory expert-parallel path
   void* ep_gather = nullptr;
   size_t ep_gather_bytes = 0;
+  // set by the expert-parallel entry points for one run_layer: GEMM2 stores its rows straight into the token
+  // owners' receive slots of this region (step ep_rows_seq) instead of the local row buffer
+  const syfi_moe_ep_desc* ep_rows = nullptr;
+  uint32_t ep_rows_seq = 0;
   // one-shot test hook (syfi_moe_debug_fault): applies to the next forward, then clears itself
   int64_t reserved_rows = 0;          // syfi_moe_reserve: row capacity the caller asked for (0 = the default rule)
   int fault_mask = 0;
@@ -125,7 +129,7 @@ int make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uin
 
 void free_workspace(Workspace& ws) {
   void* ptrs[] = {ws.topk_idx, ws.topk_w, ws.local_mask, ws.counts, ws.meta, ws.status, ws.trace, ws.row_token, ws.route_row,
-                  ws.work, ws.a_perm, ws.a_scale, ws.c_hi, ws.c_lo, ws.c_scale, ws.o_rows, ws.ep_ticket};
+                  ws.work, ws.a_perm, ws.a_scale, ws.c_hi, ws.c_lo, ws.c_scale, ws.o_rows, ws.ep_ticket, ws.row_out};
   for (void* p : ptrs)
     if (p) cudaFree(p);
   const int dev = ws.device;
@@ -178,6 +182,8 @@ int alloc_workspace(Workspace& ws, int64_t max_tokens, int64_t max_rows = 0) {
   CU_TRY(dev_alloc(&ws.c_scale, row_cap * kIBlocks, &total));
   CU_TRY(dev_alloc(&ws.o_rows, row_cap * kHidden, &total));
   CU_TRY(dev_alloc(&ws.ep_ticket, 4, &total));
+  CU_TRY(dev_alloc(&ws.row_out, row_cap, &total));
+  CU_TRY(cudaMemset(ws.row_out, 0, row_cap * sizeof(float*)));
   CU_TRY(cudaMemset(ws.ep_ticket, 0, 4 * sizeof(int)));
   CU_TRY(cudaMemset(ws.status, 0, 4 * sizeof(int)));
   CU_TRY(cudaMemset(ws.meta, 0, kMetaInts * sizeof(int)));
@@ -342,6 +348,13 @@ int run_layer(syfi_moe_ctx* ctx, const void* logits, const void* bias, const voi
   }
   CU_TRY(launch_build_rows(T, e_local, (int)offset, pair ? 128 : token_tile, ws, st));
   ctx->launches += 1;
+  const syfi_moe_ep_desc* ep_rows = ctx->ep_rows;
+  ctx->ep_rows = nullptr;
+  g2.rows_to_targets = ctx->p2.rows_to_targets = ep_rows != nullptr ? 1 : 0;
+  if (ep_rows != nullptr) {          // where GEMM2 will store every row: the token owners' memory
+    CU_TRY(launch_ep_row_targets(*ep_rows, ctx->ep_rows_seq, ws, st));
+    ctx->launches += 1;
+  }
   STAGE_MARK(2);
   if (ctx->wait_before_gather) {    // hidden states still on their way from the host (forward_host)
     CU_TRY(cudaStreamWaitEvent(st, ctx->wait_before_gather, 0));
@@ -606,6 +619,31 @@ int64_t syfi_moe_ep_region_bytes(int32_t world_size, int64_t tokens_per_rank) {
 }
 
 namespace {
+// The return leg of the expert-parallel entry points.  Default: GEMM2 stores its rows straight into the token
+// owners' memory and the owners sum them (launch_ep_row_targets / launch_ep_raise_final).  SYFI_MOE_EP_RETURN=push
+// selects the earlier scheme for comparison: rows stay local, a combine kernel after GEMM2 sums each token's local
+// routes and pushes the partial row, the owners add the partials in rank order.  All ranks must choose alike.
+bool ep_rows_in_gemm2() {
+  const char* v = getenv("SYFI_MOE_EP_RETURN");
+  return !(v != nullptr && strcmp(v, "push") == 0);
+}
+
+int ep_layer_and_return(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep, uint32_t seq, const void* logits,
+                        const void* bias, const void* hs, const void* hs_scale, const void* w13,
+                        const void* w13_scale, const void* w2, const void* w2_scale, int64_t tokens_all,
+                        int32_t e_local, int64_t offset, double scaling, void* output, int flags, cudaStream_t st) {
+  const bool fused = ep_rows_in_gemm2();
+  if (fused) { ctx->ep_rows = ep; ctx->ep_rows_seq = seq; }
+  int rc = run_layer(ctx, logits, bias, hs, hs_scale, w13, w13_scale, w2, w2_scale, tokens_all, e_local, offset,
+                     scaling, nullptr, flags, st);
+  ctx->ep_rows = nullptr;
+  if (rc) return rc;
+  if (fused) CU_TRY(launch_ep_raise_final(*ep, seq, ctx->ws, output, st));
+  else CU_TRY(launch_ep_push_final(*ep, seq, ctx->ws, output, ctx->ws.ep_ticket, st));
+  ctx->launches += 2;
+  return SYFI_MOE_OK;
+}
+
 int validate_ep(const syfi_moe_ep_desc* ep, int64_t step) {
   if (!ep) return fail(SYFI_MOE_ERR_INVALID, "ep descriptor is null");
   const int W = ep->world_size;
@@ -672,12 +710,11 @@ int syfi_moe_ep_forward(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep, int64_t s
   const uint32_t seq = (uint32_t)step;
   CU_TRY(launch_ep_publish_gather(*ep, seq, routing_logits, hidden_states, hidden_states_scale, g, g + o_hs, g + o_sc,
                                   ctx->ws.ep_ticket, ctx->ws.status, st));
-  rc = run_layer(ctx, g, routing_bias, g + o_hs, g + o_sc, gemm1_weights, gemm1_weights_scale, gemm2_weights,
-                 gemm2_weights_scale, (int64_t)NT, num_local_experts, local_expert_offset, routed_scaling_factor,
-                 nullptr, 0, st);
+  rc = ep_layer_and_return(ctx, ep, seq, g, routing_bias, g + o_hs, g + o_sc, gemm1_weights, gemm1_weights_scale,
+                           gemm2_weights, gemm2_weights_scale, (int64_t)NT, num_local_experts, local_expert_offset,
+                           routed_scaling_factor, output, 0, st);
   if (rc) return rc;
-  CU_TRY(launch_ep_push_final(*ep, seq, ctx->ws, output, ctx->ws.ep_ticket, st));
-  ctx->launches += 4;
+  ctx->launches += 2;
   return SYFI_MOE_OK;
 }
 
@@ -718,12 +755,11 @@ int syfi_moe_ep_forward_dispatch(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep, 
   CU_TRY(launch_ep_dispatch(*ep, seq, hidden_states, hidden_states_scale, num_local_experts, (int)local_expert_offset,
                             ctx->ws, g + o_hs, g + o_sc, ctx->num_sms, st));
   // 3. the layer from the row lists on, 4. partial rows back to the tokens' owners, summed there
-  rc = run_layer(ctx, nullptr, routing_bias, g + o_hs, g + o_sc, gemm1_weights, gemm1_weights_scale, gemm2_weights,
-                 gemm2_weights_scale, (int64_t)NT, num_local_experts, local_expert_offset, routed_scaling_factor,
-                 nullptr, kFlagRoutingGiven, st);
+  rc = ep_layer_and_return(ctx, ep, seq, nullptr, routing_bias, g + o_hs, g + o_sc, gemm1_weights,
+                           gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, (int64_t)NT, num_local_experts,
+                           local_expert_offset, routed_scaling_factor, output, kFlagRoutingGiven, st);
   if (rc) return rc;
-  CU_TRY(launch_ep_push_final(*ep, seq, ctx->ws, output, ctx->ws.ep_ticket, st));
-  ctx->launches += 5;
+  ctx->launches += 3;
   return SYFI_MOE_OK;
 }
 
@@ -748,13 +784,10 @@ int syfi_moe_ep_forward_replicated(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // every rank already holds all tokens: the layer for this rank's experts, then the combine that pushes each
   // token's partial row to the token's owner and the final sum of the owners
-  rc = run_layer(ctx, routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
-                 gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, NT, num_local_experts, local_expert_offset,
-                 routed_scaling_factor, nullptr, 0, st);
-  if (rc) return rc;
-  CU_TRY(launch_ep_push_final(*ep, (uint32_t)step, ctx->ws, output, ctx->ws.ep_ticket, st));
-  ctx->launches += 2;
-  return SYFI_MOE_OK;
+  return ep_layer_and_return(ctx, ep, (uint32_t)step, routing_logits, routing_bias, hidden_states,
+                             hidden_states_scale, gemm1_weights, gemm1_weights_scale, gemm2_weights,
+                             gemm2_weights_scale, NT, num_local_experts, local_expert_offset, routed_scaling_factor,
+                             output, 0, st);
 }
 
 int syfi_moe_route(syfi_moe_ctx* ctx, const void* routing_logits, const void* routing_bias, int64_t num_tokens,

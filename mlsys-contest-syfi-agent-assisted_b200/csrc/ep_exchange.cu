@@ -76,6 +76,10 @@ __device__ __forceinline__ uint32_t* out_flag(const EpView& v, int on_rank, int 
   return reinterpret_cast<uint32_t*>(v.base[on_rank] + v.flag_off) + kMaxRanks + src;
 }
 
+__device__ __forceinline__ uint32_t* fail_word(const EpView& v, int on_rank, int src) {
+  return reinterpret_cast<uint32_t*>(v.base[on_rank] + v.flag_off) + 2 * kMaxRanks + src;
+}
+
 // ------------------------------------------------------------------------------ publish
 __global__ void __launch_bounds__(256)
 ep_publish_kernel(EpView v, uint32_t seq, const uint4* __restrict__ logits, const uint4* __restrict__ hs,
@@ -362,6 +366,105 @@ ep_final_kernel(EpView v, uint32_t seq, __nv_bfloat16* __restrict__ out, int* __
   }
 }
 
+// ------------------------------------------------- GEMM2 rows straight into the owners' memory
+// The exchange fused into GEMM2: instead of storing an expert's output rows locally, summing a token's local
+// routes and pushing the partial row, GEMM2's epilogue stores every row where the token's OWNER will read it:
+// slot [token][k] of the owner's receive area, k = the route's position among the token's eight.  The transfer
+// then overlaps the GEMM tile by tile, the f32 rows never make a round trip through local memory, and the owner
+// adds the rows that arrived in route order k = 0..7 — the order of the single-GPU combine, so the result does
+// not depend on how the experts are spread over the ranks.
+//   targets : one pointer per permuted row (null for padding rows) + a presence word = step number in the
+//             owner's table for every routed (token, k)
+//   raise   : after GEMM2 (an ordinary launch: all of GEMM2's stores have been performed), out_flag[me] = seq
+//             on every rank, preceded by a failure word when this rank's step failed
+//   final   : wait for all ranks, sum_k w[k] * slot[token][k] over the present slots, round once
+__global__ void __launch_bounds__(256)
+ep_row_targets_kernel(EpView v, uint32_t seq, int tokens_all, const int* __restrict__ route_row,
+                      const int* __restrict__ row_token, const int* __restrict__ meta, int row_cap,
+                      float** __restrict__ row_out) {
+  pdl_wait();
+  pdl_trigger();
+  const int rows_total = meta[1];
+  const int stride = gridDim.x * blockDim.x;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < tokens_all * kTopK; i += stride) {
+    const int row = route_row[i];
+    if (row < 0 || row >= row_cap) continue;
+    const int t = i / kTopK, k = i % kTopK;
+    const int owner = t / v.T, tl = t % v.T;
+    const size_t slot = static_cast<size_t>(tl) * kTopK + k;
+    row_out[row] = reinterpret_cast<float*>(v.base[owner] + v.recv_off[seq & 1]) + slot * kHidden;
+    reinterpret_cast<uint32_t*>(v.base[owner] + v.has_off[seq & 1])[slot] = seq;
+  }
+  for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < rows_total && r < row_cap; r += stride)
+    if (row_token[r] < 0) row_out[r] = nullptr;
+}
+
+__global__ void __launch_bounds__(32)
+ep_raise_kernel(EpView v, uint32_t seq, const int* __restrict__ status) {
+  const bool failed = *reinterpret_cast<const volatile int*>(status) != 0;
+  __threadfence_system();
+  const int r = threadIdx.x;
+  if (r < v.world) {
+    if (failed) *fail_word(v, r, v.rank) = seq;   // same thread, same destination: ordered before the release below
+    st_release_sys(out_flag(v, r, v.rank), seq);
+  }
+}
+
+__global__ void __launch_bounds__(kPushThreads)
+ep_final_rows_kernel(EpView v, uint32_t seq, const float* __restrict__ topk_w, __nv_bfloat16* __restrict__ out,
+                     int* __restrict__ status) {
+  __shared__ int s_state;     // 0 = fine, 1 = poisoned
+  const int tl = blockIdx.x, tid = threadIdx.x;
+  if (tid == 0) {
+    int bad = 0;
+    for (int q = 0; q < v.world && !bad; ++q) bad = wait_flag(out_flag(v, v.rank, q), seq, v.wait_cycles) ? 0 : 1;
+    if (bad) atomicExch(status, kStatusPeerTimeout);
+    for (int q = 0; q < v.world && !bad; ++q)
+      if (*reinterpret_cast<const volatile uint32_t*>(fail_word(v, v.rank, q)) == seq) bad = 1;
+    if (!bad && *reinterpret_cast<const volatile int*>(status) != 0) bad = 1;
+    s_state = bad;
+  }
+  __syncthreads();
+  const bool poisoned = s_state != 0;
+  const uint32_t* has = reinterpret_cast<const uint32_t*>(v.base[v.rank] + v.has_off[seq & 1]) + static_cast<size_t>(tl) * kTopK;
+  const float4* recv = reinterpret_cast<const float4*>(v.base[v.rank] + v.recv_off[seq & 1]) +
+                       static_cast<size_t>(tl) * kTopK * (kHidden / 4);
+  const float* w = topk_w + (static_cast<size_t>(v.rank) * v.T + tl) * kTopK;
+  float4 acc[kVec];
+#pragma unroll
+  for (int i = 0; i < kVec; ++i) acc[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (!poisoned) {
+#pragma unroll 1
+    for (int k = 0; k < kTopK; ++k) {
+      if (__ldcg(has + k) != seq) continue;
+      const float wk = w[k];
+      const float4* src = recv + static_cast<size_t>(k) * (kHidden / 4);
+#pragma unroll
+      for (int i = 0; i < kVec; ++i) {
+        const float4 x = __ldcg(src + i * kPushThreads + tid);
+        acc[i].x = fmaf(wk, x.x, acc[i].x);
+        acc[i].y = fmaf(wk, x.y, acc[i].y);
+        acc[i].z = fmaf(wk, x.z, acc[i].z);
+        acc[i].w = fmaf(wk, x.w, acc[i].w);
+      }
+    }
+  } else {   // a peer never answered, or a rank's step failed: no number is better than a wrong one
+    const float nan = __int_as_float(0x7fc00000);
+#pragma unroll
+    for (int i = 0; i < kVec; ++i) acc[i] = make_float4(nan, nan, nan, nan);
+  }
+  uint2* dst = reinterpret_cast<uint2*>(out + static_cast<size_t>(tl) * kHidden);
+#pragma unroll
+  for (int i = 0; i < kVec; ++i) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(acc[i].x, acc[i].y);
+    const __nv_bfloat162 hi = __floats2bfloat162_rn(acc[i].z, acc[i].w);
+    uint2 pk;
+    pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+    pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+    dst[i * kPushThreads + tid] = pk;
+  }
+}
+
 EpView make_view(const syfi_moe_ep_desc& d) {
   EpView v;
   for (int r = 0; r < kMaxRanks; ++r) v.base[r] = r < d.world_size ? static_cast<uint8_t*>(d.region[r]) : nullptr;
@@ -372,8 +475,11 @@ EpView make_view(const syfi_moe_ep_desc& d) {
   const size_t T = v.T, W = v.world;
   size_t off = 0;
   for (int b = 0; b < 2; ++b) { v.in_off[b] = off; off += align256(T * (kExpertsGlobal * 4 + kHidden + kHBlocks * 4)); }
-  for (int b = 0; b < 2; ++b) { v.recv_off[b] = off; off += align256(W * T * kHidden * 4); }
-  for (int b = 0; b < 2; ++b) { v.has_off[b] = off; off += align256(W * T * 4); }
+  // receive area of a step: either one f32 partial row per (source rank, token) or one f32 expert row per
+  // (token, route k); the second is the larger (world_size <= 8 = routes per token) and sizes both
+  const size_t slots = (W > static_cast<size_t>(kTopK) ? W : static_cast<size_t>(kTopK)) * T;
+  for (int b = 0; b < 2; ++b) { v.recv_off[b] = off; off += align256(slots * kHidden * 4); }
+  for (int b = 0; b < 2; ++b) { v.has_off[b] = off; off += align256(slots * 4); }
   v.flag_off = off;
   return v;
 }
@@ -384,7 +490,7 @@ size_t ep_region_bytes(int world, int64_t tokens_per_rank) {
   syfi_moe_ep_desc d{};
   d.world_size = world;
   d.tokens_per_rank = tokens_per_rank;
-  return make_view(d).flag_off + align256(2 * kMaxRanks * sizeof(uint32_t));
+  return make_view(d).flag_off + align256(3 * kMaxRanks * sizeof(uint32_t));   // in flags, out flags, failure words
 }
 
 cudaError_t launch_ep_publish_gather(const syfi_moe_ep_desc& d, uint32_t seq, const void* logits, const void* hs,
@@ -428,6 +534,26 @@ cudaError_t launch_ep_dispatch(const syfi_moe_ep_desc& d, uint32_t seq, const vo
   ep_dispatch_pull_kernel<<<dim3(per_src, d.world_size), kPullThreads, 0, st>>>(
       v, seq, e_local, expert_offset, ws.topk_idx, ws.topk_w, ws.local_mask, ws.route_row, ws.counts,
       static_cast<uint4*>(g_hs), static_cast<float*>(g_scale), ws.status);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_row_targets(const syfi_moe_ep_desc& d, uint32_t seq, const Workspace& ws, cudaStream_t st) {
+  const EpView v = make_view(d);
+  const int tokens = d.world_size * static_cast<int>(d.tokens_per_rank);
+  int grid = (tokens * kTopK + 255) / 256;
+  if (grid > 1184) grid = 1184;
+  return launch_dependent(ep_row_targets_kernel, dim3(grid), dim3(256), 0, st, v, seq, tokens, ws.route_row,
+                          ws.row_token, ws.meta, ws.row_cap, ws.row_out);
+}
+
+cudaError_t launch_ep_raise_final(const syfi_moe_ep_desc& d, uint32_t seq, const Workspace& ws, void* out_bf16,
+                                  cudaStream_t st) {
+  const EpView v = make_view(d);
+  ep_raise_kernel<<<1, 32, 0, st>>>(v, seq, ws.status);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  ep_final_rows_kernel<<<static_cast<int>(d.tokens_per_rank), kPushThreads, 0, st>>>(
+      v, seq, ws.topk_w, static_cast<__nv_bfloat16*>(out_bf16), ws.status);
   return cudaGetLastError();
 }
 

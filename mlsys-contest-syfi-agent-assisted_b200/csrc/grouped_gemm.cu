@@ -106,6 +106,7 @@ struct GemmArgs {
   long long* trace_cta;     // [grid][5] per-CTA start/end (globaltimer, clock64) and SM id, SYFI_TRACE only
   long long wait_limit;     // SM clocks a wait may take before the CTA gives up (tests make it short)
   int silent_producer;      // test hook: the TMA producer issues nothing, so that the other roles' waits run out
+  float* const* row_out;    // mode 2, expert parallelism: row r goes to row_out[r] (a peer's memory; null = padding row, not stored) instead of o_rows
 };
 
 // Optional timeline trace of CTA 0 (compile with -DSYFI_TRACE): role r appends (tag, clock) pairs.
@@ -722,13 +723,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         if (lane == 0) atomicAdd(s_done, 1);
       } else {
         const int qrow = lane & 3;
-        float* o = p.o_rows + static_cast<size_t>(im.row_start + c0 + qrow) * kHidden + ft * 128 + q * 32 + (lane >> 2) * 4;
+        const int row0 = im.row_start + c0 + qrow;
+        const int col = ft * 128 + q * 32 + (lane >> 2) * 4;
 #pragma unroll
         for (int j = 0; j < CN; j += 4) {
           if (c0 + j < n_out) {
             float a0 = acc0[j], a1 = acc0[j + 1], a2 = acc0[j + 2], a3 = acc0[j + 3];
             quad_transpose_f32(a0, a1, a2, a3, lane);   // now: row c0 + j + qrow, four adjacent features
-            *reinterpret_cast<float4*>(o + static_cast<size_t>(j) * kHidden) = make_float4(a0, a1, a2, a3);
+            // expert parallelism: the row's place in its token owner's memory (plain stores over NVLink)
+            float* o = p.row_out != nullptr ? p.row_out[row0 + j] : p.o_rows + static_cast<size_t>(row0 + j) * kHidden;
+            if (o != nullptr) *reinterpret_cast<float4*>(o + col) = make_float4(a0, a1, a2, a3);
           }
         }
       }
@@ -780,7 +784,7 @@ cudaError_t gemm_set_attributes() {
 cudaError_t launch_gemm1(const GemmLaunch& g, const float* w13_scale, int e_local, const Workspace& ws, int num_sms,
                          cudaStream_t st) {
   GemmArgs a{g.w_packed, ws.work, ws.meta, ws.a_scale, w13_scale, ws.c_hi, ws.c_lo, ws.c_scale, nullptr, ws.row_cap, e_local,
-             ws.ready, ws.status, ws.trace, ws.trace + 6 * 4096, g.wait_limit, g.silent_producer};
+             ws.ready, ws.status, ws.trace, ws.trace + 6 * 4096, g.wait_limit, g.silent_producer, nullptr};
   if (g.token_tile == 128) return launch_gemm<1, 128>(g, a, num_sms, st);
   return g.token_tile == 32 ? launch_gemm<1, 32>(g, a, num_sms, st) : launch_gemm<1, 64>(g, a, num_sms, st);
 }
@@ -788,7 +792,8 @@ cudaError_t launch_gemm1(const GemmLaunch& g, const float* w13_scale, int e_loca
 cudaError_t launch_gemm2(const GemmLaunch& g, const float* w2_scale, int e_local, const Workspace& ws, int num_sms,
                          cudaStream_t st) {
   GemmArgs a{g.w_packed, ws.work, ws.meta, ws.c_scale, w2_scale, nullptr, nullptr, nullptr, ws.o_rows, ws.row_cap, e_local,
-             ws.ready, ws.status, ws.trace + 3 * 4096, ws.trace + 7 * 4096, g.wait_limit, g.silent_producer};
+             ws.ready, ws.status, ws.trace + 3 * 4096, ws.trace + 7 * 4096, g.wait_limit, g.silent_producer,
+             g.rows_to_targets ? ws.row_out : nullptr};
   if (g.token_tile == 128) return launch_gemm<2, 128>(g, a, num_sms, st);
   return g.token_tile == 32 ? launch_gemm<2, 32>(g, a, num_sms, st) : launch_gemm<2, 64>(g, a, num_sms, st);
 }

@@ -97,6 +97,7 @@ struct PairArgs {
   long long* stats;         // [grid][16] cycle counters per CTA (only written by SYFI_PAIR_STATS builds)
   long long wait_limit;     // SM clocks a wait may take before the CTA gives up (tests make it short)
   int silent_producer;      // test hook: the TMA producer issues nothing, so that the other roles' waits run out
+  float* const* row_out;    // mode 2, expert parallelism: row r goes to row_out[r] (a peer's memory; null = padding row, not stored) instead of o_rows
 };
 
 // Optional per-CTA cycle accounting (compile with -DSYFI_PAIR_STATS): where each role spends its time.
@@ -809,14 +810,16 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
 #pragma unroll
         for (int j = 0; j < CN / 2; ++j) f32x2_unpack(acc[j], out[2 * j], out[2 * j + 1]);
         const int qrow = lane & 3;
-        float* o = p.o_rows + static_cast<size_t>(im.row_start + c0 + qrow) * kHidden +
-                   (2 * im.ft + static_cast<int>(rank)) * 128 + q * 32 + (lane >> 2) * 4;
+        const int row0 = im.row_start + c0 + qrow;
+        const int col = (2 * im.ft + static_cast<int>(rank)) * 128 + q * 32 + (lane >> 2) * 4;
 #pragma unroll
         for (int j = 0; j < CN; j += 4) {
           if (c0 + j < n_out) {
             float a0 = out[j], a1 = out[j + 1], a2 = out[j + 2], a3 = out[j + 3];
             quad_transpose_f32(a0, a1, a2, a3, lane);   // now: row c0 + j + qrow, four adjacent features
-            *reinterpret_cast<float4*>(o + static_cast<size_t>(j) * kHidden) = make_float4(a0, a1, a2, a3);
+            // expert parallelism: the row's place in its token owner's memory (plain stores over NVLink)
+            float* o = p.row_out != nullptr ? p.row_out[row0 + j] : p.o_rows + static_cast<size_t>(row0 + j) * kHidden;
+            if (o != nullptr) *reinterpret_cast<float4*>(o + col) = make_float4(a0, a1, a2, a3);
           }
         }
         ST_END(3);
@@ -860,14 +863,15 @@ cudaError_t pair_gemm_set_attributes() {
 cudaError_t launch_pair_gemm1(const PairGemmLaunch& g, const float* w13_scale, int e_local, const Workspace& ws,
                               int num_sms, cudaStream_t st) {
   PairArgs a{ws.work, ws.meta, ws.a_scale, w13_scale, ws.c_hi, ws.c_lo, ws.c_scale, nullptr, ws.row_cap, e_local,
-             ws.ready, ws.status, ws.trace, g.wait_limit, g.silent_producer};
+             ws.ready, ws.status, ws.trace, g.wait_limit, g.silent_producer, nullptr};
   return launch_pair<1>(g, a, num_sms, st);
 }
 
 cudaError_t launch_pair_gemm2(const PairGemmLaunch& g, const float* w2_scale, int e_local, const Workspace& ws,
                               int num_sms, cudaStream_t st) {
   PairArgs a{ws.work, ws.meta, ws.c_scale, w2_scale, nullptr, nullptr, nullptr, ws.o_rows, ws.row_cap, e_local,
-             ws.ready, ws.status, ws.trace + 4096, g.wait_limit, g.silent_producer};
+             ws.ready, ws.status, ws.trace + 4096, g.wait_limit, g.silent_producer,
+             g.rows_to_targets ? ws.row_out : nullptr};
   return launch_pair<2>(g, a, num_sms, st);
 }
 

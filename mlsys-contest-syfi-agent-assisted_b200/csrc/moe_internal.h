@@ -76,6 +76,7 @@ struct Workspace {
   uint8_t* c_lo = nullptr;        // [row_cap, 2048] e4m3 residual term (scale = c_scale / 28)
   float* c_scale = nullptr;       // [16, row_cap]
   float* o_rows = nullptr;        // [row_cap, 7168] f32 per-route expert outputs
+  float** row_out = nullptr;      // [row_cap] expert parallelism: where GEMM2 stores each row (a peer's memory), null = nowhere
   int* ep_ticket = nullptr;       // last-CTA ticket of the expert-parallel exchange kernels (self-resetting)
   size_t bytes = 0;
 };
@@ -91,6 +92,7 @@ struct GemmLaunch {
   int token_tile;      // 32, 64 or 128: token rows per work item, must match the row-list kernel's
   long long wait_limit = 1ll << 32;   // SM clocks a device-side wait may take (about two seconds)
   int silent_producer = 0;            // test hook, see syfi_moe_debug_fault
+  int rows_to_targets = 0;            // GEMM2 stores row r at Workspace::row_out[r] instead of o_rows
 };
 
 // Tensor maps of the CTA-pair GEMM kernels (grouped_gemm_pair.cu): token-side operands use 32-row boxes.
@@ -102,6 +104,7 @@ struct PairGemmLaunch {
   CUtensorMap tm_b1w;
   long long wait_limit = 1ll << 32;   // SM clocks a device-side wait may take (about two seconds)
   int silent_producer = 0;            // test hook, see syfi_moe_debug_fault
+  int rows_to_targets = 0;            // GEMM2 stores row r at Workspace::row_out[r] instead of o_rows
 };
 
 // Programmatic dependent launch: the kernel may be scheduled while its predecessor in the stream is
@@ -164,6 +167,11 @@ void ep_dispatch_route_targets(const syfi_moe_ep_desc& d, uint32_t seq, int** to
 cudaError_t launch_ep_dispatch(const syfi_moe_ep_desc& d, uint32_t seq, const void* hs, const void* hs_scale,
                                int e_local, int expert_offset, const Workspace& ws, void* g_hs, void* g_scale,
                                int num_sms, cudaStream_t st);
+// GEMM2 rows stored straight into the owners' memory: per-row target pointers (ws.row_out) before the GEMMs,
+// flags and the owners' sum over route slots after them
+cudaError_t launch_ep_row_targets(const syfi_moe_ep_desc& d, uint32_t seq, const Workspace& ws, cudaStream_t st);
+cudaError_t launch_ep_raise_final(const syfi_moe_ep_desc& d, uint32_t seq, const Workspace& ws, void* out_bf16,
+                                  cudaStream_t st);
 cudaError_t launch_ep_push_final(const syfi_moe_ep_desc& d, uint32_t seq, const Workspace& ws, void* out_bf16,
                                  int* ticket, cudaStream_t st);
 

@@ -58,19 +58,30 @@ def _worker(rank, world, port, q):
         # The same layouts through the library's peer-memory exchange instead of NCCL.  Six steps in a row, every
         # step on different tokens, no host synchronisation in between, and rank 1 dawdling on the host before
         # some steps so that the ranks run a step apart: a wrong buffer parity, an early flag or a reused receive
-        # slot would hand a rank another step's rows.  Every step must equal the NCCL path bit for bit (two
-        # ranks: the f32 sum of two partials does not depend on the order).
+        # slot would hand a rank another step's rows.  GEMM2 stores every expert row into the token owner's
+        # memory and the owner adds them in route order, so every step must equal, bit for bit, the plain layer
+        # with all 32 experts on one GPU; the NCCL path (partials summed per rank first) agrees within tolerance.
         ok4, s4 = True, "peer exchange unavailable"
+
+        def one_gpu(lg, hs, sc):
+            o = torch.empty(lg.shape[0], 7168, dtype=torch.bfloat16, device=dev)
+            pkg.run_moe(lg, tok[1], hs, sc, fd.gemm1_weights, fd.gemm1_weights_scale, fd.gemm2_weights,
+                        fd.gemm2_weights_scale, 0, 2.5, o)
+            return o
         steps = []
         for i in range(6):
             m = pkg.make_inputs(num_tokens=32, seed=100 + 10 * i + rank, e_local=1, device="cpu")
             steps.append([t.to(dev) for t in (m.routing_logits, m.hidden_states, m.hidden_states_scale)])
+        want_out = [one_gpu(lg, hs, sc) for lg, hs, sc in steps]
         nccl_out = [ep.forward_sharded(lg, tok[1], hs, sc).clone() for lg, hs, sc in steps]
+        ok4 = all(oracle.check_output(a, b)[0] for a, b in zip(nccl_out, want_out))
         rep_tok = []
         for i in range(6):
             m = pkg.make_inputs(num_tokens=256, seed=200 + i, e_local=1, device="cpu")
             rep_tok.append([t.to(dev) for t in (m.routing_logits, m.hidden_states, m.hidden_states_scale)])
+        want_rows = [one_gpu(lg, hs, sc)[rank * r:(rank + 1) * r].clone() for lg, hs, sc in rep_tok]
         nccl_rows = [ep.forward_replicated(lg, tok[1], hs, sc, scatter_rows=True).clone() for lg, hs, sc in rep_tok]
+        ok4 = ok4 and all(oracle.check_output(a, b)[0] for a, b in zip(nccl_rows, want_rows))
         torch.cuda.synchronize()
         import time
         if ep.enable_peer_exchange(32, dev):
@@ -81,8 +92,8 @@ def _worker(rank, world, port, q):
                 ep.forward_sharded(lg, tok[1], hs, sc, outs[i])
             torch.cuda.synchronize()
             pkg.get_context(rank).check()
-            ok4 = all(torch.equal(a, b) for a, b in zip(outs, nccl_out))
-            s4 = [float((a.float() - b.float()).abs().max()) for a, b in zip(outs, nccl_out)]
+            ok4 = ok4 and all(torch.equal(a, b) for a, b in zip(outs, want_out))
+            s4 = [float((a.float() - b.float()).abs().max()) for a, b in zip(outs, want_out)]
             # forward_sharded dispatches tokens by default (only routed rows travel); the all-gather layout
             # shares the region with it: alternate the two, again without host synchronisation
             outs2 = [torch.empty(32, 7168, dtype=torch.bfloat16, device=dev) for _ in range(6)]
@@ -92,7 +103,7 @@ def _worker(rank, world, port, q):
                 ep.forward_sharded(lg, tok[1], hs, sc, outs2[i], dispatch=(i % 2 == 1))
             torch.cuda.synchronize()
             pkg.get_context(rank).check()
-            ok4 = ok4 and all(torch.equal(a, b) for a, b in zip(outs2, nccl_out))
+            ok4 = ok4 and all(torch.equal(a, b) for a, b in zip(outs2, want_out))
         # replicated tokens: the reduce-scatter fused into the combine kernel, against NCCL's reduce-scatter
         ep6 = pkg.ExpertParallelMoe(ep.w13, ep.w13_s, ep.w2, ep.w2_s, off, 2.5)
         if ep6.enable_peer_exchange(256 // world, dev):
@@ -103,8 +114,8 @@ def _worker(rank, world, port, q):
                 ep6.forward_replicated(lg, tok[1], hs, sc, outs[i], scatter_rows=True)
             torch.cuda.synchronize()
             pkg.get_context(rank).check()
-            ok4 = ok4 and all(torch.equal(a, b) for a, b in zip(outs, nccl_rows))
-            s4 = (s4, [float((a.float() - b.float()).abs().max()) for a, b in zip(outs, nccl_rows)])
+            ok4 = ok4 and all(torch.equal(a, b) for a, b in zip(outs, want_rows))
+            s4 = (s4, [float((a.float() - b.float()).abs().max()) for a, b in zip(outs, want_rows)])
         # load-imbalance configuration in miniature: skewed logits (hot experts), per-rank weights,
         # expert offset 32 * rank, replicated tokens, partial outputs summed over the ranks
         skew = pkg.make_inputs(num_tokens=192, seed=0, e_local=32, local_expert_offset=32 * rank, device=dev,
