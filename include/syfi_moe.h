@@ -176,8 +176,8 @@ int syfi_moe_ep_forward(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep, int64_t s
  * the eight expert groups, so at most half of the rows travel to a rank that owns one group), derives the
  * masks and row counts of its experts from the received routes, and runs the layer from the row lists on.
  * Against the all-gather layout: the router runs on tokens_per_rank instead of world_size * tokens_per_rank
- * tokens, no logits cross the link, and only routed rows do.  The return leg (partial rows pushed to the
- * tokens' owners, summed in rank order) is the same.  The two layouts may share a region as long as every
+ * tokens, no logits cross the link, and only routed rows do.  The return leg (GEMM2 storing each expert row
+ * into the memory of the token's owner, see below) is the same.  The two layouts may share a region as long as every
  * rank makes the same sequence of calls.  No counterpart in the reference (moe.cu:182-185 is its only
  * multi-GPU hook). */
 int syfi_moe_ep_forward_dispatch(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep, int64_t step,
@@ -189,14 +189,22 @@ int syfi_moe_ep_forward_dispatch(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep, 
                                  void* stream);
 /* The same exchange for REPLICATED tokens (the large-prefill layout: every rank holds the same
  * world_size * tokens_per_rank tokens and owns a slice of the experts; the reference's
- * local_expert_offset hook, moe.cu:182-185, used as expert parallelism).  No token gather: each rank runs
- * the layer for its experts on all tokens, and the weighted combine writes every token's f32 partial row
- * straight into the receive slot of the rank that owns the token (rank t / tokens_per_rank) — the
- * reduce-scatter is fused into the combine kernel; tokens without a local route send one presence word.
+ * local_expert_offset hook, moe.cu:182-185, used as expert parallelism).  No inbound exchange: each rank runs
+ * the layer for its experts on all tokens.
+ * Return leg of all three expert-parallel entry points: the reduce-scatter is fused into GEMM2.  GEMM2's
+ * epilogue stores every f32 expert row straight into the receive slot [token][k] of the rank that owns the
+ * token (rank t / tokens_per_rank; k = the route's position among the token's eight) with plain stores over
+ * NVLink, so the transfer overlaps the GEMM tile by tile and the rows never make a round trip through local
+ * memory; after GEMM2 a flag goes up on every rank, and each owner computes sum_k weight[k] * row[k] over the
+ * slots that arrived, in route order, and rounds once.  That is the order of the single-GPU combine, so the
+ * result equals the single-GPU layer over the union of the ranks' experts bit for bit, however the experts
+ * are spread.  (The environment variable SYFI_MOE_EP_RETURN=push, set alike on all ranks, selects the earlier
+ * scheme for comparison: rows stay local, a kernel after GEMM2 sums each token's local routes and pushes one
+ * partial row per token, the owners add the partials in rank order.)
  * Inputs: token-side tensors of ALL world_size * tokens_per_rank tokens (identical on every rank);
- * output: bf16 [tokens_per_rank, 7168], the rows of this rank's tokens summed over all ranks in rank
- * order, rounded once.  Same step / region / wait rules as syfi_moe_ep_forward; the two may share a
- * region as long as every rank makes the same sequence of calls. */
+ * output: bf16 [tokens_per_rank, 7168], the rows of this rank's tokens.  Same step / region / wait rules as
+ * syfi_moe_ep_forward; the entry points may share a region as long as every rank makes the same sequence of
+ * calls. */
 int syfi_moe_ep_forward_replicated(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep, int64_t step,
                                    const void* routing_logits, const void* routing_bias, const void* hidden_states,
                                    const void* hidden_states_scale, const void* gemm1_weights,

@@ -1,5 +1,9 @@
 // Expert-parallel exchange over peer memory (NVLink), fused with the layer's own kernels.
 //
+// Return leg (default): GEMM2 stores each expert row into the token owner's memory; see "GEMM2 rows straight
+// into the owners' memory" below (targets / raise / final).  The push / final pair described next is the earlier
+// return leg, kept selectable for comparison.
+//
 // The reference has no multi-GPU path (its only hook is local_expert_offset,
 // moe/solution/cuda/moe.cu:182-185, 250-256).  In the serving layout every rank brings its own T
 // tokens and owns 32 experts; a step is

@@ -10,8 +10,8 @@ expert with one exchange step, the sum of the ranks' partial outputs:
   partials are all-reduced (or reduce-scattered by rows) and rounded to bf16 once.
 * ``forward_sharded`` — every rank brings its own T tokens (the serving layout:
   data-parallel attention, expert-parallel MoE).  Peer-memory path: token dispatch (each rank
-  routes its own tokens, every rank pulls only the rows routed to its experts) and a sparse
-  push of partial rows back to the owners.  NCCL path: token-side tensors are all-gathered,
+  routes its own tokens, every rank pulls only the rows routed to its experts); GEMM2 stores
+  every expert row straight into the memory of the token's owner, which sums them in route order.  NCCL path: token-side tensors are all-gathered,
   each rank runs its experts over the W*T gathered tokens, and a reduce-scatter returns
   to each rank the summed rows of its own tokens.
 
@@ -110,7 +110,7 @@ class ExpertParallelMoe:
         """Tokens replicated on every rank.  Returns bf16 [T, 7168] on every rank, or with
         ``scatter_rows`` this rank's T/W rows of it (T must divide by the world size).  With
         ``scatter_rows`` and the peer-memory path enabled for T/W tokens per rank
-        (:meth:`enable_peer_exchange`), the reduce-scatter is fused into the layer's combine kernel
+        (:meth:`enable_peer_exchange`), the reduce-scatter is fused into GEMM2 (rows stored into the owners' memory)
         (``syfi_moe_ep_forward_replicated``); otherwise NCCL sums the f32 partials."""
         T = logits.shape[0]
         peer = getattr(self, "_peer", None)
