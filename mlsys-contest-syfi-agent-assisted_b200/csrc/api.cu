@@ -39,6 +39,10 @@ struct syfi_moe_ctx {
   // second stream of syfi_moe_forward_host: the hidden states travel while the router runs
   cudaStream_t copy_stream = nullptr;
   cudaEvent_t ev_copy_begin = nullptr, ev_copy_done = nullptr;
+  // third stream of syfi_moe_forward_host for large batches: finished output slices travel back while the next
+  // slice is computed
+  cudaStream_t out_stream = nullptr;
+  cudaEvent_t ev_slice_done = nullptr, ev_out_done = nullptr;
   cudaEvent_t wait_before_gather = nullptr;   // set by forward_host for one call
   // host -> device copies forward_host wants on the second stream; run_layer issues them right after it has
   // launched the router, so that the GPU starts on the router while the host is still queueing the copies
@@ -475,6 +479,9 @@ int syfi_moe_destroy(syfi_moe_ctx* ctx) {
     free_workspace(ctx->ws);
     if (ctx->stage) cudaFree(ctx->stage);
     if (ctx->ep_gather) cudaFree(ctx->ep_gather);
+    if (ctx->out_stream) cudaStreamDestroy(ctx->out_stream);
+    if (ctx->ev_slice_done) cudaEventDestroy(ctx->ev_slice_done);
+    if (ctx->ev_out_done) cudaEventDestroy(ctx->ev_out_done);
     for (cudaEvent_t e : ctx->ev)
       if (e) cudaEventDestroy(e);
     if (ctx->ev_copy_begin) cudaEventDestroy(ctx->ev_copy_begin);
@@ -578,6 +585,58 @@ int syfi_moe_forward_host(syfi_moe_ctx* ctx, const void* routing_logits_host, co
     CU_TRY(cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking));
     CU_TRY(cudaEventCreateWithFlags(&ctx->ev_copy_begin, cudaEventDisableTiming));
     CU_TRY(cudaEventCreateWithFlags(&ctx->ev_copy_done, cudaEventDisableTiming));
+  }
+  // Large batches are cut into slices of kHostSlice tokens that move through a three-stage pipeline: slice
+  // s + 1 travels to the device while slice s is computed and slice s - 1 travels back (PCIe carries both
+  // directions at once).  Tokens are independent and a token's result does not depend on the batch it is
+  // computed in, so the output is bit-identical to the unsliced call; each slice re-reads the active experts'
+  // weights from HBM (about 0.2 ms per 1024-token slice), which is less than a slice's output needs on the
+  // link (0.26 ms), so the call as a whole runs at the speed of the device-to-host copy.
+  constexpr int64_t kHostSlice = 1024;
+  if (T >= 2 * kHostSlice) {
+    if (!ctx->out_stream) {
+      CU_TRY(cudaStreamCreateWithFlags(&ctx->out_stream, cudaStreamNonBlocking));
+      CU_TRY(cudaEventCreateWithFlags(&ctx->ev_slice_done, cudaEventDisableTiming));
+      CU_TRY(cudaEventCreateWithFlags(&ctx->ev_out_done, cudaEventDisableTiming));
+    }
+    // both copy streams start after whatever the caller's stream did before
+    CU_TRY(cudaEventRecord(ctx->ev_copy_begin, st));
+    CU_TRY(cudaStreamWaitEvent(ctx->copy_stream, ctx->ev_copy_begin, 0));
+    CU_TRY(cudaStreamWaitEvent(ctx->out_stream, ctx->ev_copy_begin, 0));
+    CU_TRY(cudaMemcpyAsync(base + o_bias, routing_bias_host, b_bias, cudaMemcpyHostToDevice, ctx->copy_stream));
+    int rc = SYFI_MOE_OK;
+    for (int64_t t0 = 0; t0 < T && rc == SYFI_MOE_OK; t0 += kHostSlice) {
+      const int64_t c = T - t0 < kHostSlice ? T - t0 : kHostSlice;
+      char* d_logits = base + o_logits + (size_t)t0 * kExpertsGlobal * 4;
+      char* d_hs = base + o_hs + (size_t)t0 * kHidden;
+      char* d_hss = base + o_hss + (size_t)t0 * kHBlocks * 4;       // the slice's scales as a [56, c] block of its own
+      char* d_out = base + o_out + (size_t)t0 * kHidden * 2;
+      CU_TRY(cudaMemcpyAsync(d_logits, static_cast<const char*>(routing_logits_host) + (size_t)t0 * kExpertsGlobal * 4,
+                             (size_t)c * kExpertsGlobal * 4, cudaMemcpyHostToDevice, ctx->copy_stream));
+      CU_TRY(cudaMemcpyAsync(d_hs, static_cast<const char*>(hidden_states_host) + (size_t)t0 * kHidden,
+                             (size_t)c * kHidden, cudaMemcpyHostToDevice, ctx->copy_stream));
+      CU_TRY(cudaMemcpy2DAsync(d_hss, (size_t)c * 4, static_cast<const char*>(hidden_states_scale_host) + (size_t)t0 * 4,
+                               (size_t)T * 4, (size_t)c * 4, kHBlocks, cudaMemcpyHostToDevice, ctx->copy_stream));
+      CU_TRY(cudaEventRecord(ctx->ev_copy_done, ctx->copy_stream));
+      CU_TRY(cudaStreamWaitEvent(st, ctx->ev_copy_done, 0));
+      ctx->n_pending = 0;
+      rc = forward_common(ctx, d_logits, base + o_bias, d_hs, d_hss, gemm1_weights, gemm1_weights_scale, gemm2_weights,
+                          gemm2_weights_scale, c, num_local_experts, local_expert_offset, routed_scaling_factor, d_out,
+                          0, stream);
+      if (rc) break;
+      CU_TRY(cudaEventRecord(ctx->ev_slice_done, st));
+      CU_TRY(cudaStreamWaitEvent(ctx->out_stream, ctx->ev_slice_done, 0));
+      CU_TRY(cudaMemcpyAsync(static_cast<char*>(output_host) + (size_t)t0 * kHidden * 2, d_out, (size_t)c * kHidden * 2,
+                             cudaMemcpyDeviceToHost, ctx->out_stream));
+    }
+    // keep the caller's stream ordered behind both copy streams, whatever happened
+    cudaEventRecord(ctx->ev_copy_done, ctx->copy_stream);
+    cudaStreamWaitEvent(st, ctx->ev_copy_done, 0);
+    cudaEventRecord(ctx->ev_out_done, ctx->out_stream);
+    cudaStreamWaitEvent(st, ctx->ev_out_done, 0);
+    if (rc) return rc;
+    CU_TRY(cudaStreamSynchronize(st));
+    return SYFI_MOE_OK;
   }
   // Pinned (page-locked) host buffers are mapped into the device's address space: the router then reads
   // its 64 KB of logits straight from them and the combine kernel writes the output rows straight into

@@ -407,6 +407,25 @@ def test_host_entry_point_matches_device_entry_point(pinned, pkg):
         assert torch.equal(out.view(torch.int16), dev_out.cpu().view(torch.int16))
 
 
+@pytest.mark.parametrize("pinned", [True, False])
+def test_host_entry_point_in_slices_matches_device_entry_point(pinned, pkg):
+    """From 2048 tokens on the host entry point works in slices of 1024 tokens (copy in, compute and copy out
+    overlap); 2500 tokens make two full slices and a ragged one.  Bit-identical to the device entry point on the
+    whole batch, twice in a row on the same staging area."""
+    T = 2500
+    inp = pkg.make_inputs(num_tokens=T, seed=17, e_local=8, device=DEV)
+    dev_out, _ = _run(pkg, inp)
+    place = (lambda t: t.pin_memory()) if pinned else (lambda t: t.clone())
+    host = [place(t.cpu()) for t in (inp.routing_logits, inp.routing_bias, inp.hidden_states,
+                                     inp.hidden_states_scale)]
+    for _ in range(2):
+        out = place(torch.full((T, 7168), float("nan"), dtype=torch.bfloat16))
+        pkg.run_moe_host(*host, inp.gemm1_weights, inp.gemm1_weights_scale, inp.gemm2_weights,
+                         inp.gemm2_weights_scale, 0, 2.5, out)
+        pkg.get_context(0).check()
+        assert torch.equal(out.view(torch.int16), dev_out.cpu().view(torch.int16))
+
+
 def test_zero_tokens_is_a_no_op(pkg):
     inp = pkg.make_inputs(num_tokens=0, seed=0, e_local=2, device=DEV)
     out = torch.empty(0, 7168, dtype=torch.bfloat16, device=DEV)
