@@ -490,6 +490,22 @@ def main():
         def e2e_step():
             pkg.run_moe_host(*h_in, inp.gemm1_weights, inp.gemm1_weights_scale, inp.gemm2_weights,
                              inp.gemm2_weights_scale, inp.local_expert_offset, inp.routed_scaling_factor, h_out)
+    elif peer_ok:
+        # N GPUs end to end: every rank's host holds its own T/N tokens (the serving layout); they travel in, the
+        # ranks exchange the routed rows (token dispatch), and every rank's own output rows travel back
+        mine = slice(rank * (T // world), (rank + 1) * (T // world))
+        d_in = [inp.routing_logits[mine].contiguous(), inp.routing_bias, inp.hidden_states[mine].contiguous(),
+                inp.hidden_states_scale[:, mine].contiguous()]
+        h_in = [t.cpu().pin_memory() for t in d_in]
+        h2d = sum(t.numel() * t.element_size() for t in h_in) * world
+        d2h = h_out.numel() * h_out.element_size() * world
+
+        def e2e_step():
+            for d, h in zip(d_in, h_in):
+                d.copy_(h, non_blocking=True)
+            ep.forward_sharded(d_in[0], d_in[1], d_in[2], d_in[3], out, dispatch=True)
+            h_out.copy_(out, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
     else:
         d_in = [inp.routing_logits, inp.routing_bias, inp.hidden_states, inp.hidden_states_scale]
 
@@ -578,7 +594,12 @@ def main():
                        "workspace_bytes": ctx.workspace_bytes() if hasattr(ctx, "workspace_bytes") else None},
             "clocks": clocks,
             "e2e": {"value": T / (e2e_ms / 1e3), "unit": UNIT, "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": Ke},
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": Ke,
+                    "path": ("syfi_moe_forward_host: pinned host buffers, slices of 1024 tokens pipelined over three streams"
+                             if world == 1 else
+                             ("every rank's own T/N tokens from pinned host memory, token dispatch between the ranks, own "
+                              "output rows back; bytes are totals over the ranks" if peer_ok else
+                              "all tokens to every rank, NCCL reduce-scatter, own rows back"))},
             "gpu_launches": launches, "roofline": roofline}
     if parity is not None:
         line["parity"] = parity
