@@ -281,6 +281,29 @@ def run_moe(routing_logits, routing_bias, hidden_states, hidden_states_scale, ge
     return output
 
 
+def _register_torch_op():
+    """Expose the layer as a torch operator, ``torch.ops.syfi_moe.run_moe`` (destination-passing like the
+    reference's entry point: it mutates ``output`` and returns nothing), so that code built on the dispatcher
+    — torch.compile graphs, operator registries of serving stacks — can call it like any other op.  The
+    operator is a thin layer over :func:`run_moe`; the C ABI underneath stays the boundary other languages
+    bind."""
+    try:
+        @torch.library.custom_op("syfi_moe::run_moe", mutates_args=("output",), device_types="cuda")
+        def _op(routing_logits: torch.Tensor, routing_bias: torch.Tensor, hidden_states: torch.Tensor,
+                hidden_states_scale: torch.Tensor, gemm1_weights: torch.Tensor, gemm1_weights_scale: torch.Tensor,
+                gemm2_weights: torch.Tensor, gemm2_weights_scale: torch.Tensor, local_expert_offset: int,
+                routed_scaling_factor: float, output: torch.Tensor) -> None:
+            run_moe(routing_logits, routing_bias, hidden_states, hidden_states_scale, gemm1_weights,
+                    gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, local_expert_offset,
+                    routed_scaling_factor, output)
+        return _op
+    except Exception:      # an older torch without custom_op: the plain function remains
+        return None
+
+
+torch_op = _register_torch_op()
+
+
 class PackedWeights:
     """Weights rewritten by :func:`prepack_weights`: the two packed byte tensors (same sizes as the
     originals) and the expert count.  Pass ``packed.gemm1`` / ``packed.gemm2`` to :func:`run_moe_prepacked`

@@ -117,3 +117,13 @@ def test_tvm_ffi_binding_exports_the_reference_symbol(pkg):
     assert path and os.path.exists(path)
     lib = ctypes.CDLL(path)
     assert hasattr(lib, "__tvm_ffi_run_moe")
+
+
+def test_layer_is_registered_as_a_torch_operator(pkg):
+    """`torch.ops.syfi_moe.run_moe` exists after importing the package: eleven arguments in the order of the
+    reference's run_moe, mutating the last one."""
+    import torch
+    op = torch.ops.syfi_moe.run_moe
+    schema = str(op.default._schema)
+    assert "Tensor(a10!) output" in schema and schema.rstrip().endswith("-> ()"), schema
+    assert schema.count("Tensor") == 9

@@ -426,6 +426,16 @@ def test_host_entry_point_in_slices_matches_device_entry_point(pinned, pkg):
         assert torch.equal(out.view(torch.int16), dev_out.cpu().view(torch.int16))
 
 
+def test_torch_operator_gives_the_same_bits(pkg):
+    """The layer through the torch dispatcher (`torch.ops.syfi_moe.run_moe`) against the plain function."""
+    inp = pkg.make_inputs(num_tokens=48, seed=19, e_local=8, device=DEV)
+    want, _ = _run(pkg, inp)
+    got = torch.full((48, 7168), float("nan"), dtype=torch.bfloat16, device=DEV)
+    assert torch.ops.syfi_moe.run_moe(*inp.args(), got) is None
+    pkg.get_context(0).check()
+    assert torch.equal(got, want)
+
+
 def test_zero_tokens_is_a_no_op(pkg):
     inp = pkg.make_inputs(num_tokens=0, seed=0, e_local=2, device=DEV)
     out = torch.empty(0, 7168, dtype=torch.bfloat16, device=DEV)
