@@ -61,15 +61,10 @@ template <int MODE> struct PairCfg {
   static constexpr int kFeatItems = MODE == 1 ? kInter / 128 : kHidden / 256;   // 16 / 28 per expert and token tile
   static constexpr int kTokTile = MODE == 1 ? 256 : 128;
   static constexpr int kStages = 6;
-  // Accumulator slots in tensor memory.  Mode 1 issues a K block as two MMA groups of N = 128 (features
-  // 0..63 and 64..127 of the tile, up and gate each) into four slots of 128 columns: a slot is needed again
-  // three groups later, which leaves the hand-off MMA -> promotion -> MMA three quarters of the buffered
-  // MMA time instead of half (measured round trip: ~1500 cycles against ~700 cycles of MMA per K block).
-#ifndef PAIR_HALVES
-#define PAIR_HALVES 1
-#endif
-  static constexpr int kHalves = MODE == 1 ? PAIR_HALVES : 1;   // MMA groups (accumulator slots) per K block
-  static constexpr int kSlots = 2 * kHalves;
+  // Two accumulator slots of 256 tensor-memory columns: the MMAs of K block k + 1 run while block k is
+  // promoted.  (Four slots of 128 columns, a K block issued as two MMA groups of N = 128, doubled the
+  // hand-offs between the MMA thread and the promotion warps and were slower.)
+  static constexpr int kSlots = 2;
   static constexpr int kSlotCols = kPairTmemCols / kSlots;
   static constexpr int kScaleEntry = 128;   // floats per ring entry: one per token lane (mode 1) / token column (mode 2)
   // mode 1: the activation scales of a whole item, [56][128]; mode 2: a ring of K blocks of scale products
@@ -117,23 +112,6 @@ struct PairArgs {
 #define ST_WRITE(base, cond) do { } while (0)
 #endif
 
-// Optional timeline of cluster 0's first CTA (compile with -DSYFI_PAIR_TRACE): (tag, clock) pairs per role,
-// role r at p.stats[8192 + r * 4096 ...].
-#ifdef SYFI_PAIR_TRACE
-#define TR_DECL int tr_n = 0
-#define TR(role, tag)                                                                 \
-  do {                                                                                \
-    if (blockIdx.x == 0 && p.stats != nullptr && tr_n < 2040) {                       \
-      p.stats[8192 + (role) * 4096 + 2 * tr_n] = (tag);                               \
-      p.stats[8192 + (role) * 4096 + 2 * tr_n + 1] = clock64();                       \
-      ++tr_n;                                                                         \
-    }                                                                                 \
-  } while (0)
-#else
-#define TR_DECL do { } while (0)
-#define TR(role, tag) do { } while (0)
-#endif
-
 struct PItem {
   int expert, ft, row_start, n;
 };
@@ -178,7 +156,6 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   constexpr int SE = C::kScaleEntry;
   constexpr int kSlots = C::kSlots;
   constexpr int kSlotCols = C::kSlotCols;
-  constexpr int H = C::kHalves;
   constexpr int kIssuers = MODE == 1 ? 2 : 1;   // MMA-issuing threads (see mma_role)
 
   extern __shared__ uint8_t smem_raw[];
@@ -265,48 +242,36 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
   // independent, and tcgen05.commit tracks the MMAs of the committing thread only, so each issuer commits its
   // own slot and its own half of the stage pair (empty[] counts two arrivals).
   auto mma_role = [&](const uint32_t par) {
-    uint32_t g = par, ph = 0, sph = 0;      // this issuer's next stage and its phase, phase of its slot(s)
-    uint32_t slot = par * H;                // mode 2 (one issuer): alternates between the two slots
+    uint32_t g = par, ph = 0, sph = 0;      // this issuer's next stage and its phase, phase of its slot
+    uint32_t slot = par;                    // mode 2 (one issuer): alternates between the two slots
     int e_hint = 0;
     bool alive = true;
     ST_DECL;
-    TR_DECL;
     const long long st_start = clock64();
     (void)st_start;
     for (int i = 0; i < my_items && alive; ++i) {
       const PItem im = decode_pair_item<FI, NT>(s_work, p.e_local, item_of(i), e_hint);
-      const uint32_t idesc = umma_idesc_e4m3_m256(MODE == 1 ? 256u / H : 2u * im.n);
+      const uint32_t idesc = umma_idesc_e4m3_m256(MODE == 1 ? 256u : 2u * im.n);
       for (int kb = static_cast<int>(par); kb < KB; kb += kIssuers) {
         ST_BEGIN();
         if (!mbar_wait_bounded_tell(&full[g], ph, s_abort, peer_abort, kStatusWaitTimeoutMma, p.wait_limit)) { alive = false; break; }
         ST_END(0);
         const uint32_t sb = smem_u32(smem + g * kStageBytes);
         const uint64_t a0 = umma_smem_desc_sw128(sb);
+        const uint64_t b0 = umma_smem_desc_sw128(sb + kTile);
+        ST_BEGIN();
+        if (!mbar_wait_bounded_tell(&tempty[slot], sph ^ 1u, s_abort, peer_abort, kStatusWaitTimeoutMma, p.wait_limit)) { alive = false; break; }
+        ST_END(1);
+        tc_fence_after();
+        const uint32_t d0 = tmem_base + slot * kSlotCols;
 #pragma unroll
-        for (int h = 0; h < H; ++h) {
-          const uint32_t sl = slot + h;
-          ST_BEGIN();
-          if (!mbar_wait_bounded_tell(&tempty[sl], sph ^ 1u, s_abort, peer_abort, kStatusWaitTimeoutMma, p.wait_limit)) { alive = false; break; }
-          ST_END(1);
-          if (MODE == 1 && par == 0) TR(0, 1);       // operands and slot are there
-          tc_fence_after();
-          const uint64_t b0 = umma_smem_desc_sw128(sb + kTile + h * (kTile / H));
-          const uint32_t d0 = tmem_base + sl * kSlotCols;
-#pragma unroll
-#ifndef PAIR_NO_MMA
-          for (int k4 = 0; k4 < 4; ++k4) umma_f8_pair(d0, a0 + 2 * k4, b0 + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
-#else
-          (void)a0; (void)b0; (void)d0; (void)idesc;
-#endif
-          if (h == H - 1 && (kIssuers == 2 || (g & 1u))) umma_commit_pair(&empty[g >> 1], 3);
-          umma_commit_pair(&tfull[sl], 3);
-          if (MODE == 1 && par == 0) TR(0, 2);       // issued and committed
-        }
-        if (!alive) break;
+        for (int k4 = 0; k4 < 4; ++k4) umma_f8_pair(d0, a0 + 2 * k4, b0 + 2 * k4, idesc, k4 > 0 ? 1u : 0u);
+        if (kIssuers == 2 || (g & 1u)) umma_commit_pair(&empty[g >> 1], 3);
+        umma_commit_pair(&tfull[slot], 3);
         if (kIssuers == 2) {
           sph ^= 1u;
         } else {
-          slot ^= static_cast<uint32_t>(H);
+          slot ^= 1u;
           if (slot == 0) sph ^= 1u;
         }
         g += kIssuers;
@@ -401,30 +366,18 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
             if (!mbar_wait_bounded_tell(&empty[g >> 1], ph ^ 1u, s_abort, peer_abort, kStatusWaitTimeoutProducer,
                                         p.wait_limit)) { alive = false; break; }
             ST_END(0);
-#ifdef PAIR_NO_LOAD
-            if (rank == 0) { mbar_arrive(&full[g]); mbar_arrive(&full[g + 1]); }
-#else
             if (rank == 0) {
               mbar_arrive_expect_tx(&full[g], stage_tx);
               mbar_arrive_expect_tx(&full[g + 1], stage_tx);
             }
-#endif
             // boxes that continue each other along K are issued back to back (a row's 256 contiguous
             // bytes are served by L2 far faster than two separate 128-byte visits)
             uint8_t* st0 = smem + g * kStageBytes;
             uint8_t* st1 = st0 + kStageBytes;
             const int x0 = kb * 128;
-#ifndef PAIR_NO_LOAD
             tma_load_2d_pair(st0 + w_off, &tm_w, full0[g], x0, wrow, pol_w);
             tma_load_2d_pair(st1 + w_off, &tm_w, full0[g + 1], x0 + 128, wrow, pol_w);
-#endif
-            for (int b = 0; b < (
-#ifdef PAIR_NO_LOAD
-                                 0
-#else
-                                 boxes
-#endif
-                                 ); ++b) {
+            for (int b = 0; b < boxes; ++b) {
               tma_load_2d_pair(st0 + tok_off + b * box_pitch, mb, full0[g], x0, my_row + box_rows * b, pol_b);
               tma_load_2d_pair(st1 + tok_off + b * box_pitch, mb, full0[g + 1], x0 + 128, my_row + box_rows * b, pol_b);
             }
@@ -571,7 +524,6 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     int e_hint = 0;
     const uint64_t inv_ratio = f32x2_pack(1.0f / kLoRatio, 1.0f / kLoRatio);
     ST_DECL;
-    TR_DECL;
     const long long st_start = clock64();
     (void)st_start; (void)inv_ratio; (void)wp;
 
@@ -604,79 +556,38 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
           // item, see the end of the previous item) times the weight scales of the up and the gate block
           const float a = s_scale[kb * 128 + tl];
           const float su = a * ws[kb], sg = a * ws[64 + kb];
+          ST_BEGIN();
+          if (!mbar_wait_bounded_tell(&tfull[sl], sph, s_abort, peer_abort, kStatusWaitTimeoutEpilogue, p.wait_limit)) { ok = false; break; }
+          ST_END(0);
+          tc_fence_after();
 #ifdef SYFI_PAIR_STATS
-          long long st_p0 = 0;
+          const long long st_p0 = clock64();
 #endif
-          // H accumulator groups per K block; group h holds features (128 / H) h .. of the tile, up at columns
-          // 0 .. 128 / H - 1 and gate behind them; this thread owns UC = 32 / H of them per group
-          constexpr int UC = 32 / H;
+          const uint32_t t0 = lane_addr + sl * kSlotCols + grp * 32;
+          // scalar FMAs (measured faster here than packed f32x2 ones, whose operand pairs cost extra moves);
+          // the slot goes back to the MMA thread as soon as its last values are in registers
 #pragma unroll
-          for (int h = 0; h < H; ++h) {
-            ST_BEGIN();
-            if (!mbar_wait_bounded_tell(&tfull[sl], sph, s_abort, peer_abort, kStatusWaitTimeoutEpilogue, p.wait_limit)) { ok = false; break; }
-            ST_END(0);
-            if (warp == 4 && lane == 0) TR(1, 1);     // accumulator complete
-            tc_fence_after();
-#ifdef SYFI_PAIR_STATS
-            st_p0 = clock64();
-#endif
-            const uint32_t t0 = lane_addr + sl * kSlotCols + grp * UC;
-#ifndef PAIR_NO_PROMOTE
-            // scalar FMAs (measured faster here than packed f32x2 ones, whose operand pairs cost extra moves);
-            // the slot goes back to the MMA thread as soon as its last values are in registers
-#if defined(PAIR_LD2)
-            // sixteen up and sixteen gate columns per round: two loads in flight
-#pragma unroll
-            for (int c = 0; c < UC / 16; ++c) {
-              uint32_t ru[16], rg[16];
-              tmem_ld16(t0 + c * 16, ru);
-              tmem_ld16(t0 + 128 / H + c * 16, rg);
-              tmem_ld_wait();
-              if (c == UC / 16 - 1) {
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster_relaxed(mapa_tempty + 8u * sl);
-              }
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                up[h * UC + c * 16 + j] = fmaf(__uint_as_float(ru[j]), su, up[h * UC + c * 16 + j]);
-                gt[h * UC + c * 16 + j] = fmaf(__uint_as_float(rg[j]), sg, gt[h * UC + c * 16 + j]);
-              }
+          for (int c = 0; c < 4; ++c) {
+            const bool is_gate = c >= 2;
+            const int cc = c & 1;
+            uint32_t r[16];
+            tmem_ld16(t0 + (is_gate ? 128 : 0) + cc * 16, r);
+            tmem_ld_wait();
+            if (c == 3) {
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive_cluster_relaxed(mapa_tempty + 8u * sl);
             }
-#else
 #pragma unroll
-            for (int c = 0; c < 2 * UC / 16; ++c) {
-              const bool is_gate = c >= UC / 16;
-              const int cc = is_gate ? c - UC / 16 : c;
-              uint32_t r[16];
-              tmem_ld16(t0 + (is_gate ? 128 / H : 0) + cc * 16, r);
-              tmem_ld_wait();
-              if (c == 2 * UC / 16 - 1) {
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster_relaxed(mapa_tempty + 8u * sl);
-                if (warp == 4 && lane == 0) TR(1, 3);     // slot released
-              }
-#pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                if (!is_gate) up[h * UC + cc * 16 + j] = fmaf(__uint_as_float(r[j]), su, up[h * UC + cc * 16 + j]);
-                else gt[h * UC + cc * 16 + j] = fmaf(__uint_as_float(r[j]), sg, gt[h * UC + cc * 16 + j]);
-              }
+            for (int j = 0; j < 16; ++j) {
+              if (!is_gate) up[cc * 16 + j] = fmaf(__uint_as_float(r[j]), su, up[cc * 16 + j]);
+              else gt[cc * 16 + j] = fmaf(__uint_as_float(r[j]), sg, gt[cc * 16 + j]);
             }
-#endif
-#else
-            up[h] = su; gt[h] = sg; (void)t0;
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster_relaxed(mapa_tempty + 8u * sl);
-#endif
-            if (++sl == kSlots) { sl = 0; sph ^= 1u; }
-#ifdef SYFI_PAIR_STATS
-            st_acc[2] += clock64() - st_p0;
-#endif
-            if (warp == 4 && lane == 0) TR(1, 4);     // promoted
           }
-          if (!ok) break;
+          if (++sl == kSlots) { sl = 0; sph ^= 1u; }
+#ifdef SYFI_PAIR_STATS
+          st_acc[2] += clock64() - st_p0;
+#endif
         }
         if (ok) {   // the weight scales go back to the producer
           __syncwarp();
@@ -736,18 +647,11 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
             hw[j] = hp;
             lw[j] = lp;
           }
-          // c[h * UC ..] are features (128 / H) h + UC grp .. of the tile: H chunks of UC bytes per term
-          constexpr int UC = 32 / H;
-#pragma unroll
-          for (int h = 0; h < H; ++h) {
-            const size_t off = row * kInter + static_cast<size_t>(im.ft) * 128 + h * (128 / H) + grp * UC;
-#pragma unroll
-            for (int v = 0; v < UC / 16; ++v) {
-              const int w0 = (h * UC + v * 16) / 4;
-              *reinterpret_cast<uint4*>(p.c_hi + off + v * 16) = make_uint4(hw[w0], hw[w0 + 1], hw[w0 + 2], hw[w0 + 3]);
-              *reinterpret_cast<uint4*>(p.c_lo + off + v * 16) = make_uint4(lw[w0], lw[w0 + 1], lw[w0 + 2], lw[w0 + 3]);
-            }
-          }
+          const size_t off = row * kInter + static_cast<size_t>(im.ft) * 128 + grp * 32;
+          *reinterpret_cast<uint4*>(p.c_hi + off) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+          *reinterpret_cast<uint4*>(p.c_hi + off + 16) = make_uint4(hw[4], hw[5], hw[6], hw[7]);
+          *reinterpret_cast<uint4*>(p.c_lo + off) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+          *reinterpret_cast<uint4*>(p.c_lo + off + 16) = make_uint4(lw[4], lw[5], lw[6], lw[7]);
         }
         named_bar_sync(1 + q, 128);             // the next item's scales are in place, the amax exchange is free
         // hand the item to the publisher warp (see grouped_gemm.cu)
@@ -774,6 +678,8 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
 #endif
           const float* sc = s_scale + s * SE + c0;
           const uint32_t t0 = lane_addr + sl * kSlotCols + c0;
+          // (handing the slot back before the arithmetic of the last chunk, as mode 1 does, costs registers
+          // here and was slower: 400 us against 359 us)
 #pragma unroll
           for (int ch = 0; ch < CN / 16; ++ch) {
             if (c0 + ch * 16 < n) {

@@ -276,30 +276,15 @@ __device__ __forceinline__ bool mbar_wait_bounded_pair(uint64_t* bar, uint32_t p
   }
 }
 // The same for barriers that only this CTA's threads, its own loads or tcgen05.commit signal (CTA-scope
-// acquire), still telling the partner when it gives up.
-__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-#ifdef PAIR_SPIN
-#define PAIR_POLL mbar_test_wait
-#else
-#define PAIR_POLL mbar_try_wait
-#endif
+// acquire), still telling the partner when it gives up.  (Polling with mbarrier.test_wait instead of
+// try_wait was measured and changed nothing.)
 __device__ __forceinline__ bool mbar_wait_bounded_tell(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                                        uint32_t peer_abort_cluster_addr, int code,
                                                        long long limit_cycles = (1ll << 31)) {
-  if (PAIR_POLL(bar, parity)) return true;
+  if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (true) {
-    if (PAIR_POLL(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) return true;
     if (*abort_flag != 0) return false;
     if (clock64() - t0 > limit_cycles) {
       *abort_flag = code;
