@@ -60,18 +60,29 @@ build_rows_kernel(int T, int e_local, int expert_offset, const uint32_t* __restr
   }
 
   int base = 0;
+  // The token's mask and its eight routes are requested together (the routes are only needed when the mask
+  // hits, but asking afterwards costs a second dependent round trip per pass), and one pass ahead: a pass is
+  // a round trip to L2 plus two barriers, and with the next pass's loads already in flight only the barriers
+  // remain on the critical path.
+  uint32_t m_nx = 0;
+  int4 r0_nx = make_int4(-1, -1, -1, -1), r1_nx = r0_nx;
+  auto request = [&](int t) {
+    m_nx = 0;
+    r0_nx = make_int4(-1, -1, -1, -1);
+    r1_nx = r0_nx;
+    if (t < T) {
+      m_nx = local_mask[t];
+      const int4* rp = reinterpret_cast<const int4*>(topk_idx + t * kTopK);
+      r0_nx = __ldg(rp);
+      r1_nx = __ldg(rp + 1);
+    }
+  };
+  request(tid);
   for (int t0 = 0; t0 < T; t0 += kBuildThreads) {
     const int t = t0 + tid;
-    // the token's mask and its eight routes are requested together (the routes are only needed when the
-    // mask hits, but asking afterwards costs a second dependent round trip per pass)
-    uint32_t m = 0;
-    int4 r0 = make_int4(-1, -1, -1, -1), r1 = r0;
-    if (t < T) {
-      m = local_mask[t];
-      const int4* rp = reinterpret_cast<const int4*>(topk_idx + t * kTopK);
-      r0 = __ldg(rp);
-      r1 = __ldg(rp + 1);
-    }
+    const uint32_t m = m_nx;
+    const int4 r0 = r0_nx, r1 = r1_nx;
+    request(t + kBuildThreads);
     const bool has = (m >> e) & 1u;
     const unsigned b = __ballot_sync(0xffffffffu, has);
     if (lane == 0) s_warp[warp] = __popc(b);
