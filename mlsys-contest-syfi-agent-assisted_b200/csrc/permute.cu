@@ -10,6 +10,8 @@
 // token t in expert e is the number of earlier tokens with bit e set; CTA e computes
 // that with ballots.  Every expert's row range is padded to a multiple of 16 rows
 // (the tcgen05 N granularity), padding rows carry token -1 and zero data.
+#include <cstdlib>
+
 #include "moe_internal.h"
 #include "ptx.cuh"
 
@@ -27,6 +29,8 @@ build_rows_kernel(int T, int e_local, int expert_offset, const uint32_t* __restr
                   int token_tile, int* __restrict__ status, int* __restrict__ ready, int* __restrict__ counts_last) {
   __shared__ int s_warp[kBuildThreads / 32];
   const int e = blockIdx.x;
+  // large batches: gridDim.y CTAs share an expert, each ranks one contiguous range of the tokens
+  const int split = blockIdx.y, splits = gridDim.y;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   pdl_wait();
   pdl_trigger();
@@ -52,14 +56,31 @@ build_rows_kernel(int T, int e_local, int expert_offset, const uint32_t* __restr
   const int cnt_pad = (cnt + kRowPad - 1) / kRowPad * kRowPad;
   // the GEMM1 -> GEMM2 readiness counters start every call at zero (nothing of the previous call is
   // still running: the router in front of this kernel is an ordinary launch)
-  if (tid == 0) { ready[e] = 0; counts_last[e] = cnt; }
-  if (e == 0 && tid >= e_local && tid < kMaxLocalExperts) { ready[tid] = 0; counts_last[tid] = 0; }
+  if (split == 0) {
+    if (tid == 0) { ready[e] = 0; counts_last[e] = cnt; }
+    if (e == 0 && tid >= e_local && tid < kMaxLocalExperts) { ready[tid] = 0; counts_last[tid] = 0; }
+  }
   if (rows_total > row_cap) {  // sizing bug: refuse to write out of bounds
-    if (tid == 0) { atomicExch(status, kStatusBadIndex); if (e == 0) { meta[0] = 0; meta[1] = 0; meta[2] = 0; meta[3] = 0; } }
+    if (tid == 0 && split == 0) { atomicExch(status, kStatusBadIndex); if (e == 0) { meta[0] = 0; meta[1] = 0; meta[2] = 0; meta[3] = 0; } }
     return;
   }
 
+  // this CTA's token range, and the expert's rows among the tokens before it: one coalesced sweep over their
+  // masks (4 bytes per token) and a block-wide sum, instead of ranking them pass by pass
+  const int per = ((T + splits * kBuildThreads - 1) / (splits * kBuildThreads)) * kBuildThreads;
+  const int t_begin = min(T, split * per), t_end = min(T, t_begin + per);
   int base = 0;
+  if (split > 0) {
+    int mine = 0;
+    for (int t = tid; t < t_begin; t += kBuildThreads) mine += (local_mask[t] >> e) & 1u;
+    mine = __reduce_add_sync(full, mine);
+    if (lane == 0) s_warp[warp] = mine;
+    __syncthreads();
+#pragma unroll
+    for (int w = 0; w < kBuildThreads / 32; ++w) base += s_warp[w];
+    __syncthreads();
+  }
+
   // The token's mask and its eight routes are requested together (the routes are only needed when the mask
   // hits, but asking afterwards costs a second dependent round trip per pass), and one pass ahead: a pass is
   // a round trip to L2 plus two barriers, and with the next pass's loads already in flight only the barriers
@@ -77,8 +98,8 @@ build_rows_kernel(int T, int e_local, int expert_offset, const uint32_t* __restr
       r1_nx = __ldg(rp + 1);
     }
   };
-  request(tid);
-  for (int t0 = 0; t0 < T; t0 += kBuildThreads) {
+  request(t_begin + tid);
+  for (int t0 = t_begin; t0 < t_end; t0 += kBuildThreads) {
     const int t = t0 + tid;
     const uint32_t m = m_nx;
     const int4 r0 = r0_nx, r1 = r1_nx;
@@ -106,6 +127,7 @@ build_rows_kernel(int T, int e_local, int expert_offset, const uint32_t* __restr
     base += block_total;
     __syncthreads();
   }
+  if (split != 0) return;
   for (int r = cnt + tid; r < cnt_pad; r += kBuildThreads) row_token[row_off + r] = -1;
   if (tid == 0) {
     ExpertWork ew;
@@ -159,7 +181,11 @@ cudaError_t launch_build_rows(int T, int e_local, int expert_offset, int token_t
     return launch_dependent(build_rows_kernel<256>, dim3(e_local), dim3(256), 0, st, T, e_local, expert_offset,
                             ws.local_mask, ws.counts, ws.topk_idx, ws.row_token, ws.route_row, ws.work, ws.meta,
                             ws.row_cap, token_tile, ws.status, ws.ready, ws.counts_last);
-  return launch_dependent(build_rows_kernel<1024>, dim3(e_local), dim3(1024), 0, st, T, e_local, expert_offset,
+  // from 4096 tokens on, four CTAs per expert (each ranks a quarter of the tokens after counting the expert's
+  // rows in the quarters before it): 18 -> about 8 us at 8192 tokens
+  int splits = T >= 4096 ? 4 : 1;
+  if (const char* v = getenv("SYFI_DEBUG_ROW_SPLITS")) splits = atoi(v) > 0 ? atoi(v) : splits;
+  return launch_dependent(build_rows_kernel<1024>, dim3(e_local, splits), dim3(1024), 0, st, T, e_local, expert_offset,
                           ws.local_mask, ws.counts, ws.topk_idx, ws.row_token, ws.route_row, ws.work, ws.meta,
                           ws.row_cap, token_tile, ws.status, ws.ready, ws.counts_last);
 }

@@ -11,9 +11,10 @@ CUDA submission, moe/solution/cuda/moe.cu, graded against it by an external
 harness, moe/scripts/debug_correctness.py:39-55); it ships in the third-party
 package flashinfer-python 0.6.11.post2 as
 ``flashinfer/trace/templates/moe.py`` (routing at :139-170, expert math at
-:56-100).  The restatement keeps that file's operation order so routing is
-bit-identical on the same host, and only differs in dequantising just the
-experts that received tokens (the published reference dequantises all of them).
+:56-100).  The restatement keeps that file's operation order, and differs in two places:
+it dequantises just the experts that received tokens (the published reference
+dequantises all of them), and on the host it cross-checks the router's float32
+sigmoid against a float64 evaluation (see route()).
 
 Pinning: ``tests/golden/make_golden.py`` runs the published reference function
 in a container that has flashinfer installed and stores its routing and output
@@ -44,6 +45,15 @@ def route(routing_logits, routing_bias, routed_scaling_factor, top_k=8, n_group=
     bias = routing_bias.to(torch.float32).reshape(-1)
     T, E = logits.shape
     s = 1.0 / (1.0 + torch.exp(-logits))
+    if logits.device.type == "cpu":
+        # The float32 vector exp of one host was seen to be off by 1e-5 in one process out of fourteen (a token
+        # whose fourth and fifth group scores differ by 78 ulp changed groups), and a checker must not be the
+        # flaky part: the float32 evaluation (the published reference's) is kept when it agrees with a float64
+        # evaluation to a few ulp, which it does on a sound host, and replaced by the rounded float64 values
+        # otherwise.
+        s64 = (1.0 / (1.0 + torch.exp(-logits.to(torch.float64)))).to(torch.float32)
+        if not torch.allclose(s, s64, rtol=1e-6, atol=0.0):
+            s = s64
     biased = s + bias
     gsz = E // n_group
     grouped = biased.view(T, n_group, gsz)
@@ -157,5 +167,11 @@ def check_routing(topk_idx, topk_w, ref_idx, ref_w, w_rtol=1e-5, w_atol=1e-6):
     a_w = topk_w.detach().cpu().float().gather(1, a_ord)
     b_w = ref_w.detach().cpu().float().gather(1, b_ord)
     w_ok = bool(torch.allclose(a_w, b_w, rtol=w_rtol, atol=w_atol)) if same else False
-    bad = int((a_idx != b_idx).any(dim=1).sum())
-    return same and w_ok, {"idx_equal": same, "weights_close": w_ok, "tokens_differing": bad}
+    differ = (a_idx != b_idx).any(dim=1)
+    bad = int(differ.sum())
+    stats = {"idx_equal": same, "weights_close": w_ok, "tokens_differing": bad}
+    if bad:      # the first token whose expert sets differ, for the report
+        t = int(torch.nonzero(differ)[0])
+        stats["first_differing_token"] = {"token": t, "got": a_idx[t].tolist(), "want": b_idx[t].tolist(),
+                                          "got_w": [float(x) for x in a_w[t]], "want_w": [float(x) for x in b_w[t]]}
+    return same and w_ok, stats
