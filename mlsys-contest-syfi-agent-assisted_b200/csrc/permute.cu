@@ -10,8 +10,6 @@
 // token t in expert e is the number of earlier tokens with bit e set; CTA e computes
 // that with ballots.  Every expert's row range is padded to a multiple of 16 rows
 // (the tcgen05 N granularity), padding rows carry token -1 and zero data.
-#include <cstdlib>
-
 #include "moe_internal.h"
 #include "ptx.cuh"
 
@@ -183,8 +181,7 @@ cudaError_t launch_build_rows(int T, int e_local, int expert_offset, int token_t
                             ws.row_cap, token_tile, ws.status, ws.ready, ws.counts_last);
   // from 4096 tokens on, four CTAs per expert (each ranks a quarter of the tokens after counting the expert's
   // rows in the quarters before it): 18 -> about 8 us at 8192 tokens
-  int splits = T >= 4096 ? 4 : 1;
-  if (const char* v = getenv("SYFI_DEBUG_ROW_SPLITS")) splits = atoi(v) > 0 ? atoi(v) : splits;
+  const int splits = T >= 4096 ? 4 : 1;
   return launch_dependent(build_rows_kernel<1024>, dim3(e_local, splits), dim3(1024), 0, st, T, e_local, expert_offset,
                           ws.local_mask, ws.counts, ws.topk_idx, ws.row_token, ws.route_row, ws.work, ws.meta,
                           ws.row_cap, token_tile, ws.status, ws.ready, ws.counts_last);
