@@ -49,7 +49,7 @@ def test_routing_with_skewed_logits(pkg, oracle):
 
 
 # -------------------------------------------------------------- permutation
-@pytest.mark.parametrize("T,E,off", [(64, 32, 0), (300, 8, 0), (129, 4, 36)])
+@pytest.mark.parametrize("T,E,off", [(64, 32, 0), (300, 8, 0), (129, 4, 36), (5000, 32, 0), (8200, 5, 16)])
 def test_row_lists(T, E, off, pkg):
     inp = pkg.make_inputs(num_tokens=T, seed=1, e_local=E, local_expert_offset=off, device=DEV)
     _, stats = _run(pkg, inp)
@@ -81,7 +81,7 @@ def test_row_lists(T, E, off, pkg):
     # per-expert work table: row ranges tile the padded row space, token tiles are counted consistently
     work, _ = ctx.debug_read("expert_work", torch.int32)
     work = work.view(32, 4)[:E]
-    tile = 32 if T <= 1024 else 64
+    tile = 32 if T <= 1024 else 64 if T < 6144 else 128     # from 4096 tokens on, four CTAs share an expert's tokens
     bounds = torch.cumsum(torch.cat([torch.zeros(1, dtype=torch.long), pad]), 0)
     tile_off = 0
     for e, (row_off, rows_pad, t_off, tiles) in enumerate(work.tolist()):
@@ -147,6 +147,16 @@ def _check_against_gpu_oracle(pkg, oracle, inp):
     ok, ostats = oracle.check_output(out, ref)
     assert ok, (ostats, stats)
     return out, stats
+
+
+def test_twice_the_largest_configuration_matches_oracle(pkg, oracle):
+    """16384 tokens, 32 local experts: twice the largest configuration (experts with up to ~2600 rows,
+    ~18000 routed rows), against the oracle run with torch on the GPU."""
+    inp = pkg.make_inputs(num_tokens=16384, seed=0, e_local=32, device=DEV)
+    _, stats = _check_against_gpu_oracle(pkg, oracle, inp)
+    assert stats["routes"] > 16384 and stats["active_experts"] >= 30
+    del inp
+    torch.cuda.empty_cache()
 
 
 def test_full_prefill_configuration_matches_oracle(pkg, oracle):
