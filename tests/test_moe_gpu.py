@@ -470,12 +470,13 @@ def test_argument_validation(pkg):
     pkg.get_context(0).check()
 
 
-@pytest.mark.parametrize("T,E,seed", [(8, 2, 3), (77, 8, 4), (1500, 32, 5)])
+@pytest.mark.parametrize("T,E,seed", [(8, 2, 3), (77, 8, 4), (1500, 32, 5), (6200, 6, 9)])
 def test_token_dispatch_on_one_rank_equals_the_plain_layer(T, E, seed, pkg):
     """The token-dispatch entry point with a world of one rank: route, publish, pull the routed rows from
     the rank's own region, the layer from the row lists on, push and final sum.  Everything but the link is
     exercised, and the result must equal the plain layer bit for bit — over several steps on different
-    tokens (alternating buffer sets) and interleaved with the all-gather layout on the same region."""
+    tokens (alternating buffer sets) and interleaved with the all-gather layout on the same region.  The
+    largest case runs the CTA-pair kernels, whose GEMM2 epilogue then stores through the row targets."""
     nbytes = pkg.ep_region_bytes(1, T)
     region = torch.zeros(nbytes, dtype=torch.uint8, device=DEV)
     desc = pkg.EpDesc()
