@@ -260,7 +260,11 @@ int syfi_moe_debug_read(syfi_moe_ctx* ctx, const char* name, void* dst_host, int
  *   wait_limit_cycles  SM clocks any wait inside the GEMM kernels may take (0 = the normal limit, 2^32);
  *   mask               1 = GEMM1's TMA producer issues nothing (its MMA / epilogue waits run out: status
  *                      102 / 103), 2 = GEMM1 is not launched (GEMM2's wait for GEMM1's experts runs out:
- *                      106), 4 = GEMM2 is not launched, 8 = GEMM2's TMA producer issues nothing.
+ *                      106), 4 = GEMM2 is not launched, 8 = GEMM2's TMA producer issues nothing;
+ *                      expert-parallel entry points only: 16 = the step stops after this rank has raised its
+ *                      flags (no owners' sum), 32 = only the owners' sum of the step runs (the routing of the
+ *                      previous call on this context is used) — with these a test walks several ranks through
+ *                      a step on one GPU, rank after rank, with no kernel waiting for a later launch.
  * Nothing faults, traps or spins without limit: the roles give up, the kernel frees its tensor memory and
  * returns, syfi_moe_check reports the status, and the context stays usable.  The output of such a call is
  * undefined. */

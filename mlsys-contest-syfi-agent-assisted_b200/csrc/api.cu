@@ -692,14 +692,29 @@ int ep_layer_and_return(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep, uint32_t 
                         const void* w13_scale, const void* w2, const void* w2_scale, int64_t tokens_all,
                         int32_t e_local, int64_t offset, double scaling, void* output, int flags, cudaStream_t st) {
   const bool fused = ep_rows_in_gemm2();
-  if (fused) { ctx->ep_rows = ep; ctx->ep_rows_seq = seq; }
-  int rc = run_layer(ctx, logits, bias, hs, hs_scale, w13, w13_scale, w2, w2_scale, tokens_all, e_local, offset,
-                     scaling, nullptr, flags, st);
-  ctx->ep_rows = nullptr;
-  if (rc) return rc;
-  if (fused) CU_TRY(launch_ep_raise_final(*ep, seq, ctx->ws, output, st));
-  else CU_TRY(launch_ep_push_final(*ep, seq, ctx->ws, output, ctx->ws.ep_ticket, st));
-  ctx->launches += 2;
+  // test hook (syfi_moe_debug_fault, bits 16 and 32): a step cut in two, so that a test can walk several ranks
+  // through one step on ONE GPU, one after the other — all ranks up to their flags, then all owners' sums —
+  // without any kernel waiting for a kernel launched later
+  const int phase = fused ? (ctx->fault_mask & (16 | 32)) : 0;
+  ctx->fault_mask &= ~(16 | 32);
+  if (!(phase & 32)) {
+    if (fused) { ctx->ep_rows = ep; ctx->ep_rows_seq = seq; }
+    int rc = run_layer(ctx, logits, bias, hs, hs_scale, w13, w13_scale, w2, w2_scale, tokens_all, e_local, offset,
+                       scaling, nullptr, flags, st);
+    ctx->ep_rows = nullptr;
+    if (rc) return rc;
+    if (!fused) {
+      CU_TRY(launch_ep_push_final(*ep, seq, ctx->ws, output, ctx->ws.ep_ticket, st));
+      ctx->launches += 2;
+      return SYFI_MOE_OK;
+    }
+    CU_TRY(launch_ep_raise(*ep, seq, ctx->ws, st));
+    ctx->launches += 1;
+  }
+  if (!(phase & 16)) {
+    CU_TRY(launch_ep_final_rows(*ep, seq, ctx->ws, output, st));
+    ctx->launches += 1;
+  }
   return SYFI_MOE_OK;
 }
 
@@ -945,7 +960,8 @@ int syfi_moe_debug_read(syfi_moe_ctx* ctx, const char* name, void* dst_host, int
 
 int syfi_moe_debug_fault(syfi_moe_ctx* ctx, int32_t mask, int64_t wait_limit_cycles) {
   if (!ctx) return fail(SYFI_MOE_ERR_INVALID, "context is null");
-  if (mask < 0 || mask > 15) return fail(SYFI_MOE_ERR_INVALID, "mask must be a combination of 1, 2, 4 and 8");
+  if (mask < 0 || mask > 63 || (mask & 48) == 48)
+    return fail(SYFI_MOE_ERR_INVALID, "mask must be a combination of 1, 2, 4, 8 and one of 16, 32");
   if (wait_limit_cycles < 0) return fail(SYFI_MOE_ERR_INVALID, "wait_limit_cycles must not be negative");
   std::lock_guard<std::mutex> lock(ctx->mu);
   ctx->fault_mask = mask;

@@ -550,12 +550,15 @@ cudaError_t launch_ep_row_targets(const syfi_moe_ep_desc& d, uint32_t seq, const
                           ws.row_token, ws.meta, ws.row_cap, ws.row_out);
 }
 
-cudaError_t launch_ep_raise_final(const syfi_moe_ep_desc& d, uint32_t seq, const Workspace& ws, void* out_bf16,
-                                  cudaStream_t st) {
+cudaError_t launch_ep_raise(const syfi_moe_ep_desc& d, uint32_t seq, const Workspace& ws, cudaStream_t st) {
   const EpView v = make_view(d);
   ep_raise_kernel<<<1, 32, 0, st>>>(v, seq, ws.status);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_final_rows(const syfi_moe_ep_desc& d, uint32_t seq, const Workspace& ws, void* out_bf16,
+                                 cudaStream_t st) {
+  const EpView v = make_view(d);
   ep_final_rows_kernel<<<static_cast<int>(d.tokens_per_rank), kPushThreads, 0, st>>>(
       v, seq, ws.topk_w, static_cast<__nv_bfloat16*>(out_bf16), ws.status);
   return cudaGetLastError();

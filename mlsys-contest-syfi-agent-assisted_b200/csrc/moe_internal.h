@@ -170,8 +170,9 @@ cudaError_t launch_ep_dispatch(const syfi_moe_ep_desc& d, uint32_t seq, const vo
 // GEMM2 rows stored straight into the owners' memory: per-row target pointers (ws.row_out) before the GEMMs,
 // flags and the owners' sum over route slots after them
 cudaError_t launch_ep_row_targets(const syfi_moe_ep_desc& d, uint32_t seq, const Workspace& ws, cudaStream_t st);
-cudaError_t launch_ep_raise_final(const syfi_moe_ep_desc& d, uint32_t seq, const Workspace& ws, void* out_bf16,
-                                  cudaStream_t st);
+cudaError_t launch_ep_raise(const syfi_moe_ep_desc& d, uint32_t seq, const Workspace& ws, cudaStream_t st);
+cudaError_t launch_ep_final_rows(const syfi_moe_ep_desc& d, uint32_t seq, const Workspace& ws, void* out_bf16,
+                                 cudaStream_t st);
 cudaError_t launch_ep_push_final(const syfi_moe_ep_desc& d, uint32_t seq, const Workspace& ws, void* out_bf16,
                                  int* ticket, cudaStream_t st);
 

@@ -498,6 +498,48 @@ def test_token_dispatch_on_one_rank_equals_the_plain_layer(T, E, seed, pkg):
     assert stats["routes"] > 0      # the cases route rows to the local experts
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_ranks_walked_through_a_step_on_one_gpu_sum_to_the_plain_layer(world, pkg):
+    """Several ranks of the replicated-token layout on ONE GPU, one after the other: every rank runs its expert
+    slice up to its flags (GEMM2 storing each row into the region of the token's owner), then every owner sums
+    what arrived.  No kernel waits for a kernel launched later.  Three steps on different tokens (alternating
+    buffer sets); every owner's rows must equal the plain layer with all 32 experts bit for bit."""
+    T, per = 256, 256 // world
+    full = pkg.make_inputs(num_tokens=T, seed=41, e_local=32, device=DEV)
+    regions = [torch.zeros(pkg.ep_region_bytes(world, per), dtype=torch.uint8, device=DEV) for _ in range(world)]
+    descs = []
+    for r in range(world):
+        d = pkg.EpDesc()
+        d.world_size, d.rank, d.tokens_per_rank = world, r, per
+        for q in range(world):
+            d.region[q] = regions[q].data_ptr()
+        d.wait_limit_cycles = 1 << 27
+        descs.append(d)
+    ctx = pkg.get_context(0)
+    e_per = 32 // world
+    for step in range(1, 4):
+        tok = pkg.make_inputs(num_tokens=T, seed=500 + step, e_local=1, device="cpu")
+        lg, hs, sc = (t.to(DEV) for t in (tok.routing_logits, tok.hidden_states, tok.hidden_states_scale))
+        want = torch.empty(T, 7168, dtype=torch.bfloat16, device=DEV)
+        pkg.run_moe(lg, full.routing_bias, hs, sc, *full.args()[4:8], 0, 2.5, want)
+        outs = [torch.full((per, 7168), float("nan"), dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+
+        def call(r):
+            sl = slice(r * e_per, (r + 1) * e_per)
+            pkg.run_moe_ep_replicated(descs[r], step, lg, full.routing_bias, hs, sc, full.gemm1_weights[sl],
+                                      full.gemm1_weights_scale[sl], full.gemm2_weights[sl],
+                                      full.gemm2_weights_scale[sl], r * e_per, 2.5, outs[r])
+        for r in range(world):          # every rank up to its flags
+            ctx.debug_fault(16, 0)
+            call(r)
+        for r in range(world):          # every owner's sum
+            ctx.debug_fault(32, 0)
+            call(r)
+        ctx.check()
+        got = torch.cat(outs, 0)
+        assert torch.equal(got, want), (step, float((got.float() - want.float()).abs().max()))
+
+
 def test_peer_wait_runs_out_without_hanging(pkg):
     """Failure detection without a GPU fault: an expert-parallel step whose 'peer' never publishes
     (a second local buffer stands in for rank 1).  The flag waits give up after their limit (set short
