@@ -264,7 +264,9 @@ int syfi_moe_debug_read(syfi_moe_ctx* ctx, const char* name, void* dst_host, int
  *                      expert-parallel entry points only: 16 = the step stops after this rank has raised its
  *                      flags (no owners' sum), 32 = only the owners' sum of the step runs (the routing of the
  *                      previous call on this context is used) — with these a test walks several ranks through
- *                      a step on one GPU, rank after rank, with no kernel waiting for a later launch.
+ *                      a step on one GPU, rank after rank, with no kernel waiting for a later launch;
+ *                      syfi_moe_ep_forward_dispatch only: 64 = the step stops after the rank has published its
+ *                      tokens, 128 = the step starts behind the publication (at the pull).
  * Nothing faults, traps or spins without limit: the roles give up, the kernel frees its tensor memory and
  * returns, syfi_moe_check reports the status, and the context stays usable.  The output of such a call is
  * undefined. */

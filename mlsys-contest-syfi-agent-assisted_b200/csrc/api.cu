@@ -817,23 +817,35 @@ int syfi_moe_ep_forward_dispatch(syfi_moe_ctx* ctx, const syfi_moe_ep_desc* ep, 
   if ((rc = ensure_ep_gather(ctx, need))) return rc;
   char* g = static_cast<char*>(ctx->ep_gather);
   const uint32_t seq = (uint32_t)step;
-  // 1. route this rank's own tokens; ids and weights go straight into the step's in-buffer of the region
-  //    (no expert counts as local here: masks and row counters are made by the pull, per destination)
-  Workspace own = ctx->ws;
-  ep_dispatch_route_targets(*ep, seq, &own.topk_idx, &own.topk_w);
-  if (!ctx->counters_clean) CU_TRY(cudaMemsetAsync(ctx->ws.counts, 0, sizeof(int) * 2 * kMaxLocalExperts, st));
-  ctx->counters_clean = false;
-  CU_TRY(launch_router(static_cast<const float*>(routing_logits), routing_bias, (int)T, 0, 0,
-                       (float)routed_scaling_factor, own, true, st));
-  // 2. publish rows and scales, pull the rows routed to this rank's experts from every rank
-  CU_TRY(launch_ep_dispatch(*ep, seq, hidden_states, hidden_states_scale, num_local_experts, (int)local_expert_offset,
-                            ctx->ws, g + o_hs, g + o_sc, ctx->num_sms, st));
-  // 3. the layer from the row lists on, 4. partial rows back to the tokens' owners, summed there
+  // test hook (syfi_moe_debug_fault, bits 64 and 128): the step may stop after the publication or start behind
+  // it, so that a test can walk several ranks through a step on one GPU
+  const int dphase = ctx->fault_mask & (64 | 128);
+  ctx->fault_mask &= ~(64 | 128);
+  if (!(dphase & 128)) {
+    // 1. route this rank's own tokens; ids and weights go straight into the step's in-buffer of the region
+    //    (no expert counts as local here: masks and row counters are made by the pull, per destination)
+    Workspace own = ctx->ws;
+    ep_dispatch_route_targets(*ep, seq, &own.topk_idx, &own.topk_w);
+    CU_TRY(launch_router(static_cast<const float*>(routing_logits), routing_bias, (int)T, 0, 0,
+                         (float)routed_scaling_factor, own, true, st));
+    // 2. publish rows and scales
+    CU_TRY(launch_ep_dispatch_publish(*ep, seq, hidden_states, hidden_states_scale, ctx->ws, ctx->num_sms, st));
+    ctx->launches = 2;
+  }
+  if (dphase & 64) return SYFI_MOE_OK;
+  // 3. pull the rows routed to this rank's experts from every rank (the pull counts rows per expert)
+  if (!(ctx->fault_mask & 32)) {   // (bit 32 of the test hook: only the owners' sum is wanted)
+    if (!ctx->counters_clean) CU_TRY(cudaMemsetAsync(ctx->ws.counts, 0, sizeof(int) * 2 * kMaxLocalExperts, st));
+    ctx->counters_clean = false;
+    CU_TRY(launch_ep_dispatch_pull(*ep, seq, num_local_experts, (int)local_expert_offset, ctx->ws, g + o_hs, g + o_sc,
+                                   ctx->num_sms, st));
+  }
+  // 4. the layer from the row lists on, rows back to the tokens' owners, summed there
   rc = ep_layer_and_return(ctx, ep, seq, nullptr, routing_bias, g + o_hs, g + o_sc, gemm1_weights,
                            gemm1_weights_scale, gemm2_weights, gemm2_weights_scale, (int64_t)NT, num_local_experts,
                            local_expert_offset, routed_scaling_factor, output, kFlagRoutingGiven, st);
   if (rc) return rc;
-  ctx->launches += 3;
+  ctx->launches += 3;   // router, publish, pull
   return SYFI_MOE_OK;
 }
 
@@ -960,8 +972,8 @@ int syfi_moe_debug_read(syfi_moe_ctx* ctx, const char* name, void* dst_host, int
 
 int syfi_moe_debug_fault(syfi_moe_ctx* ctx, int32_t mask, int64_t wait_limit_cycles) {
   if (!ctx) return fail(SYFI_MOE_ERR_INVALID, "context is null");
-  if (mask < 0 || mask > 63 || (mask & 48) == 48)
-    return fail(SYFI_MOE_ERR_INVALID, "mask must be a combination of 1, 2, 4, 8 and one of 16, 32");
+  if (mask < 0 || mask > 255 || (mask & 48) == 48 || (mask & 192) == 192)
+    return fail(SYFI_MOE_ERR_INVALID, "mask must be a combination of 1, 2, 4, 8, one of 16 / 32 and one of 64 / 128");
   if (wait_limit_cycles < 0) return fail(SYFI_MOE_ERR_INVALID, "wait_limit_cycles must not be negative");
   std::lock_guard<std::mutex> lock(ctx->mu);
   ctx->fault_mask = mask;

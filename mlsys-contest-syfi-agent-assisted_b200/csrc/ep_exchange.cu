@@ -519,9 +519,8 @@ void ep_dispatch_route_targets(const syfi_moe_ep_desc& d, uint32_t seq, int** to
   *topk_w = reinterpret_cast<float*>(in + disp_w_off(v.T));
 }
 
-cudaError_t launch_ep_dispatch(const syfi_moe_ep_desc& d, uint32_t seq, const void* hs, const void* hs_scale,
-                               int e_local, int expert_offset, const Workspace& ws, void* g_hs, void* g_scale,
-                               int num_sms, cudaStream_t st) {
+cudaError_t launch_ep_dispatch_publish(const syfi_moe_ep_desc& d, uint32_t seq, const void* hs, const void* hs_scale,
+                                       const Workspace& ws, int num_sms, cudaStream_t st) {
   const EpView v = make_view(d);
   const long long vecs = static_cast<long long>(v.T) * (kHidden / 16);
   int pub = static_cast<int>((vecs + 256 * 4 - 1) / (256 * 4));       // about four 16-byte vectors per thread
@@ -529,8 +528,12 @@ cudaError_t launch_ep_dispatch(const syfi_moe_ep_desc& d, uint32_t seq, const vo
   if (pub < 1) pub = 1;
   ep_publish_tokens_kernel<<<pub, 256, 0, st>>>(v, seq, static_cast<const uint4*>(hs),
                                                static_cast<const float*>(hs_scale), ws.ep_ticket);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_dispatch_pull(const syfi_moe_ep_desc& d, uint32_t seq, int e_local, int expert_offset,
+                                    const Workspace& ws, void* g_hs, void* g_scale, int num_sms, cudaStream_t st) {
+  const EpView v = make_view(d);
   const int chunks = (v.T + kPullTokens - 1) / kPullTokens;
   int per_src = (num_sms * 8 + d.world_size - 1) / d.world_size;   // about eight CTAs per SM over all sources
   if (per_src > chunks) per_src = chunks;

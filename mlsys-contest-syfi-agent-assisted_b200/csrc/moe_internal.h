@@ -164,9 +164,10 @@ cudaError_t launch_ep_publish_gather(const syfi_moe_ep_desc& d, uint32_t seq, co
 // token dispatch: where the router of this rank's own tokens must write (inside the step's in-buffer), and the
 // publish + sparse pull that fills ws.topk_idx / topk_w / local_mask / route_row / counts for all W*T tokens
 void ep_dispatch_route_targets(const syfi_moe_ep_desc& d, uint32_t seq, int** topk_idx, float** topk_w);
-cudaError_t launch_ep_dispatch(const syfi_moe_ep_desc& d, uint32_t seq, const void* hs, const void* hs_scale,
-                               int e_local, int expert_offset, const Workspace& ws, void* g_hs, void* g_scale,
-                               int num_sms, cudaStream_t st);
+cudaError_t launch_ep_dispatch_publish(const syfi_moe_ep_desc& d, uint32_t seq, const void* hs, const void* hs_scale,
+                                       const Workspace& ws, int num_sms, cudaStream_t st);
+cudaError_t launch_ep_dispatch_pull(const syfi_moe_ep_desc& d, uint32_t seq, int e_local, int expert_offset,
+                                    const Workspace& ws, void* g_hs, void* g_scale, int num_sms, cudaStream_t st);
 // GEMM2 rows stored straight into the owners' memory: per-row target pointers (ws.row_out) before the GEMMs,
 // flags and the owners' sum over route slots after them
 cudaError_t launch_ep_row_targets(const syfi_moe_ep_desc& d, uint32_t seq, const Workspace& ws, cudaStream_t st);

@@ -540,6 +540,50 @@ def test_ranks_walked_through_a_step_on_one_gpu_sum_to_the_plain_layer(world, pk
         assert torch.equal(got, want), (step, float((got.float() - want.float()).abs().max()))
 
 
+@pytest.mark.parametrize("world", [2, 4])
+def test_ranks_walked_through_a_dispatch_step_on_one_gpu(world, pkg):
+    """Token dispatch between several ranks on ONE GPU, in three sweeps over the ranks: every rank routes and
+    publishes its own tokens; every rank pulls the rows routed to its experts out of the OTHER ranks' regions,
+    runs its experts and stores the rows into the owners' regions; every owner sums.  Different tokens on every
+    rank and in every step; each rank's output must equal the plain layer with all 32 experts on its tokens."""
+    per, e_per = 96, 32 // world
+    full = pkg.make_inputs(num_tokens=8, seed=43, e_local=32, device=DEV)
+    regions = [torch.zeros(pkg.ep_region_bytes(world, per), dtype=torch.uint8, device=DEV) for _ in range(world)]
+    descs = []
+    for r in range(world):
+        d = pkg.EpDesc()
+        d.world_size, d.rank, d.tokens_per_rank = world, r, per
+        for q in range(world):
+            d.region[q] = regions[q].data_ptr()
+        d.wait_limit_cycles = 1 << 27
+        descs.append(d)
+    ctx = pkg.get_context(0)
+    for step in range(1, 4):
+        toks, wants = [], []
+        for r in range(world):
+            tk = pkg.make_inputs(num_tokens=per, seed=600 + 10 * step + r, e_local=1, device="cpu")
+            lg, hs, sc = (t.to(DEV) for t in (tk.routing_logits, tk.hidden_states, tk.hidden_states_scale))
+            toks.append((lg, hs, sc))
+            w = torch.empty(per, 7168, dtype=torch.bfloat16, device=DEV)
+            pkg.run_moe(lg, full.routing_bias, hs, sc, *full.args()[4:8], 0, 2.5, w)
+            wants.append(w)
+        outs = [torch.full((per, 7168), float("nan"), dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+
+        def call(r):
+            sl = slice(r * e_per, (r + 1) * e_per)
+            lg, hs, sc = toks[r]
+            pkg.run_moe_ep(descs[r], step, lg, full.routing_bias, hs, sc, full.gemm1_weights[sl],
+                           full.gemm1_weights_scale[sl], full.gemm2_weights[sl], full.gemm2_weights_scale[sl],
+                           r * e_per, 2.5, outs[r], dispatch=True)
+        for mask in (64, 128 | 16, 128 | 32):     # publish; pull + experts + flags; owners' sums
+            for r in range(world):
+                ctx.debug_fault(mask, 0)
+                call(r)
+        ctx.check()
+        for r in range(world):
+            assert torch.equal(outs[r], wants[r]), (step, r, float((outs[r].float() - wants[r].float()).abs().max()))
+
+
 def test_peer_wait_runs_out_without_hanging(pkg):
     """Failure detection without a GPU fault: an expert-parallel step whose 'peer' never publishes
     (a second local buffer stands in for rank 1).  The flag waits give up after their limit (set short
