@@ -498,7 +498,7 @@ def test_token_dispatch_on_one_rank_equals_the_plain_layer(T, E, seed, pkg):
     assert stats["routes"] > 0      # the cases route rows to the local experts
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_ranks_walked_through_a_step_on_one_gpu_sum_to_the_plain_layer(world, pkg):
     """Several ranks of the replicated-token layout on ONE GPU, one after the other: every rank runs its expert
     slice up to its flags (GEMM2 storing each row into the region of the token's owner), then every owner sums
@@ -540,7 +540,7 @@ def test_ranks_walked_through_a_step_on_one_gpu_sum_to_the_plain_layer(world, pk
         assert torch.equal(got, want), (step, float((got.float() - want.float()).abs().max()))
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_ranks_walked_through_a_dispatch_step_on_one_gpu(world, pkg):
     """Token dispatch between several ranks on ONE GPU, in three sweeps over the ranks: every rank routes and
     publishes its own tokens; every rank pulls the rows routed to its experts out of the OTHER ranks' regions,
