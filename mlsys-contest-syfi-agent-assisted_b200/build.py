@@ -14,8 +14,9 @@ import sys
 
 CSRC = os.path.join(os.path.dirname(os.path.abspath(__file__)), "csrc")
 LIB = os.path.join(CSRC, "libsyfi_moe.so")
-SOURCES = ["api.cu", "router.cu", "permute.cu", "grouped_gemm.cu", "grouped_gemm_pair.cu", "combine.cu", "ep_exchange.cu", "prepack.cu"]
-HEADERS = ["moe_internal.h", "ptx.cuh", os.path.join("..", "..", "include", "syfi_moe.h")]
+SOURCES = ["api.cu", "router.cu", "permute.cu", "grouped_gemm.cu", "grouped_gemm_pair.cu", "combine.cu", "ep_exchange.cu", "prepack.cu", "dsa_indexer.cu"]
+HEADERS = ["moe_internal.h", "ptx.cuh", os.path.join("..", "..", "include", "syfi_moe.h"),
+           os.path.join("..", "..", "include", "syfi_dsa.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-shared", "-Xptxas", "-v"]
 

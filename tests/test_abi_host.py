@@ -127,3 +127,16 @@ def test_layer_is_registered_as_a_torch_operator(pkg):
     schema = str(op.default._schema)
     assert "Tensor(a10!) output" in schema and schema.rstrip().endswith("-> ()"), schema
     assert schema.count("Tensor") == 9
+
+
+def test_indexer_header_symbols_are_exported_and_bound(pkg):
+    """Every function include/syfi_dsa.h declares is exported by the shared library and bound by the Python mirror."""
+    from importlib import import_module
+    text = open(os.path.join(ROOT, "include", "syfi_dsa.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    names = sorted(set(re.findall(r"\b(syfi_dsa_[a-z0-9_]+)\s*\(", text)))
+    assert names == ["syfi_dsa_check", "syfi_dsa_topk_indexer"]
+    lib = ctypes.CDLL(pkg.library_path())
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/syfi_dsa.h but not exported"
+    assert sorted(import_module(pkg.__name__ + ".dsa").ABI.keys()) == names
