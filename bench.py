@@ -309,6 +309,66 @@ def gemm1_roofline(T, rows, active, stage_ms, peaks, world):
 
 
 # --------------------------------------------------------------------------- GPU arm
+def run_dsa_indexer(args):
+    """The sibling operator on one GPU: 32 sequences of 65536 tokens (2 M tokens, 277 MB of index cache: larger than
+    L2), scored and cut to the best 2048 each.  One JSON line: scored tokens per second, the HBM roofline of the
+    operator as a whole (algorithmic bytes = the cache bytes of the sequences' tokens + queries + output), the
+    reference's own entry point (pure torch, dsa_indexer/solution/python/dsa_topk_indexer.py, restated by the oracle)
+    evaluated on the same GPU and on the host cores, and one parity step."""
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the indexer has no CPU path")
+    pkg = importlib.import_module(PKG)
+    dsa_oracle = importlib.import_module("oracle.dsa_oracle")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    seq_lens = [65536] * 32
+    W, K = max(args.warmup, 3), max(min(args.steps, 100), 1)
+    inputs = tuple(t.to(dev) for t in dsa_oracle.make_inputs(seq_lens, seed=0))
+    q, cache, w, sl, table = inputs
+    out = torch.empty(len(seq_lens), dsa_oracle.TOPK, dtype=torch.int32, device=dev)
+
+    def step():
+        pkg.run_dsa_topk_indexer(q, cache, w, sl, table, out)
+    for _ in range(W):
+        step()
+    pkg.dsa_check()
+    peaks = measured_peaks()
+    sampler = ClockSampler(0)
+    sampler.start()
+    ms = time_layer(torch, step, K, torch.cuda.synchronize, None, dev)
+    sampler.sample()
+    clocks = sampler.finish()
+    pkg.dsa_check()
+    tokens = sum(seq_lens)
+    nbytes = tokens * 132 + q.numel() + w.numel() * 4 + out.numel() * 4
+    want, scores = dsa_oracle.topk_indexer(*inputs)           # the reference's torch code on this GPU: parity ...
+    ok, pstats = dsa_oracle.check_topk(out, want, scores, sl.cpu(), table.cpu())
+    ref_ms = time_layer(torch, lambda: dsa_oracle.topk_indexer(*inputs), 3, torch.cuda.synchronize, None, dev)   # ... and time
+    line = {"metric": "dsa_indexer_scored_tokens_per_s", "value": tokens / (ms / 1e3), "unit": "tokens/s", "n_gpus": 1,
+            "steps": K, "warmup": W, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f8e4m3", "data": "synthetic",
+            "config": {"workload": "dsa_topk_indexer_fp8_h64_d128_topk2048_ps64: 32 sequences of 65536 tokens, pages "
+                                   "scattered over a 277 MB cache, seed 0", "l2": "inputs larger than L2"},
+            "clocks": clocks, "gpu_launches": 2 * K,
+            "roofline": {"bound": "hbm", "achieved": nbytes / (ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
+                         "unit": "GB/s", "frac": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "traffic": None,
+                         "peak_source": peaks.get("source", "MEASURED_PEAKS.json"), "kernel": "dsa_score_kernel + dsa_select_kernel"},
+            "parity": {"ok": bool(ok), "selection": pstats,
+                       "against": "the reference's torch entry point restated by the oracle, evaluated on this GPU"},
+            "gpu_reference": {"impl": "the definition's configured entry point (pure torch) on the same GPU",
+                              "ms_per_step": ref_ms, "times_slower": ref_ms / ms}}
+    if not args.no_cpu_baseline:
+        small = dsa_oracle.make_inputs([65536] * 2, seed=0)
+        t0 = time.perf_counter()
+        dsa_oracle.topk_indexer(*small)
+        dt = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": 2 * 65536 / dt, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                                "sample": "the oracle on 2 of the 32 sequences, %.2f s" % dt}
+    print(json.dumps(line), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -322,9 +382,13 @@ def main():
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--no-parity", action="store_true")
     ap.add_argument("--no-gpu-reference", action="store_true")
+    ap.add_argument("--operator", default="moe", choices=["moe", "dsa-indexer"],
+                    help="dsa-indexer: the sibling operator (DSA top-k indexer) on one GPU instead of the MoE layer")
     args = ap.parse_args()
     if args.tokens is None:
         args.tokens = 8192 if args.config == 3 else 4096
+    if args.operator == "dsa-indexer":
+        return run_dsa_indexer(args)
     if args.impl == "reference":
         return run_reference_arm(args)
 

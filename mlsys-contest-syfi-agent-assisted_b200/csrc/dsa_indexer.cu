@@ -266,6 +266,7 @@ struct Scratch {
   float* scores = nullptr;
   size_t floats = 0;
   int* status = nullptr;
+  bool checked = false;
 };
 std::mutex g_mu;
 Scratch g_scratch[64];
@@ -290,13 +291,16 @@ extern "C" int syfi_dsa_topk_indexer(const void* q_index_fp8, const void* k_inde
     if (!p || (reinterpret_cast<uintptr_t>(p) & 15u)) return fail(SYFI_DSA_ERR_INVALID, "a tensor argument is null or not 16-byte aligned");
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return fail(SYFI_DSA_ERR_CUDA, "no current CUDA device: this library has no CPU path");
-  cudaDeviceProp prop;
-  if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess || prop.major != 10)
-    return fail(SYFI_DSA_ERR_CUDA, "this library is built for sm_100a (B200) only");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int max_ls = max_pages * kPage;
   std::lock_guard<std::mutex> lock(g_mu);
   Scratch& s = g_scratch[dev];
+  if (!s.checked) {     // once per device: the attribute queries cost more than the kernels
+    int major = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess || major != 10)
+      return fail(SYFI_DSA_ERR_CUDA, "this library is built for sm_100a (B200) only");
+    s.checked = true;
+  }
   const size_t need = static_cast<size_t>(batch) * max_ls;
   if (need > s.floats) {
     if (cudaDeviceSynchronize() != cudaSuccess) return fail(SYFI_DSA_ERR_CUDA, "device synchronisation failed");
