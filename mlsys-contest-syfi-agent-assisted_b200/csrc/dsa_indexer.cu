@@ -188,10 +188,11 @@ constexpr int kSelectChunk = 16 * kSelectThreads;   // 16384 positions per selec
 // lower position", and the cut is one exact item value: an 8-pass radix select over the 64 bits (one byte per
 // pass, a histogram in shared memory filled through warp-aggregated increments, since most scores of a sequence
 // share their top bytes), a compaction of the items at or above the cut, and a bitonic sort.
-// get(j) returns the calling thread's j-th item (j < per_thread), 0 where it has none.
+// get(j) returns the calling thread's j-th item (j < per_thread), 0 where it has none; without `sorted` the winners
+// are left in arbitrary order.
 template <typename Get>
-__device__ __forceinline__ void select_best(Get get, int per_thread, int k, unsigned long long* s_item, int* s_hist,
-                                            int* s_misc) {
+__device__ __forceinline__ void select_best(Get get, int per_thread, int k, bool sorted, unsigned long long* s_item,
+                                            int* s_hist, int* s_misc) {
   const int tid = threadIdx.x, lane = tid & 31;
   for (int i = tid; i < kKeep; i += kSelectThreads) s_item[i] = 0ull;
   unsigned long long prefix = 0ull, mask = 0ull;
@@ -206,14 +207,26 @@ __device__ __forceinline__ void select_best(Get get, int per_thread, int k, unsi
       if (bin < 256 && lane == __ffs(peers) - 1) atomicAdd(&s_hist[bin], __popc(peers));
     }
     __syncthreads();
-    if (tid == 0) {
-      int seen = 0, pick = 0;
-      for (int v = 255; v >= 0; --v) {
-        if (seen + s_hist[v] >= want) { pick = v; break; }
-        seen += s_hist[v];
+    // the byte value at which the count from the top reaches `want`: thread t < 256 owns value 255 - t, an
+    // inclusive scan in thread order counts the items with that byte or a larger one
+    int h = 0, incl = 0;
+    if (tid < 256) {
+      h = s_hist[255 - tid];
+      incl = h;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, d);
+        if (lane >= d) incl += up;
       }
-      s_misc[0] = pick;
-      s_misc[1] = seen;
+      if (lane == 31) s_misc[4 + (tid >> 5)] = incl;
+    }
+    __syncthreads();
+    if (tid < 256) {
+      for (int w = 0; w < (tid >> 5); ++w) incl += s_misc[4 + w];
+      if (incl >= want && incl - h < want) {
+        s_misc[0] = 255 - tid;
+        s_misc[1] = incl - h;
+      }
     }
     __syncthreads();
     prefix |= static_cast<unsigned long long>(s_misc[0]) << shift;
@@ -228,7 +241,8 @@ __device__ __forceinline__ void select_best(Get get, int per_thread, int k, unsi
     const unsigned long long it = get(j);
     if (it != 0ull && it >= cut) s_item[atomicAdd(&s_misc[2], 1)] = it;
   }
-  for (int size = 2; size <= kKeep; size <<= 1) {
+  // (the candidates a first-level CTA hands to the merge need no order)
+  for (int size = 2; sorted && size <= kKeep; size <<= 1) {
     for (int stride = size >> 1; stride > 0; stride >>= 1) {
       __syncthreads();
       for (int i = tid; i < kKeep / 2; i += kSelectThreads) {
@@ -264,7 +278,7 @@ dsa_select_kernel(const float* __restrict__ scores, int max_ls, const int32_t* _
                   int32_t* __restrict__ out) {
   __shared__ unsigned long long s_item[kKeep];
   __shared__ int s_hist[256];
-  __shared__ int s_misc[4];
+  __shared__ int s_misc[12];
   const int b = blockIdx.y, c = blockIdx.x, tid = threadIdx.x;
   const int n = min(seq_lens[b], max_ls);
   const int chunks = (n + kSelectChunk - 1) / kSelectChunk;
@@ -285,7 +299,7 @@ dsa_select_kernel(const float* __restrict__ scores, int max_ls, const int32_t* _
                   : 0ull;
   }
   const int k = min(kKeep, len);
-  select_best([&](int j) { return mine[j]; }, 16, k, s_item, s_hist, s_misc);
+  select_best([&](int j) { return mine[j]; }, 16, k, chunks == 1, s_item, s_hist, s_misc);
   if (chunks == 1) {
     write_tokens(s_item, k, block_table + static_cast<size_t>(b) * max_pages, o);
   } else {
@@ -301,7 +315,7 @@ dsa_merge_kernel(const unsigned long long* __restrict__ cand, int max_chunks, in
                  int32_t* __restrict__ out) {
   __shared__ unsigned long long s_item[kKeep];
   __shared__ int s_hist[256];
-  __shared__ int s_misc[4];
+  __shared__ int s_misc[12];
   const int b = blockIdx.x, tid = threadIdx.x;
   const int n = min(seq_lens[b], max_ls);
   const int chunks = (n + kSelectChunk - 1) / kSelectChunk;
@@ -310,7 +324,7 @@ dsa_merge_kernel(const unsigned long long* __restrict__ cand, int max_chunks, in
   const int total = chunks * kKeep;
   const int per_thread = (total + kSelectThreads - 1) / kSelectThreads;
   select_best([&](int j) { const int i = j * kSelectThreads + tid; return i < total ? src[i] : 0ull; }, per_thread,
-              kKeep, s_item, s_hist, s_misc);
+              kKeep, true, s_item, s_hist, s_misc);
   write_tokens(s_item, kKeep, block_table + static_cast<size_t>(b) * max_pages, out + static_cast<size_t>(b) * kKeep);
 }
 
