@@ -203,8 +203,12 @@ __device__ __forceinline__ void select_best(Get get, int per_thread, int k, bool
     for (int j = 0; j < per_thread; ++j) {
       const unsigned long long it = get(j);
       const int bin = (it != 0ull && (it & mask) == prefix) ? static_cast<int>((it >> shift) & 255ull) : 256;
-      const unsigned peers = __match_any_sync(0xffffffffu, bin);
-      if (bin < 256 && lane == __ffs(peers) - 1) atomicAdd(&s_hist[bin], __popc(peers));
+      if (shift >= 48) {      // sign and exponent: a handful of values, so the warp adds up its lanes first
+        const unsigned peers = __match_any_sync(0xffffffffu, bin);
+        if (bin < 256 && lane == __ffs(peers) - 1) atomicAdd(&s_hist[bin], __popc(peers));
+      } else if (bin < 256) { // mantissa and position bytes: spread out, and fewer items match the prefix each pass
+        atomicAdd(&s_hist[bin], 1);
+      }
     }
     __syncthreads();
     // the byte value at which the count from the top reaches `want`: thread t < 256 owns value 255 - t, an
@@ -323,8 +327,18 @@ dsa_merge_kernel(const unsigned long long* __restrict__ cand, int max_chunks, in
   const unsigned long long* src = cand + static_cast<size_t>(b) * max_chunks * kKeep;
   const int total = chunks * kKeep;
   const int per_thread = (total + kSelectThreads - 1) / kSelectThreads;
-  select_best([&](int j) { const int i = j * kSelectThreads + tid; return i < total ? src[i] : 0ull; }, per_thread,
-              kKeep, true, s_item, s_hist, s_misc);
+  if (per_thread <= 16) {   // up to 8 chunks (131072 tokens): the candidates stay in registers over the eight passes
+    unsigned long long mine[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int i = j * kSelectThreads + tid;
+      mine[j] = i < total ? src[i] : 0ull;
+    }
+    select_best([&](int j) { return mine[j]; }, 16, kKeep, true, s_item, s_hist, s_misc);
+  } else {
+    select_best([&](int j) { const int i = j * kSelectThreads + tid; return i < total ? src[i] : 0ull; }, per_thread,
+                kKeep, true, s_item, s_hist, s_misc);
+  }
   write_tokens(s_item, kKeep, block_table + static_cast<size_t>(b) * max_pages, out + static_cast<size_t>(b) * kKeep);
 }
 
