@@ -230,20 +230,28 @@ __device__ __forceinline__ void select_best(Get get, int per_thread, int k, bool
       if (incl >= want && incl - h < want) {
         s_misc[0] = 255 - tid;
         s_misc[1] = incl - h;
+        s_misc[3] = h;
       }
     }
     __syncthreads();
     prefix |= static_cast<unsigned long long>(s_misc[0]) << shift;
     mask |= 255ull << shift;
     want -= s_misc[1];
+    const bool all_taken = s_misc[3] == want;   // every item that still matches the prefix is wanted: no more passes
     __syncthreads();
+    if (all_taken) break;
   }
-  const unsigned long long cut = prefix;       // the k-th best item itself
+  const unsigned long long cut = prefix;       // the k-th best item (its leading bytes, when the passes stopped early)
   if (tid == 0) s_misc[2] = 0;
   __syncthreads();
-  for (int j = 0; j < per_thread; ++j) {
+  for (int j = 0; j < per_thread; ++j) {     // one counter increment per warp and round, not per winner
     const unsigned long long it = get(j);
-    if (it != 0ull && it >= cut) s_item[atomicAdd(&s_misc[2], 1)] = it;
+    const bool win = it != 0ull && it >= cut;
+    const unsigned winners = __ballot_sync(0xffffffffu, win);
+    int base = 0;
+    if (lane == 0 && winners != 0u) base = atomicAdd(&s_misc[2], __popc(winners));
+    base = __shfl_sync(0xffffffffu, base, 0);
+    if (win) s_item[base + __popc(winners & ((1u << lane) - 1u))] = it;
   }
   // (the candidates a first-level CTA hands to the merge need no order)
   for (int size = 2; sorted && size <= kKeep; size <<= 1) {
