@@ -2,6 +2,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
                     [--config 3|4] [--tokens T] [--no-cpu-baseline] [--no-decode] [--no-parity]
+                    [--operator moe|dsa-indexer]
 
 One "step" is one call of the layer on one batch of synthetic tokens.
 
@@ -12,8 +13,8 @@ Workloads (seeded synthetic tensors with the definition's shapes and value distr
   sharded by expert: rank r owns experts [32 r / N, 32 (r + 1) / N) (slices of the same seed-0
   weights), every rank holds all T tokens and computes the f32 partial of its experts; the partial rows
   are summed over the ranks and each rank ends with the bf16 rows of its own T / N tokens (a
-  reduce-scatter by rows, fused into the layer's combine kernel over NVLink peer memory; NCCL's
-  reduce-scatter when the ranks cannot map each other).  Total work is fixed as N grows: "strong"
+  reduce-scatter by rows, fused into GEMM2 over NVLink peer memory: its epilogue stores every expert row into
+  the memory of the token's owner, which sums them; NCCL's reduce-scatter when the ranks cannot map each other).  Total work is fixed as N grows: "strong"
   scaling.
 * config 4 (``--config 4``), the full 256-expert layer with load imbalance: T = 4096 tokens shared by
   all ranks, logits of 16 hot experts raised by 1.5, rank r owns experts [32 r, 32 r + 32) drawn from
@@ -36,6 +37,12 @@ sm_100a into ``baseline/_ref``), timed on the same GPU and workloads by ``baseli
 
 ``--impl reference`` times the CPU restatement of the definition's reference (the oracle) on the host
 cores, on a bounded sample of the same workload, and prints the same line.
+
+At N > 1 the line also carries ``return_leg`` (the step with GEMM2 storing its rows into the owners' memory against
+the step with the combine-and-push kernel), ``sharded`` (the serving layout, every rank bringing its own T / N tokens:
+token dispatch against the all-gather, and whether its output equals the replicated step's bit for bit) and an ``e2e``
+measured on the serving layout.  ``--operator dsa-indexer`` times the sibling operator (the DSA top-k indexer) on one
+GPU instead and prints a line of the same shape.
 """
 from __future__ import annotations
 
