@@ -192,7 +192,7 @@ constexpr int kSelectChunk = 16 * kSelectThreads;   // 16384 positions per selec
 // are left in arbitrary order.
 template <typename Get>
 __device__ __forceinline__ void select_best(Get get, int per_thread, int k, bool sorted, unsigned long long* s_item,
-                                            int* s_hist, int* s_misc) {
+                                            unsigned long long* s_swap, int* s_hist, int* s_misc) {
   const int tid = threadIdx.x, lane = tid & 31;
   for (int i = tid; i < kKeep; i += kSelectThreads) s_item[i] = 0ull;
   unsigned long long prefix = 0ull, mask = 0ull;
@@ -253,18 +253,45 @@ __device__ __forceinline__ void select_best(Get get, int per_thread, int k, bool
     base = __shfl_sync(0xffffffffu, base, 0);
     if (win) s_item[base + __popc(winners & ((1u << lane) - 1u))] = it;
   }
-  // (the candidates a first-level CTA hands to the merge need no order)
-  for (int size = 2; sorted && size <= kKeep; size <<= 1) {
-    for (int stride = size >> 1; stride > 0; stride >>= 1) {
-      __syncthreads();
-      for (int i = tid; i < kKeep / 2; i += kSelectThreads) {
-        const int lo = 2 * i - (i & (stride - 1));
-        const int hi = lo + stride;
-        const bool desc = (lo & size) == 0;
-        const unsigned long long a = s_item[lo], c = s_item[hi];
-        if ((a < c) == desc) { s_item[lo] = c; s_item[hi] = a; }
+  __syncthreads();
+  if (sorted) {
+    // Bitonic sort, descending, two adjacent items per thread in registers.  A compare-exchange at distance d pairs
+    // item i with item i ^ d: d = 1 is inside the thread, d = 2 .. 32 pairs this thread with lane ^ (d / 2) of its
+    // warp (shuffles, no barrier), d >= 64 goes through shared memory (two buffers in turn: one barrier per stage,
+    // 15 stages instead of 66 barriers).  The first of a pair keeps the larger item where the block of `size`
+    // items it lies in is sorted downwards ((i & size) == 0), the smaller one otherwise.
+    unsigned long long e0 = s_item[2 * tid], e1 = s_item[2 * tid + 1];
+    unsigned long long* buf = s_swap;
+    unsigned long long* other = s_item;
+    auto pick = [](unsigned long long a, unsigned long long c, bool keep_max) {
+      return keep_max ? (a > c ? a : c) : (a < c ? a : c);
+    };
+    for (int size = 2; size <= kKeep; size <<= 1) {
+      const bool desc = ((2 * tid) & size) == 0;
+      for (int stride = size >> 1; stride >= 64; stride >>= 1) {
+        buf[2 * tid] = e0;
+        buf[2 * tid + 1] = e1;
+        __syncthreads();
+        const int half = stride >> 1;
+        const int pt = tid ^ half;
+        const bool keep_max = ((tid & half) == 0) == desc;
+        e0 = pick(e0, buf[2 * pt], keep_max);
+        e1 = pick(e1, buf[2 * pt + 1], keep_max);
+        unsigned long long* t = buf; buf = other; other = t;
       }
+      for (int stride = (size >> 1) < 32 ? (size >> 1) : 32; stride >= 2; stride >>= 1) {
+        const int half = stride >> 1;
+        const bool keep_max = ((tid & half) == 0) == desc;
+        e0 = pick(e0, __shfl_xor_sync(0xffffffffu, e0, half), keep_max);
+        e1 = pick(e1, __shfl_xor_sync(0xffffffffu, e1, half), keep_max);
+      }
+      const unsigned long long hi = e0 > e1 ? e0 : e1, lo = e0 > e1 ? e1 : e0;
+      e0 = desc ? hi : lo;
+      e1 = desc ? lo : hi;
     }
+    __syncthreads();                             // every reader of either buffer is through
+    s_item[2 * tid] = e0;
+    s_item[2 * tid + 1] = e1;
   }
   __syncthreads();
 }
@@ -289,6 +316,7 @@ dsa_select_kernel(const float* __restrict__ scores, int max_ls, const int32_t* _
                   const int32_t* __restrict__ block_table, int max_pages, unsigned long long* __restrict__ cand,
                   int32_t* __restrict__ out) {
   __shared__ unsigned long long s_item[kKeep];
+  __shared__ unsigned long long s_swap[kKeep];   // second buffer of the sort
   __shared__ int s_hist[256];
   __shared__ int s_misc[12];
   const int b = blockIdx.y, c = blockIdx.x, tid = threadIdx.x;
@@ -311,7 +339,7 @@ dsa_select_kernel(const float* __restrict__ scores, int max_ls, const int32_t* _
                   : 0ull;
   }
   const int k = min(kKeep, len);
-  select_best([&](int j) { return mine[j]; }, 16, k, chunks == 1, s_item, s_hist, s_misc);
+  select_best([&](int j) { return mine[j]; }, 16, k, chunks == 1, s_item, s_swap, s_hist, s_misc);
   if (chunks == 1) {
     write_tokens(s_item, k, block_table + static_cast<size_t>(b) * max_pages, o);
   } else {
@@ -326,6 +354,7 @@ dsa_merge_kernel(const unsigned long long* __restrict__ cand, int max_chunks, in
                  const int32_t* __restrict__ seq_lens, const int32_t* __restrict__ block_table, int max_pages,
                  int32_t* __restrict__ out) {
   __shared__ unsigned long long s_item[kKeep];
+  __shared__ unsigned long long s_swap[kKeep];   // second buffer of the sort
   __shared__ int s_hist[256];
   __shared__ int s_misc[12];
   const int b = blockIdx.x, tid = threadIdx.x;
@@ -342,10 +371,10 @@ dsa_merge_kernel(const unsigned long long* __restrict__ cand, int max_chunks, in
       const int i = j * kSelectThreads + tid;
       mine[j] = i < total ? src[i] : 0ull;
     }
-    select_best([&](int j) { return mine[j]; }, 16, kKeep, true, s_item, s_hist, s_misc);
+    select_best([&](int j) { return mine[j]; }, 16, kKeep, true, s_item, s_swap, s_hist, s_misc);
   } else {
     select_best([&](int j) { const int i = j * kSelectThreads + tid; return i < total ? src[i] : 0ull; }, per_thread,
-                kKeep, true, s_item, s_hist, s_misc);
+                kKeep, true, s_item, s_swap, s_hist, s_misc);
   }
   write_tokens(s_item, kKeep, block_table + static_cast<size_t>(b) * max_pages, out + static_cast<size_t>(b) * kKeep);
 }
